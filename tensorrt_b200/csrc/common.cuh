@@ -1,0 +1,152 @@
+// Shared host/device helpers for the sm_100a BERT kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "bert_b200.h"
+
+namespace b200
+{
+
+// ---- host-side error plumbing -------------------------------------------------------------
+// No exception crosses the C ABI: every failure is a status code plus a thread-local message
+// (the reference logs through ILogger and returns nullptr / STATUS_FAILURE,
+// plugin/vc/checkMacrosPlugin.h:198-201, and may exit the process on assertion; this library never exits).
+void setLastError(char const* fmt, ...);
+char const* getLastError();
+
+#define B200_FAIL(code, ...)                                                                                           \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        ::b200::setLastError(__VA_ARGS__);                                                                             \
+        return (code);                                                                                                 \
+    } while (0)
+
+#define B200_REQUIRE(cond, ...)                                                                                        \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        if (!(cond))                                                                                                   \
+        {                                                                                                              \
+            ::b200::setLastError(__VA_ARGS__);                                                                         \
+            return BERT_B200_BAD_PARAM;                                                                                \
+        }                                                                                                              \
+    } while (0)
+
+inline int32_t checkLaunch(char const* what)
+{
+    cudaError_t const e = cudaPeekAtLastError();
+    if (e != cudaSuccess)
+    {
+        setLastError("%s: %s", what, cudaGetErrorString(e));
+        return BERT_B200_CUDA_ERROR;
+    }
+    return BERT_B200_OK;
+}
+
+inline bool aligned16(void const* p)
+{
+    return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+// Number of SMs of the current device (cached per device id).
+int32_t smCount();
+
+#ifdef __CUDACC__
+// ---- device helpers -----------------------------------------------------------------------
+
+__device__ __forceinline__ float warpSum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warpMax(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// 128-bit global load through the read-only path, no L1 allocation (streamed once).
+__device__ __forceinline__ uint4 ldgStream(void const* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// 128-bit global load kept in L1/L2 (parameters, re-used rows).
+__device__ __forceinline__ uint4 ldgKeep(void const* p)
+{
+    return __ldg(reinterpret_cast<uint4 const*>(p));
+}
+
+__device__ __forceinline__ void stgStream(void* p, uint4 v)
+{
+    asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void unpackHalf8(uint4 const& v, float (&f)[8])
+{
+    __half2 const* h = reinterpret_cast<__half2 const*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+    {
+        float2 const t = __half22float2(h[i]);
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ uint4 packHalf8(float const (&f)[8])
+{
+    uint4 v;
+    __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return v;
+}
+
+__device__ __forceinline__ void unpackChar4(uint32_t w, float (&f)[4])
+{
+    f[0] = static_cast<float>(static_cast<int8_t>(w & 0xff));
+    f[1] = static_cast<float>(static_cast<int8_t>((w >> 8) & 0xff));
+    f[2] = static_cast<float>(static_cast<int8_t>((w >> 16) & 0xff));
+    f[3] = static_cast<float>(static_cast<int8_t>(w >> 24));
+}
+
+// Round-to-nearest-even, saturate to [-128,127], pack four values into one word
+// (same result as the reference's float4_to_char4, plugin/common/common.cuh:482-504).
+__device__ __forceinline__ uint32_t packChar4(float a, float b, float c, float d)
+{
+    int32_t ia, ib, ic, id;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ia) : "f"(a));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ib) : "f"(b));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ic) : "f"(c));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(id) : "f"(d));
+    return (static_cast<uint32_t>(ia) & 0xffu) | ((static_cast<uint32_t>(ib) & 0xffu) << 8)
+        | ((static_cast<uint32_t>(ic) & 0xffu) << 16) | ((static_cast<uint32_t>(id) & 0xffu) << 24);
+}
+
+__device__ __forceinline__ int8_t quantChar(float a)
+{
+    int32_t ia;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ia) : "f"(a));
+    return static_cast<int8_t>(ia);
+}
+#endif // __CUDACC__
+
+} // namespace b200

@@ -1,0 +1,373 @@
+// Host-side BERT encoder driver: the layer loop that strings the plugin kernels together, in the
+// order the reference BERT network used them (EmbLayerNorm -> per layer: FC(QKV) -> QKVToContext ->
+// FC -> SkipLayerNorm -> FC+GELU -> FC -> SkipLayerNorm). The reference tree dropped that network
+// builder (demo/BERT, CHANGELOG.md:24); its plugin-level pieces are
+// plugin/embLayerNormPlugin/embLayerNormVarSeqlenPlugin.cpp:370-514, plugin/fcPlugin/fcPlugin.cpp:551-610,
+// plugin/bertQKVToContextPlugin/qkvToContextPlugin.cpp:1210-1324 and
+// plugin/skipLayerNormPlugin/skipLayerNormPlugin.cpp:698-785.
+//
+// All device memory (weights, workspace, I/O) belongs to the caller; nothing is allocated here.
+#include "common.cuh"
+
+#include <cmath>
+#include <new>
+#include <vector>
+
+struct bert_b200_encoder
+{
+    bert_b200_encoder_config cfg;
+    std::vector<bert_b200_layer_weights> layers;
+    int32_t lastLaunches = 0;
+};
+
+namespace b200
+{
+namespace
+{
+
+inline int64_t alignUp(int64_t v, int64_t a)
+{
+    return (v + a - 1) / a * a;
+}
+
+struct Workspace
+{
+    int32_t* ids;
+    int32_t* seg;
+    int32_t* cu;
+    uint32_t* status;
+    uint8_t* x;    // [T][E]   layer input / output
+    uint8_t* qkv;  // [T][3E]
+    uint8_t* ctx;  // [T][E]
+    uint8_t* ao;   // [T][E]   attention output projection, later FFN output projection
+    uint8_t* h1;   // [T][E]
+    uint8_t* f1;   // [T][F]
+    uint8_t* xf16; // [T][E]   FP16 copy of the embedding output (INT8 mode)
+    int64_t bytes;
+};
+
+Workspace carve(bert_b200_encoder_config const& c, int32_t maxTokens, int32_t maxBatch, void* base)
+{
+    int64_t const elem = c.type_id == BERT_B200_INT8 ? 1 : 2;
+    int64_t const T = maxTokens;
+    int64_t const E = c.hidden_size;
+    int64_t const F = c.ffn_size;
+    int64_t off = 0;
+    auto take = [&](int64_t n) {
+        int64_t const o = off;
+        off = alignUp(off + n, 1024);
+        return o;
+    };
+    int64_t const oIds = take(T * 4);
+    int64_t const oSeg = take(T * 4);
+    int64_t const oCu = take((static_cast<int64_t>(maxBatch) + 1) * 4);
+    int64_t const oStatus = take(16);
+    int64_t const oX = take(T * E * elem);
+    int64_t const oQkv = take(T * 3 * E * elem);
+    int64_t const oCtx = take(T * E * elem);
+    int64_t const oAo = take(T * E * elem);
+    int64_t const oH1 = take(T * E * elem);
+    int64_t const oF1 = take(T * F * elem);
+    int64_t const oXf = c.type_id == BERT_B200_INT8 ? take(T * E * 2) : oX;
+    Workspace w{};
+    auto* b = static_cast<uint8_t*>(base);
+    w.ids = reinterpret_cast<int32_t*>(b + oIds);
+    w.seg = reinterpret_cast<int32_t*>(b + oSeg);
+    w.cu = reinterpret_cast<int32_t*>(b + oCu);
+    w.status = reinterpret_cast<uint32_t*>(b + oStatus);
+    w.x = b + oX;
+    w.qkv = b + oQkv;
+    w.ctx = b + oCtx;
+    w.ao = b + oAo;
+    w.h1 = b + oH1;
+    w.f1 = b + oF1;
+    w.xf16 = b + oXf;
+    w.bytes = off;
+    return w;
+}
+
+__global__ void dequantKernel(int64_t const n16, int8_t const* __restrict__ in, __half* __restrict__ out, float const scale)
+{
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n16;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    {
+        uint4 const v = ldgStream(in + i * 16);
+        uint32_t const* w = reinterpret_cast<uint32_t const*>(&v);
+        float f[16];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+        {
+            float t[4];
+            unpackChar4(w[k], t);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                f[4 * k + j] = t[j] * scale;
+        }
+        float lo[8], hi[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            lo[j] = f[j];
+            hi[j] = f[8 + j];
+        }
+        stgStream(out + i * 16, packHalf8(lo));
+        stgStream(out + i * 16 + 8, packHalf8(hi));
+    }
+}
+
+int32_t checkConfig(bert_b200_encoder_config const* c)
+{
+    B200_REQUIRE(c != nullptr, "encoder: null config");
+    B200_REQUIRE(c->type_id == BERT_B200_FP16 || c->type_id == BERT_B200_INT8, "encoder: type_id %d", c->type_id);
+    B200_REQUIRE(c->num_layers > 0 && c->hidden_size > 0 && c->num_heads > 0 && c->ffn_size > 0, "encoder: bad sizes");
+    B200_REQUIRE(c->hidden_size == c->num_heads * 64, "encoder: head size must be 64 (hidden %d, heads %d)", c->hidden_size,
+        c->num_heads);
+    B200_REQUIRE(c->ffn_size % 16 == 0, "encoder: ffn_size must be a multiple of 16");
+    B200_REQUIRE(c->word_emb && c->pos_emb && c->tok_emb && c->emb_gamma && c->emb_beta && c->layers_host,
+        "encoder: null weight pointer");
+    return BERT_B200_OK;
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t bert_b200_encoder_workspace_size(bert_b200_encoder_config const* cfg, int32_t max_tokens, int32_t max_batch)
+{
+    if (checkConfig(cfg) != BERT_B200_OK || max_tokens < 0 || max_batch < 0)
+        return -1;
+    return carve(*cfg, max_tokens, max_batch, nullptr).bytes;
+}
+
+extern "C" int32_t bert_b200_encoder_create(bert_b200_encoder_config const* cfg, bert_b200_encoder** out)
+{
+    int32_t const st = checkConfig(cfg);
+    if (st != BERT_B200_OK)
+        return st;
+    B200_REQUIRE(out != nullptr, "encoder_create: null output");
+    auto* e = new (std::nothrow) bert_b200_encoder();
+    if (!e)
+        B200_FAIL(BERT_B200_FAILURE, "encoder_create: out of host memory");
+    e->cfg = *cfg;
+    e->layers.assign(cfg->layers_host, cfg->layers_host + cfg->num_layers);
+    e->cfg.layers_host = e->layers.data();
+    for (auto const& l : e->layers)
+    {
+        if (!(l.wt_qkv && l.b_qkv && l.wt_out && l.b_out && l.ln1_gamma && l.ln1_beta && l.wt_ffn1 && l.b_ffn1 && l.wt_ffn2
+                && l.b_ffn2 && l.ln2_gamma && l.ln2_beta))
+        {
+            delete e;
+            B200_FAIL(BERT_B200_BAD_PARAM, "encoder_create: null layer weight pointer");
+        }
+    }
+    *out = e;
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_destroy(bert_b200_encoder* enc)
+{
+    delete enc;
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_last_launch_count(bert_b200_encoder const* enc)
+{
+    return enc ? enc->lastLaunches : 0;
+}
+
+static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t B, int32_t total, int32_t maxSeqlen,
+    int32_t const* ids, int32_t const* seg, int32_t const* cu, Workspace const& w, void* output)
+{
+    bert_b200_encoder_config const& c = enc->cfg;
+    bool const i8 = c.type_id == BERT_B200_INT8;
+    int32_t const E = c.hidden_size;
+    int32_t const F = c.ffn_size;
+    int64_t const T = total;
+    int32_t launches = 0;
+    int32_t st;
+#define B200_STEP(call)                                                                                                \
+    do                                                                                                                 \
+    {                                                                                                                  \
+        st = (call);                                                                                                   \
+        if (st != BERT_B200_OK)                                                                                        \
+            return st;                                                                                                 \
+        ++launches;                                                                                                    \
+    } while (0)
+
+    if (cudaMemsetAsync(w.status, 0, sizeof(uint32_t), stream) != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward: clearing the status word failed");
+    // FP16: embedding output is the first layer input. INT8: additionally quantised with the first layer's input scale.
+    B200_STEP(bert_b200_emb_layer_norm_var_seqlen(stream, BERT_B200_FP16, E, B, maxSeqlen, total, ids, seg, cu, c.emb_beta,
+        c.emb_gamma, c.word_emb, c.pos_emb, c.tok_emb, c.vocab_size, c.type_vocab_size, i8 ? static_cast<void*>(w.xf16) : w.x,
+        nullptr, i8 ? reinterpret_cast<int8_t*>(w.x) : nullptr, i8 ? 1.f / enc->layers[0].s_in : 0.f));
+
+    float const rsqrtD = 0.125f; // head size 64
+    for (int32_t li = 0; li < c.num_layers; ++li)
+    {
+        bert_b200_layer_weights const& l = enc->layers[li];
+        bert_b200_fc_params fc{};
+        fc.type_id = c.type_id;
+        fc.out_type_id = c.type_id;
+        fc.m = T;
+        fc.status_word = w.status;
+
+        // QKV projection (+ bias)
+        fc.n = 3 * E;
+        fc.k = E;
+        fc.a = w.x;
+        fc.lda = E;
+        fc.wt = l.wt_qkv;
+        fc.c = w.qkv;
+        fc.ldc = 3 * E;
+        fc.bias = l.b_qkv;
+        fc.activation = BERT_B200_ACT_NONE;
+        fc.alpha = i8 ? l.s_in * l.s_wqkv : 1.f;
+        fc.out_scale = i8 ? 1.f / l.s_qkv : 1.f;
+        B200_STEP(bert_b200_fc(&fc, stream));
+
+        bert_b200_mha_params mha{};
+        mha.type_id = c.type_id;
+        mha.B = B;
+        mha.S = maxSeqlen;
+        mha.num_heads = c.num_heads;
+        mha.head_size = 64;
+        mha.total = total;
+        mha.qkv = w.qkv;
+        mha.out = w.ctx;
+        mha.cu_seqlens = cu;
+        mha.scale_bmm1 = i8 ? l.s_qkv * l.s_qkv * rsqrtD : rsqrtD;
+        mha.scale_softmax = i8 ? 1.f / c.dq_probs : 1.f;
+        mha.scale_bmm2 = i8 ? c.dq_probs * l.s_qkv / l.s_ctx : 1.f;
+        mha.status_word = w.status;
+        B200_STEP(bert_b200_mha(&mha, stream));
+
+        // attention output projection (bias is applied by the SkipLayerNorm that follows)
+        fc.n = E;
+        fc.k = E;
+        fc.a = w.ctx;
+        fc.lda = E;
+        fc.wt = l.wt_out;
+        fc.c = w.ao;
+        fc.ldc = E;
+        fc.bias = nullptr;
+        fc.alpha = i8 ? l.s_ctx * l.s_wout : 1.f;
+        fc.out_scale = i8 ? 1.f / l.s_attn_out : 1.f;
+        B200_STEP(bert_b200_fc(&fc, stream));
+
+        if (i8)
+            B200_STEP(bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
+                reinterpret_cast<int8_t*>(w.x), l.ln1_beta, l.ln1_gamma, reinterpret_cast<int8_t*>(w.h1), l.b_out,
+                l.s_attn_out, l.s_in, 1.f / l.s_ln1));
+        else
+            B200_STEP(bert_b200_skip_layer_norm(
+                stream, BERT_B200_FP16, E, T * E, w.ao, w.x, l.ln1_beta, l.ln1_gamma, w.h1, l.b_out));
+
+        // FFN up projection + bias + erf-GELU
+        fc.n = F;
+        fc.k = E;
+        fc.a = w.h1;
+        fc.lda = E;
+        fc.wt = l.wt_ffn1;
+        fc.c = w.f1;
+        fc.ldc = F;
+        fc.bias = l.b_ffn1;
+        fc.activation = BERT_B200_ACT_GELU_ERF;
+        fc.alpha = i8 ? l.s_ln1 * l.s_wffn1 : 1.f;
+        fc.out_scale = i8 ? 1.f / l.s_ffn1 : 1.f;
+        B200_STEP(bert_b200_fc(&fc, stream));
+
+        // FFN down projection
+        fc.n = E;
+        fc.k = F;
+        fc.a = w.f1;
+        fc.lda = F;
+        fc.wt = l.wt_ffn2;
+        fc.c = w.ao;
+        fc.ldc = E;
+        fc.bias = nullptr;
+        fc.activation = BERT_B200_ACT_NONE;
+        fc.alpha = i8 ? l.s_ffn1 * l.s_wffn2 : 1.f;
+        fc.out_scale = i8 ? 1.f / l.s_ffn2 : 1.f;
+        B200_STEP(bert_b200_fc(&fc, stream));
+
+        bool const last = li + 1 == c.num_layers;
+        if (i8)
+            B200_STEP(bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
+                reinterpret_cast<int8_t*>(w.h1), l.ln2_beta, l.ln2_gamma, reinterpret_cast<int8_t*>(w.x), l.b_ffn2, l.s_ffn2,
+                l.s_ln1, 1.f / l.s_out));
+        else
+            B200_STEP(bert_b200_skip_layer_norm(stream, BERT_B200_FP16, E, T * E, w.ao, w.h1, l.ln2_beta, l.ln2_gamma,
+                last ? output : static_cast<void*>(w.x), l.b_ffn2));
+    }
+    if (i8)
+    {
+        int64_t const n16 = T * E / 16;
+        int const grid = static_cast<int>(n16 / 256 + 1 < smCount() * 8 ? n16 / 256 + 1 : smCount() * 8);
+        dequantKernel<<<grid, 256, 0, stream>>>(
+            n16, reinterpret_cast<int8_t const*>(w.x), static_cast<__half*>(output), enc->layers.back().s_out);
+        B200_STEP(checkLaunch("dequantKernel"));
+    }
+#undef B200_STEP
+    enc->lastLaunches = launches;
+    return BERT_B200_OK;
+}
+
+static int32_t checkForward(bert_b200_encoder* enc, int32_t B, int32_t total, int32_t maxSeqlen, void const* a,
+    void const* b, void const* c, void* workspace, int64_t workspaceBytes, void* output, Workspace* w)
+{
+    B200_REQUIRE(enc != nullptr, "encoder_forward: null encoder");
+    B200_REQUIRE(B > 0 && total > 0 && maxSeqlen > 0 && maxSeqlen <= 512, "encoder_forward: bad sizes B=%d total=%d S=%d", B,
+        total, maxSeqlen);
+    B200_REQUIRE(maxSeqlen <= enc->cfg.max_positions, "encoder_forward: max_seqlen %d exceeds the position table (%d)",
+        maxSeqlen, enc->cfg.max_positions);
+    B200_REQUIRE(a && b && c && workspace && output, "encoder_forward: null pointer");
+    B200_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 1023u) == 0, "encoder_forward: workspace must be 1024-byte aligned");
+    *w = carve(enc->cfg, total, B, workspace);
+    B200_REQUIRE(w->bytes <= workspaceBytes, "encoder_forward: workspace too small (%lld < %lld)",
+        static_cast<long long>(workspaceBytes), static_cast<long long>(w->bytes));
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_forward(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids, int32_t const* segment_ids, int32_t const* cu_seqlens, void* workspace,
+    int64_t workspace_bytes, void* output)
+{
+    Workspace w{};
+    int32_t const st
+        = checkForward(enc, B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, workspace, workspace_bytes, output, &w);
+    if (st != BERT_B200_OK)
+        return st;
+    return forwardImpl(enc, static_cast<cudaStream_t>(stream), B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, w,
+        output);
+}
+
+extern "C" int32_t bert_b200_encoder_forward_host(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids_host, int32_t const* segment_ids_host, int32_t const* cu_seqlens_host,
+    void* workspace, int64_t workspace_bytes, void* output_dev, void* output_host)
+{
+    Workspace w{};
+    int32_t st = checkForward(enc, B, total, max_seqlen, input_ids_host, segment_ids_host, cu_seqlens_host, workspace,
+        workspace_bytes, output_dev, &w);
+    if (st != BERT_B200_OK)
+        return st;
+    B200_REQUIRE(output_host != nullptr, "encoder_forward_host: null output_host");
+    auto s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(w.ids, input_ids_host, sizeof(int32_t) * total, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w.seg, segment_ids_host, sizeof(int32_t) * total, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w.cu, cu_seqlens_host, sizeof(int32_t) * (B + 1), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host: H2D copy: %s", cudaGetErrorString(e));
+    st = forwardImpl(enc, s, B, total, max_seqlen, w.ids, w.seg, w.cu, w, output_dev);
+    if (st != BERT_B200_OK)
+        return st;
+    e = cudaMemcpyAsync(output_host, output_dev, sizeof(__half) * static_cast<size_t>(total) * enc->cfg.hidden_size,
+        cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess)
+        e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host: D2H copy: %s", cudaGetErrorString(e));
+    return BERT_B200_OK;
+}

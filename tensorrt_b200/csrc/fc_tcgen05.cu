@@ -1,0 +1,480 @@
+// Fully connected layer on the sm_100a tensor cores: C = epilogue(A * Wt^T).
+//
+// Replaces the cublasLtMatmul call of the reference FC plugin (plugin/fcPlugin/fcPlugin.cpp:551-610)
+// and the separate bias / GELU / quantise layers that follow it in the reference graph.
+//
+// Design (one persistent CTA per SM, 6 warps, warp specialised):
+//   warp 0  : TMA producer - A[128 x 128B] and Wt[BLOCK_N x 128B] tiles, 128-byte swizzle, into a
+//             STAGES-deep shared-memory ring guarded by full/empty mbarriers.
+//   warp 1  : allocates all 512 TMEM columns, then one lane issues tcgen05.mma (UMMA 128 x BLOCK_N x 16
+//             for FP16 / x 32 for INT8) with the accumulator in TMEM; tcgen05.commit releases ring
+//             stages and publishes finished accumulators.
+//   warps 2-5: epilogue - tcgen05.ld the accumulator (double buffered, so tile i+1's main loop
+//             overlaps tile i's epilogue), scale / bias / erf-GELU / quantise, 128-bit stores.
+// Every mbarrier wait is bounded (see sm100.cuh); on expiry the CTA drains, frees TMEM and exits,
+// and the status word tells the host.
+#include "sm100.cuh"
+
+#include <mutex>
+
+namespace b200
+{
+
+int32_t fcF32(bert_b200_fc_params const& p, cudaStream_t stream);
+
+namespace
+{
+
+constexpr int kBlockM = 128;
+constexpr int kRowBytes = 128; // one swizzle span = BLOCK_K * sizeof(In)
+constexpr int kTmemCols = 512;
+constexpr int kFcThreads = 192;
+
+struct FcArgs
+{
+    int64_t M, N, K;
+    void* C;
+    int64_t ldc;
+    float const* bias;
+    int32_t act;
+    float alpha;
+    float outScale;
+    uint32_t* statusWord;
+};
+
+template <int BLOCK_N>
+struct FcSmem
+{
+    static constexpr int kStages = BLOCK_N == 256 ? 4 : 6;
+    static constexpr int kABytes = kBlockM * kRowBytes;
+    static constexpr int kBBytes = BLOCK_N * kRowBytes;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierOff = kStages * kStageBytes;
+    // full[kStages], empty[kStages], accFull[2], accEmpty[2], tmem base, abort flag
+    static constexpr int kTotal = kBarrierOff + (2 * kStages + 4) * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024; // slack for 1024-byte alignment of the ring
+};
+
+// erf by Abramowitz-Stegun 7.1.26 (|error| <= 1.5e-7), two MUFU ops (rcp, ex2) per value.
+__device__ __forceinline__ float fastErf(float x)
+{
+    float const ax = fabsf(x);
+    float const t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
+    float p = fmaf(1.061405429f, t, -1.453152027f);
+    p = fmaf(p, t, 1.421413741f);
+    p = fmaf(p, t, -0.284496736f);
+    p = fmaf(p, t, 0.254829592f);
+    p *= t;
+    float const e = exp2f(-1.4426950408889634f * ax * ax);
+    float const r = fmaf(-p, e, 1.f);
+    return copysignf(r, x);
+}
+
+__device__ __forceinline__ float geluErf(float x)
+{
+    return 0.5f * x * (1.f + fastErf(x * 0.70710678118654752440f));
+}
+
+template <typename Out>
+__device__ __forceinline__ void storeChunk32(Out* dst, float const (&v)[32], float outScale, int validCols);
+
+template <>
+__device__ __forceinline__ void storeChunk32<__half>(__half* dst, float const (&v)[32], float, int validCols)
+{
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+    {
+        if (g * 8 < validCols)
+        {
+            float f[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                f[j] = v[g * 8 + j];
+            *reinterpret_cast<uint4*>(dst + g * 8) = packHalf8(f);
+        }
+    }
+}
+
+template <>
+__device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&v)[32], float outScale, int validCols)
+{
+#pragma unroll
+    for (int g = 0; g < 2; ++g)
+    {
+        if (g * 16 < validCols)
+        {
+            uint4 o;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                w[j] = packChar4(v[g * 16 + 4 * j] * outScale, v[g * 16 + 4 * j + 1] * outScale,
+                    v[g * 16 + 4 * j + 2] * outScale, v[g * 16 + 4 * j + 3] * outScale);
+            *reinterpret_cast<uint4*>(dst + g * 16) = o;
+        }
+    }
+}
+
+template <typename In, int BLOCK_N, typename Out>
+__global__ void __launch_bounds__(kFcThreads, 1)
+    fcTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, FcArgs const args)
+{
+    using L = FcSmem<BLOCK_N>;
+    constexpr bool kInt8 = sizeof(In) == 1;
+    constexpr int kBlockK = kRowBytes / sizeof(In);
+    constexpr int kUmmaKBytes = 32; // UMMA K = 16 halves or 32 bytes
+    constexpr uint32_t kIdesc
+        = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, static_cast<uint32_t>(kBlockM), static_cast<uint32_t>(BLOCK_N));
+
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + L::kStages * L::kABytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarrierOff);
+    uint64_t* empty = full + L::kStages;
+    uint64_t* accFull = empty + L::kStages;
+    uint64_t* accEmpty = accFull + 2;
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmpty + 2);
+    volatile uint32_t* abortFlag = tmemSlot + 1;
+
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < L::kStages; ++i)
+        {
+            mbarInit(&full[i], 1);
+            mbarInit(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i)
+        {
+            mbarInit(&accFull[i], 1);
+            mbarInit(&accEmpty[i], 128);
+        }
+        *abortFlag = 0;
+        fenceBarrierInit();
+        prefetchTensorMap(&mapA);
+        prefetchTensorMap(&mapB);
+    }
+    if (warp == 1)
+        tmemAlloc(tmemSlot, kTmemCols);
+    tcFenceBefore();
+    __syncthreads();
+    tcFenceAfter();
+    uint32_t const tmemBase = *tmemSlot;
+
+    int64_t const mBlocks = (args.M + kBlockM - 1) / kBlockM;
+    int64_t const nBlocks = (args.N + BLOCK_N - 1) / BLOCK_N;
+    int64_t const numTiles = mBlocks * nBlocks;
+    int const kBlocks = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
+
+    if (warp == 0)
+    {
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x)
+            {
+                int32_t const m0 = static_cast<int32_t>(tile / nBlocks) * kBlockM;
+                int32_t const n0 = static_cast<int32_t>(tile % nBlocks) * BLOCK_N;
+                for (int kb = 0; kb < kBlocks; ++kb)
+                {
+                    if (!mbarWait(&empty[stage], phase ^ 1u, abortFlag, kWaitStageFree))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    mbarArriveExpectTx(&full[stage], L::kStageBytes);
+                    tmaLoad2d(sA + stage * L::kABytes, &mapA, &full[stage], kb * kBlockK, m0);
+                    tmaLoad2d(sB + stage * L::kBBytes, &mapB, &full[stage], kb * kBlockK, n0);
+                    if (++stage == L::kStages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            // Tail: wait until the MMA side has released every stage, so that no tcgen05.commit
+            // arrival is still in flight towards this CTA's shared memory when it exits.
+            for (int i = 0; i < L::kStages && ok; ++i)
+            {
+                ok = mbarWait(&empty[stage], phase ^ 1u, abortFlag, kWaitStageFree);
+                if (++stage == L::kStages)
+                {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t accPhase = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < numTiles && ok; tile += gridDim.x)
+            {
+                if (!mbarWait(&accEmpty[acc], accPhase ^ 1u, abortFlag, kWaitAccFree))
+                    break;
+                tcFenceAfter();
+                uint32_t const dTmem = tmemBase + static_cast<uint32_t>(acc * BLOCK_N);
+                for (int kb = 0; kb < kBlocks; ++kb)
+                {
+                    if (!mbarWait(&full[stage], phase, abortFlag, kWaitTmaFull))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tcFenceAfter();
+                    uint32_t const aBase = smemAddr(sA + stage * L::kABytes);
+                    uint32_t const bBase = smemAddr(sB + stage * L::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k)
+                    {
+                        uint64_t const aDesc = makeSmemDesc(aBase + k * kUmmaKBytes, 16, 1024, kSwizzle128B);
+                        uint64_t const bDesc = makeSmemDesc(bBase + k * kUmmaKBytes, 16, 1024, kSwizzle128B);
+                        if (kInt8)
+                            mmaI8(dTmem, aDesc, bDesc, kIdesc, (kb | k) != 0);
+                        else
+                            mmaF16(dTmem, aDesc, bDesc, kIdesc, (kb | k) != 0);
+                    }
+                    tcCommit(&empty[stage]);
+                    if (++stage == L::kStages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                tcCommit(&accFull[acc]);
+                acc ^= 1;
+                if (acc == 0)
+                    accPhase ^= 1u;
+            }
+        }
+    }
+    else
+    {
+        int const quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        int acc = 0;
+        uint32_t accPhase = 0;
+        Out* const C = static_cast<Out*>(args.C);
+        for (int64_t tile = blockIdx.x; tile < numTiles; tile += gridDim.x)
+        {
+            int64_t const m0 = (tile / nBlocks) * kBlockM;
+            int64_t const n0 = (tile % nBlocks) * BLOCK_N;
+            if (!mbarWait(&accFull[acc], accPhase, abortFlag, kWaitAccFull))
+                break;
+            tcFenceAfter();
+            int64_t const row = m0 + quad * 32 + lane;
+            uint32_t const taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+#pragma unroll 1
+            for (int c = 0; c < BLOCK_N / 32; ++c)
+            {
+                uint32_t r[32];
+                tmemLoad32(taddr + c * 32, r);
+                tmemLoadWait();
+                int64_t const col = n0 + c * 32;
+                int const validCols = static_cast<int>(args.N - col < 32 ? args.N - col : 32);
+                if (validCols <= 0)
+                    continue; // warp-uniform
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                {
+                    float const a = kInt8 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
+                    v[j] = a * args.alpha;
+                }
+                if (args.bias)
+                {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                    {
+                        if (j < validCols)
+                        {
+                            float4 const b = __ldg(reinterpret_cast<float4 const*>(args.bias + col + j));
+                            v[j] += b.x;
+                            v[j + 1] += b.y;
+                            v[j + 2] += b.z;
+                            v[j + 3] += b.w;
+                        }
+                    }
+                }
+                if (args.act == BERT_B200_ACT_GELU_ERF)
+                {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        v[j] = geluErf(v[j]);
+                }
+                if (row < args.M)
+                    storeChunk32<Out>(C + row * args.ldc + col, v, args.outScale, validCols);
+            }
+            tcFenceBefore();
+            mbarArrive(&accEmpty[acc]);
+            acc ^= 1;
+            if (acc == 0)
+                accPhase ^= 1u;
+        }
+    }
+
+    __syncthreads();
+    uint32_t const aborted = *abortFlag;
+    if (aborted != 0)
+    {
+        // Give copies / MMAs still in flight a bounded time to land before shared memory and TMEM go away.
+        uint64_t const t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull)
+            __nanosleep(1000);
+        if (threadIdx.x == 0 && args.statusWord)
+            atomicMax(args.statusWord, aborted);
+        __syncthreads();
+    }
+    if (warp == 1)
+    {
+        __syncwarp();
+        tcFenceAfter();
+        tmemFree(tmemBase, kTmemCols);
+    }
+}
+
+template <typename In, int BLOCK_N, typename Out>
+int32_t launchFc(bert_b200_fc_params const& p, cudaStream_t stream)
+{
+    using L = FcSmem<BLOCK_N>;
+    constexpr int kBlockK = kRowBytes / sizeof(In);
+    CUtensorMapDataType const dt = sizeof(In) == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mapA, mapB;
+    {
+        uint64_t const dims[2] = {static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.m)};
+        uint64_t const strides[1] = {static_cast<uint64_t>(p.lda) * sizeof(In)};
+        uint32_t const box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(kBlockM)};
+        int32_t const st = makeTensorMap(&mapA, dt, 2, p.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    {
+        uint64_t const dims[2] = {static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.n)};
+        uint64_t const strides[1] = {static_cast<uint64_t>(p.k) * sizeof(In)};
+        uint32_t const box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(BLOCK_N)};
+        int32_t const st = makeTensorMap(&mapB, dt, 2, p.wt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    auto kernel = fcTcgen05Kernel<In, BLOCK_N, Out>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "fc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    int64_t const tiles = ((p.m + kBlockM - 1) / kBlockM) * ((p.n + BLOCK_N - 1) / BLOCK_N);
+    int const grid = static_cast<int>(tiles < smCount() ? tiles : smCount());
+    FcArgs args{p.m, p.n, p.k, p.c, p.ldc, p.bias, p.activation, p.alpha, p.out_scale, p.status_word};
+    kernel<<<grid, kFcThreads, L::kDynamic, stream>>>(mapA, mapB, args);
+    return checkLaunch("fcTcgen05Kernel");
+}
+
+// Tiles of 128 x BLOCK_N over the SMs: pick the BLOCK_N that wastes less of the last wave.
+int pickBlockN(int64_t m, int64_t n)
+{
+    if (n <= 128)
+        return 128;
+    int const sms = smCount();
+    auto cost = [&](int bn) {
+        int64_t const tiles = ((m + kBlockM - 1) / kBlockM) * ((n + bn - 1) / bn);
+        int64_t const waves = (tiles + sms - 1) / sms;
+        // time ~ waves * tile work; 128-wide tiles run the tensor pipe a little less efficiently
+        return static_cast<double>(waves) * bn * (bn == 128 ? 1.06 : 1.0);
+    };
+    return cost(128) < cost(256) ? 128 : 256;
+}
+
+} // namespace
+
+EncodeTiledFn getEncodeTiled()
+{
+    static std::mutex mtx;
+    static EncodeTiledFn fn = nullptr;
+    std::lock_guard<std::mutex> lock(mtx);
+    if (!fn)
+    {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+            && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+int32_t makeTensorMap(CUtensorMap* map, CUtensorMapDataType type, int rank, void const* base, uint64_t const* dims,
+    uint64_t const* stridesBytes, uint32_t const* box, CUtensorMapSwizzle swizzle)
+{
+    EncodeTiledFn const fn = getEncodeTiled();
+    if (!fn)
+        B200_FAIL(BERT_B200_NOT_INITIALIZED, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t d[5];
+    cuuint64_t s[4];
+    cuuint32_t b[5];
+    cuuint32_t es[5];
+    for (int i = 0; i < rank; ++i)
+    {
+        d[i] = dims[i];
+        b[i] = box[i];
+        es[i] = 1;
+        if (i > 0)
+            s[i - 1] = stridesBytes[i - 1];
+    }
+    CUresult const r = fn(map, type, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, s, b, es,
+        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        B200_FAIL(BERT_B200_BAD_PARAM, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return BERT_B200_OK;
+}
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int32_t bert_b200_fc(bert_b200_fc_params const* params, void* stream)
+{
+    B200_REQUIRE(params != nullptr, "fc: null params");
+    bert_b200_fc_params const& p = *params;
+    B200_REQUIRE(p.m >= 0 && p.n > 0 && p.k > 0, "fc: bad sizes m=%lld n=%lld k=%lld", static_cast<long long>(p.m),
+        static_cast<long long>(p.n), static_cast<long long>(p.k));
+    B200_REQUIRE(p.a && p.wt && p.c, "fc: null pointer");
+    B200_REQUIRE(p.lda >= p.k && p.ldc >= p.n, "fc: lda/ldc smaller than the row length");
+    B200_REQUIRE(p.activation == BERT_B200_ACT_NONE || p.activation == BERT_B200_ACT_GELU_ERF, "fc: unknown activation %d",
+        p.activation);
+    if (p.m == 0)
+        return BERT_B200_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (p.type_id == BERT_B200_FP32)
+    {
+        B200_REQUIRE(p.out_type_id == BERT_B200_FP32, "fc: FP32 input needs FP32 output");
+        return fcF32(p, s);
+    }
+    B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "fc: type_id %d", p.type_id);
+    B200_REQUIRE(p.m < (1ll << 31) && p.n < (1ll << 31) && p.k < (1ll << 31), "fc: sizes exceed the 32-bit TMA coordinates");
+    int const elem = p.type_id == BERT_B200_FP16 ? 2 : 1;
+    B200_REQUIRE((p.k * elem) % 16 == 0 && (p.lda * elem) % 16 == 0, "fc: row bytes of A / Wt must be a multiple of 16");
+    B200_REQUIRE(aligned16(p.a) && aligned16(p.wt) && aligned16(p.c), "fc: A, Wt and C must be 16-byte aligned");
+    B200_REQUIRE(p.n % 16 == 0, "fc: n=%lld must be a multiple of 16", static_cast<long long>(p.n));
+    B200_REQUIRE(!p.bias || aligned16(p.bias), "fc: bias must be 16-byte aligned");
+    int const outElem = p.out_type_id == BERT_B200_FP16 ? 2 : 1;
+    B200_REQUIRE((p.ldc * outElem) % 16 == 0, "fc: row bytes of C must be a multiple of 16");
+    int const bn = pickBlockN(p.m, p.n);
+    if (p.type_id == BERT_B200_FP16)
+    {
+        B200_REQUIRE(p.out_type_id == BERT_B200_FP16, "fc: FP16 input needs FP16 output");
+        return bn == 128 ? launchFc<__half, 128, __half>(p, s) : launchFc<__half, 256, __half>(p, s);
+    }
+    if (p.out_type_id == BERT_B200_INT8)
+        return bn == 128 ? launchFc<int8_t, 128, int8_t>(p, s) : launchFc<int8_t, 256, int8_t>(p, s);
+    B200_REQUIRE(p.out_type_id == BERT_B200_FP16, "fc: INT8 input needs INT8 or FP16 output");
+    return bn == 128 ? launchFc<int8_t, 128, __half>(p, s) : launchFc<int8_t, 256, __half>(p, s);
+}

@@ -1,0 +1,544 @@
+// Fused multi-head attention on the sm_100a tensor cores (head size 64, sequence length <= 512),
+// FP16 and INT8, fixed [S,B,N,3,d] and packed [total,N,3,d] layouts.
+//
+// Replaces the precompiled fused attention kernels the reference launches through
+// FusedMHARunnerFP16/Int8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265) and the
+// unfused cuBLAS + softmax path (mhaRunner.cu:533-601).
+//
+// One CTA = one (sequence, head, 128-query tile); 10 warps:
+//   warp 0    : TMA - Q tile and every 128-key K / V block of the sequence (swizzled, own mbarrier each).
+//   warp 1    : TMEM allocation; one lane issues tcgen05.mma:
+//                 S_j = Q K_j^T           (128 x 128 per key block, accumulators in TMEM columns 128j..)
+//                 O  += P_j V_j           (128 x 64, accumulator in TMEM columns 0..63, re-using S_0's columns)
+//   warps 2-9 : softmax, two threads per query row (each owns 64 of every 128 key columns):
+//                 pass A  row maximum over all key blocks straight from TMEM,
+//                 pass B  p = exp2(x*scale*log2e - max) -> FP16 P_j into swizzled shared memory for the PV product
+//                         (INT8: exp values go back to TMEM, pass C quantises p/sum*scale_softmax to INT8 P_j),
+//                 epilogue O / rowsum (INT8: O * scale_bmm2, round, saturate) -> 128-bit global stores.
+// The whole score row lives in TMEM, so the softmax uses the exact row maximum and never rescales O.
+// Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
+#include "sm100.cuh"
+
+namespace b200
+{
+
+int32_t mhaF32(bert_b200_mha_params const& p, cudaStream_t stream);
+
+namespace
+{
+
+constexpr int kQTile = 128;
+constexpr int kKeyBlock = 128;
+constexpr int kHeadSize = 64;
+constexpr int kMaxBlocks = 4; // S <= 512
+constexpr int kMhaThreads = 320;
+constexpr int kSoftmaxThreads = 256;
+
+struct MhaArgs
+{
+    int32_t B, S, N, total;
+    int32_t fixedLayout;
+    void* out;
+    int32_t const* cu;
+    int32_t const* maskIdx;
+    float scaleBmm1, scaleSoftmax, scaleBmm2;
+    uint32_t* statusWord;
+};
+
+template <typename T>
+struct MhaSmem
+{
+    static constexpr int kElem = sizeof(T);
+    static constexpr int kRowBytes = kHeadSize * kElem;           // 128 (FP16) or 64 (INT8)
+    static constexpr int kTileBytes = kQTile * kRowBytes;         // Q tile, one K block, one V block
+    static constexpr int kPBytes = kQTile * kKeyBlock * kElem;    // one P block: 32 KB (FP16) or 16 KB (INT8)
+    // [ P ring (2 blocks), overlaying Q and K once the scores are complete ][ V blocks ][ barriers ]
+    static __host__ __device__ constexpr int vOffset(int nb)
+    {
+        int const qk = (1 + nb) * kTileBytes;
+        return qk > 2 * kPBytes ? qk : 2 * kPBytes;
+    }
+    static __host__ __device__ constexpr int barrierOffset(int nb)
+    {
+        return vOffset(nb) + nb * kTileBytes;
+    }
+    static constexpr int kBarrierBytes = (kMaxBlocks * 4 + 2 + 1) * 8 + 16 + 2 * kQTile * 4 * 2;
+    static __host__ __device__ constexpr int dynamicBytes(int nb)
+    {
+        return barrierOffset(nb) + kBarrierBytes + 1024;
+    }
+};
+
+__device__ __forceinline__ float ex2Approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void softmaxBarrier()
+{
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmemStore32(uint32_t taddr, uint32_t const (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmemStoreWait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kMhaThreads, 1)
+    mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, MhaArgs const args)
+{
+    using L = MhaSmem<T>;
+    constexpr bool kInt8 = sizeof(T) == 1;
+    constexpr uint64_t kSwz = kInt8 ? kSwizzle64B : kSwizzle128B; // Q, K, V rows are 64 B (INT8) or 128 B (FP16)
+    constexpr uint32_t kAtomBytes = 8 * L::kRowBytes;             // 8 rows of a swizzle atom: SBO
+    constexpr int kQkMmas = kInt8 ? 2 : 4;                        // head size 64 = 2 x 32 (INT8) or 4 x 16 (FP16)
+    constexpr int kPvMmas = kInt8 ? 4 : 8;                        // 128 keys = 4 x 32 or 8 x 16
+    constexpr uint32_t kIdescQk = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, 128u, 128u);
+    constexpr uint32_t kIdescPv = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 1u, 128u, 64u);
+
+    int const qTile = blockIdx.x;
+    int const head = blockIdx.y;
+    int const b = blockIdx.z;
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+
+    // ---- sequence geometry (uniform over the CTA) ----
+    int32_t rowBase, rows, len;
+    if (args.fixedLayout)
+    {
+        rowBase = 0;
+        rows = args.S;
+        len = args.maskIdx ? min(max(__ldg(args.maskIdx + b), 0), args.S) : args.S;
+    }
+    else
+    {
+        rowBase = __ldg(args.cu + b);
+        len = min(max(__ldg(args.cu + b + 1) - rowBase, 0), args.S);
+        rows = len;
+    }
+    int const q0 = qTile * kQTile;
+    if (q0 >= rows)
+        return;
+    int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
+    T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(head) * kHeadSize;
+    auto outRow = [&](int q) -> T* {
+        int64_t const r = args.fixedLayout ? static_cast<int64_t>(q) * args.B + b : static_cast<int64_t>(rowBase) + q;
+        return outBase + r * outRowStride;
+    };
+    if (len == 0)
+    {
+        // no valid key: every probability is zero and so is the context row
+        for (int i = threadIdx.x; i < kQTile * (L::kRowBytes / 16); i += kMhaThreads)
+        {
+            int const q = q0 + i / (L::kRowBytes / 16);
+            if (q < rows)
+                reinterpret_cast<uint4*>(outRow(q))[i % (L::kRowBytes / 16)] = make_uint4(0, 0, 0, 0);
+        }
+        return;
+    }
+    int const nb = (len + kKeyBlock - 1) / kKeyBlock;
+    uint32_t const tmemCols = nb <= 1 ? 128u : (nb == 2 ? 256u : 512u);
+
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sP = smem;                          // 2 x kPBytes, valid once all scores are complete
+    uint8_t* sQ = smem;                          // kTileBytes
+    uint8_t* sK = smem + L::kTileBytes;          // nb x kTileBytes
+    uint8_t* sV = smem + L::vOffset(nb);         // nb x kTileBytes
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::barrierOffset(nb));
+    uint64_t* qkFull = bars;                     // [4] Q+K_0, K_1, ...
+    uint64_t* vFull = bars + kMaxBlocks;         // [4]
+    uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete
+    uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written (256 arrivals)
+    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [2] PV product consumed ring slot
+    uint64_t* oFull = pFree + 2;                 // [1]
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(oFull + 1);
+    volatile uint32_t* abortFlag = tmemSlot + 1;
+    float* rowRed = reinterpret_cast<float*>(tmemSlot + 4); // [2][2][128]: max then sum, per half
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < kMaxBlocks; ++i)
+        {
+            mbarInit(&qkFull[i], 1);
+            mbarInit(&vFull[i], 1);
+            mbarInit(&sFull[i], 1);
+            mbarInit(&pReady[i], kSoftmaxThreads);
+        }
+        mbarInit(&pFree[0], 1);
+        mbarInit(&pFree[1], 1);
+        mbarInit(oFull, 1);
+        *abortFlag = 0;
+        fenceBarrierInit();
+        prefetchTensorMap(&mapQkv);
+    }
+    if (warp == 1)
+        tmemAlloc(tmemSlot, tmemCols);
+    tcFenceBefore();
+    __syncthreads();
+    tcFenceAfter();
+    uint32_t const tmemBase = *tmemSlot;
+
+    if (warp == 0)
+    {
+        if (lane == 0)
+        {
+            int32_t const c1 = args.fixedLayout ? b : 0;
+            int32_t const rowQ = args.fixedLayout ? q0 : rowBase + q0;
+            int32_t const rowK = args.fixedLayout ? 0 : rowBase;
+            int32_t const colQ = head * 3 * kHeadSize;
+            mbarArriveExpectTx(&qkFull[0], 2 * L::kTileBytes);
+            tmaLoad3d(sQ, &mapQkv, &qkFull[0], colQ, c1, rowQ);
+            tmaLoad3d(sK, &mapQkv, &qkFull[0], colQ + kHeadSize, c1, rowK);
+            for (int j = 1; j < nb; ++j)
+            {
+                mbarArriveExpectTx(&qkFull[j], L::kTileBytes);
+                tmaLoad3d(sK + j * L::kTileBytes, &mapQkv, &qkFull[j], colQ + kHeadSize, c1, rowK + j * kKeyBlock);
+            }
+            for (int j = 0; j < nb; ++j)
+            {
+                mbarArriveExpectTx(&vFull[j], L::kTileBytes);
+                tmaLoad3d(sV + j * L::kTileBytes, &mapQkv, &vFull[j], colQ + 2 * kHeadSize, c1, rowK + j * kKeyBlock);
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0)
+        {
+            bool ok = true;
+            uint32_t const qAddr = smemAddr(sQ);
+            for (int j = 0; j < nb && ok; ++j)
+            {
+                ok = mbarWait(&qkFull[j], 0, abortFlag, kWaitTmaFull);
+                if (!ok)
+                    break;
+                tcFenceAfter();
+                uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kQkMmas; ++k)
+                {
+                    uint64_t const aDesc = makeSmemDesc(qAddr + k * 32, 16, kAtomBytes, kSwz);
+                    uint64_t const bDesc = makeSmemDesc(kAddr + k * 32, 16, kAtomBytes, kSwz);
+                    if (kInt8)
+                        mmaI8(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
+                    else
+                        mmaF16(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
+                }
+                tcCommit(&sFull[j]);
+            }
+            for (int j = 0; j < nb && ok; ++j)
+            {
+                ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull) && mbarWait(&pReady[j], 0, abortFlag, kWaitSoftmax);
+                if (!ok)
+                    break;
+                tcFenceAfter();
+                uint32_t const pAddr = smemAddr(sP + (j & 1) * L::kPBytes);
+                uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kPvMmas; ++k)
+                {
+                    // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
+                    uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
+                    uint64_t const aDesc = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
+                    // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
+                    uint64_t const bDesc = makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
+                    if (kInt8)
+                        mmaI8(tmemBase, aDesc, bDesc, kIdescPv, (j | k) != 0);
+                    else
+                        mmaF16(tmemBase, aDesc, bDesc, kIdescPv, (j | k) != 0);
+                }
+                if (j + 1 < nb)
+                    tcCommit(&pFree[j & 1]);
+                else
+                    tcCommit(oFull);
+            }
+        }
+    }
+    else
+    {
+        int const quad = warp & 3;
+        int const half = (warp - 2) >> 2; // which 64 of every 128 key columns this thread owns
+        int const r = quad * 32 + lane;   // query row inside the tile = TMEM lane
+        uint32_t const tRow = tmemBase + (static_cast<uint32_t>(quad * 32) << 16);
+        float const sl2 = args.scaleBmm1 * 1.4426950408889634f;
+        bool ok = true;
+
+        // ---- pass A: row maximum ----
+        float mx = -INFINITY;
+        for (int j = 0; j < nb && ok; ++j)
+        {
+            ok = mbarWait(&sFull[j], 0, abortFlag, kWaitSoftmax);
+            if (!ok)
+                break;
+            tcFenceAfter();
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+            {
+                int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                uint32_t x[32];
+                tmemLoad32(tRow + col0, x);
+                tmemLoadWait();
+                int const limit = len - col0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                {
+                    float const v = kInt8 ? static_cast<float>(static_cast<int32_t>(x[i])) : __uint_as_float(x[i]);
+                    if (i < limit)
+                        mx = fmaxf(mx, v);
+                }
+            }
+        }
+        rowRed[half * kQTile + r] = mx;
+        softmaxBarrier();
+        mx = fmaxf(rowRed[r], rowRed[kQTile + r]);
+        float const mOff = mx * sl2;
+
+        // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
+        float sum = 0.f;
+        for (int j = 0; j < nb && ok; ++j)
+        {
+            if (!kInt8 && j >= 2)
+            {
+                ok = mbarWait(&pFree[j & 1], ((j >> 1) - 1) & 1, abortFlag, kWaitSoftmax);
+                if (!ok)
+                    break;
+            }
+            uint8_t* pRow = sP + (j & 1) * L::kPBytes + half * (kQTile * 128) + r * 128;
+#pragma unroll
+            for (int c = 0; c < 2; ++c)
+            {
+                int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                uint32_t x[32];
+                tmemLoad32(tRow + col0, x);
+                tmemLoadWait();
+                int const limit = len - col0;
+                float p[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                {
+                    float const v = kInt8 ? static_cast<float>(static_cast<int32_t>(x[i])) : __uint_as_float(x[i]);
+                    float const e = ex2Approx(fmaf(v, sl2, -mOff));
+                    p[i] = i < limit ? e : 0.f;
+                    sum += p[i];
+                }
+                if (kInt8)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        x[i] = __float_as_uint(p[i]);
+                    tmemStore32(tRow + col0, x);
+                }
+                else
+                {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                    {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            f[i] = p[g * 8 + i];
+                        int const chunk = c * 4 + g; // 16-byte chunk inside the 128-byte row of this 64-key tile
+                        *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
+                    }
+                }
+            }
+            if (!kInt8)
+            {
+                fenceProxyAsync();
+                tcFenceBefore();
+                mbarArrive(&pReady[j]);
+            }
+        }
+        if (kInt8)
+            tmemStoreWait();
+        rowRed[2 * kQTile + half * kQTile + r] = sum;
+        softmaxBarrier();
+        sum = rowRed[2 * kQTile + r] + rowRed[3 * kQTile + r];
+        float const inv = 1.f / sum;
+
+        if (kInt8)
+        {
+            // ---- pass C (INT8): P_q = sat8(rni(p / sum * scale_softmax)) ----
+            float const pq = inv * args.scaleSoftmax;
+            for (int j = 0; j < nb && ok; ++j)
+            {
+                if (j >= 2)
+                {
+                    ok = mbarWait(&pFree[j & 1], ((j >> 1) - 1) & 1, abortFlag, kWaitSoftmax);
+                    if (!ok)
+                        break;
+                }
+                uint8_t* pRow = sP + (j & 1) * L::kPBytes + r * 128;
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                {
+                    int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                    uint32_t x[32];
+                    tmemLoad32(tRow + col0, x);
+                    tmemLoadWait();
+#pragma unroll
+                    for (int g = 0; g < 2; ++g)
+                    {
+                        uint4 o;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = packChar4(__uint_as_float(x[g * 16 + 4 * i]) * pq,
+                                __uint_as_float(x[g * 16 + 4 * i + 1]) * pq, __uint_as_float(x[g * 16 + 4 * i + 2]) * pq,
+                                __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                        int const chunk = half * 4 + c * 2 + g; // 16 keys per 16-byte chunk, 128 keys per row
+                        *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
+                    }
+                }
+                fenceProxyAsync();
+                tcFenceBefore();
+                mbarArrive(&pReady[j]);
+            }
+        }
+
+        // ---- epilogue: normalise / requantise the context row ----
+        if (ok)
+            ok = mbarWait(oFull, 0, abortFlag, kWaitAccFull);
+        if (ok)
+        {
+            tcFenceAfter();
+            uint32_t x[32];
+            tmemLoad32(tRow + half * 32, x);
+            tmemLoadWait();
+            int const q = q0 + r;
+            if (q < rows)
+            {
+                T* dst = outRow(q) + half * 32;
+                if (kInt8)
+                {
+                    float const s2 = args.scaleBmm2;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g)
+                    {
+                        uint4 o;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            w[i] = packChar4(static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 1])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 2])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 3])) * s2);
+                        reinterpret_cast<uint4*>(dst)[g] = o;
+                    }
+                }
+                else
+                {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g)
+                    {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            f[i] = __uint_as_float(x[g * 8 + i]) * inv;
+                        reinterpret_cast<uint4*>(dst)[g] = packHalf8(f);
+                    }
+                }
+            }
+        }
+        tcFenceBefore();
+    }
+
+    __syncthreads();
+    uint32_t const aborted = *abortFlag;
+    if (aborted != 0)
+    {
+        uint64_t const t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull)
+            __nanosleep(1000);
+        if (threadIdx.x == 0 && args.statusWord)
+            atomicMax(args.statusWord, aborted);
+        __syncthreads();
+    }
+    if (warp == 1)
+    {
+        __syncwarp();
+        tcFenceAfter();
+        tmemFree(tmemBase, tmemCols);
+    }
+}
+
+template <typename T>
+int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
+{
+    using L = MhaSmem<T>;
+    bool const fixedLayout = p.cu_seqlens == nullptr;
+    int64_t const rowElems = static_cast<int64_t>(3) * p.num_heads * kHeadSize;
+    CUtensorMap map;
+    {
+        // dim0: the 3*N*d values of one token; dim1: batch (fixed layout only); dim2: sequence position / packed row
+        uint64_t const dims[3] = {static_cast<uint64_t>(rowElems), fixedLayout ? static_cast<uint64_t>(p.B) : 1ull,
+            fixedLayout ? static_cast<uint64_t>(p.S) : static_cast<uint64_t>(p.total)};
+        uint64_t const strides[2] = {static_cast<uint64_t>(rowElems) * sizeof(T),
+            (fixedLayout ? static_cast<uint64_t>(p.B) : 1ull) * static_cast<uint64_t>(rowElems) * sizeof(T)};
+        uint32_t const box[3] = {kHeadSize, 1, kKeyBlock};
+        int32_t const st = makeTensorMap(&map, sizeof(T) == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+            3, p.qkv, dims, strides, box, sizeof(T) == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
+    int const smem = L::dynamicBytes(nbMax);
+    auto kernel = mhaTcgen05Kernel<T>;
+    cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    MhaArgs args{p.B, p.S, p.num_heads, p.total, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
+        p.scale_softmax, p.scale_bmm2, p.status_word};
+    dim3 const grid((p.S + kQTile - 1) / kQTile, p.num_heads, p.B);
+    kernel<<<grid, kMhaThreads, smem, stream>>>(map, args);
+    return checkLaunch("mhaTcgen05Kernel");
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* stream)
+{
+    B200_REQUIRE(params != nullptr, "mha: null params");
+    bert_b200_mha_params const& p = *params;
+    B200_REQUIRE(p.B >= 0 && p.S > 0 && p.num_heads > 0 && p.head_size > 0, "mha: bad sizes B=%d S=%d N=%d d=%d", p.B, p.S,
+        p.num_heads, p.head_size);
+    B200_REQUIRE(p.qkv && p.out, "mha: null pointer");
+    B200_REQUIRE(p.cu_seqlens == nullptr || p.total >= 0, "mha: packed layout needs total >= 0");
+    if (p.B == 0 || (p.cu_seqlens && p.total == 0))
+        return BERT_B200_OK;
+    B200_REQUIRE(p.B <= 65535 && p.num_heads <= 65535, "mha: B and num_heads are limited to 65535");
+    auto s = static_cast<cudaStream_t>(stream);
+    if (p.type_id == BERT_B200_FP32)
+        return mhaF32(p, s);
+    B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "mha: type_id %d", p.type_id);
+    if (p.head_size != kHeadSize)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: the tensor-core path needs head_size 64 (got %d)", p.head_size);
+    if (p.S > kMaxBlocks * kKeyBlock)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: S=%d exceeds %d", p.S, kMaxBlocks * kKeyBlock);
+    if (p.interleaved)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: the interleaved (CHW32) layout is not implemented yet");
+    B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
+    if (p.type_id == BERT_B200_FP16)
+        return launchMha<__half>(p, s);
+    return launchMha<int8_t>(p, s);
+}

@@ -1,0 +1,654 @@
+// Residual + bias + LayerNorm for sm_100a: FP32/FP16 rows, INT8 linear rows and INT8 CHW32-interleaved
+// tokens. All kernels are single pass (every input byte is read once, every output byte written
+// once), use 128-bit global accesses, keep the row in registers and accumulate statistics in FP32.
+//
+// Replaces the reference kernels skipln_vec / skipLayerNormKernel[Small] / skiplnDQQ
+// (plugin/skipLayerNormPlugin/skipLayerNormKernel.cu:43-217) and skiplnDQQ_vec3/4,
+// skipln_vec32_hface/mtron (plugin/skipLayerNormPlugin/skipLayerNormInt8InterleavedKernel{HFace,MTron}.cu).
+#include "common.cuh"
+
+#include <limits>
+
+namespace b200
+{
+namespace
+{
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * 32;
+
+// Sums `v` over the WPR warps that share one row. `slot` is this row's scratch line in shared memory.
+template <int WPR>
+__device__ __forceinline__ float rowSum(float v, float* slot, int wInRow, int lane)
+{
+    v = warpSum(v);
+    if (WPR == 1)
+        return v;
+    if (lane == 0)
+        slot[wInRow] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < WPR; ++w)
+        t += slot[w];
+    __syncthreads();
+    return t;
+}
+
+template <typename T>
+struct Vec;
+template <>
+struct Vec<__half>
+{
+    static constexpr int kElems = 8;
+    static __device__ __forceinline__ void unpack(uint4 const& v, float (&f)[8])
+    {
+        unpackHalf8(v, f);
+    }
+    static __device__ __forceinline__ uint4 pack(float const (&f)[8])
+    {
+        return packHalf8(f);
+    }
+};
+template <>
+struct Vec<float>
+{
+    static constexpr int kElems = 4;
+    static __device__ __forceinline__ void unpack(uint4 const& v, float (&f)[4])
+    {
+        f[0] = __uint_as_float(v.x);
+        f[1] = __uint_as_float(v.y);
+        f[2] = __uint_as_float(v.z);
+        f[3] = __uint_as_float(v.w);
+    }
+    static __device__ __forceinline__ uint4 pack(float const (&f)[4])
+    {
+        return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+    }
+};
+
+// One row is shared by WPR warps; each lane owns CPL 16-byte chunks: chunk (i*WPR + wInRow)*32 + lane.
+// The grid strides over rows, so gamma/beta/bias chunks (always the same columns for a lane) stay
+// in L1 after the first row.
+template <typename T, int CPL, int WPR, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64_t const rows, T const* __restrict__ in,
+    T const* __restrict__ skip, T const* __restrict__ beta, T const* __restrict__ gamma, T const* __restrict__ bias,
+    T* __restrict__ out, float const eps)
+{
+    constexpr int E = Vec<T>::kElems;
+    constexpr int kRowsPerCta = kWarpsPerCta / WPR;
+    __shared__ float red[kRowsPerCta][WPR > 1 ? WPR : 1];
+
+    int const lane = threadIdx.x & 31;
+    int const warp = threadIdx.x >> 5;
+    int const rowInCta = warp / WPR;
+    int const wInRow = warp % WPR;
+    int const chunksPerRow = ld / E;
+    float const rld = 1.f / static_cast<float>(ld);
+
+    int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
+         row += static_cast<int64_t>(gridDim.x) * kRowsPerCta)
+    {
+        bool const rowOk = row < rows;
+        T const* inRow = in + row * ld;
+        T const* skipRow = skip + row * ld;
+
+        uint4 a[CPL], b[CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            bool const ok = rowOk && c < chunksPerRow;
+            a[i] = ok ? ldgStream(inRow + c * E) : make_uint4(0, 0, 0, 0);
+            b[i] = ok ? ldgStream(skipRow + c * E) : make_uint4(0, 0, 0, 0);
+        }
+
+        float x[CPL][E];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            float fb[E];
+            Vec<T>::unpack(a[i], x[i]);
+            Vec<T>::unpack(b[i], fb);
+#pragma unroll
+            for (int j = 0; j < E; ++j)
+                x[i][j] += fb[j];
+            if (HAS_BIAS && c < chunksPerRow)
+            {
+                uint4 const bv = ldgKeep(bias + c * E);
+                Vec<T>::unpack(bv, fb);
+#pragma unroll
+                for (int j = 0; j < E; ++j)
+                    x[i][j] += fb[j];
+            }
+#pragma unroll
+            for (int j = 0; j < E; ++j)
+                s += x[i][j];
+        }
+        float const mu = rowSum<WPR>(s, red[rowInCta], wInRow, lane) * rld;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            if (c < chunksPerRow)
+            {
+#pragma unroll
+                for (int j = 0; j < E; ++j)
+                {
+                    float const d = x[i][j] - mu;
+                    q += d * d;
+                }
+            }
+        }
+        float const var = rowSum<WPR>(q, red[rowInCta], wInRow, lane) * rld;
+        float const rsigma = rsqrtf(var + eps);
+
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            if (rowOk && c < chunksPerRow)
+            {
+                float g[E], bt[E];
+                Vec<T>::unpack(ldgKeep(gamma + c * E), g);
+                Vec<T>::unpack(ldgKeep(beta + c * E), bt);
+#pragma unroll
+                for (int j = 0; j < E; ++j)
+                    x[i][j] = g[j] * (x[i][j] - mu) * rsigma + bt[j];
+                stgStream(out + row * ld + c * E, Vec<T>::pack(x[i]));
+            }
+        }
+    }
+}
+
+// Any ld, scalar accesses, one warp per row; the row is revisited from L1/L2 instead of registers.
+template <typename T, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads) skipLnScalarKernel(int32_t const ld, int64_t const rows,
+    T const* __restrict__ in, T const* __restrict__ skip, T const* __restrict__ beta, T const* __restrict__ gamma,
+    T const* __restrict__ bias, T* __restrict__ out, float const eps)
+{
+    int const lane = threadIdx.x & 31;
+    int const warp = threadIdx.x >> 5;
+    float const rld = 1.f / static_cast<float>(ld);
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpsPerCta + warp; row < rows;
+         row += static_cast<int64_t>(gridDim.x) * kWarpsPerCta)
+    {
+        T const* a = in + row * ld;
+        T const* b = skip + row * ld;
+        float s = 0.f;
+        for (int i = lane; i < ld; i += 32)
+            s += static_cast<float>(a[i]) + static_cast<float>(b[i]) + (HAS_BIAS ? static_cast<float>(bias[i]) : 0.f);
+        float const mu = warpSum(s) * rld;
+        float q = 0.f;
+        for (int i = lane; i < ld; i += 32)
+        {
+            float const d
+                = static_cast<float>(a[i]) + static_cast<float>(b[i]) + (HAS_BIAS ? static_cast<float>(bias[i]) : 0.f) - mu;
+            q += d * d;
+        }
+        float const rsigma = rsqrtf(warpSum(q) * rld + eps);
+        for (int i = lane; i < ld; i += 32)
+        {
+            float const v
+                = static_cast<float>(a[i]) + static_cast<float>(b[i]) + (HAS_BIAS ? static_cast<float>(bias[i]) : 0.f);
+            out[row * ld + i] = static_cast<T>(static_cast<float>(gamma[i]) * (v - mu) * rsigma + static_cast<float>(beta[i]));
+        }
+    }
+}
+
+// INT8 linear rows: 16 values per 128-bit load, FP16 parameters (two 128-bit loads per chunk).
+template <int CPL, int WPR, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, int64_t const rows,
+    int8_t const* __restrict__ in, int8_t const* __restrict__ skip, __half const* __restrict__ beta,
+    __half const* __restrict__ gamma, __half const* __restrict__ bias, int8_t* __restrict__ out, float const dqIn,
+    float const dqSkip, float const qScale, float const eps)
+{
+    constexpr int E = 16;
+    constexpr int kRowsPerCta = kWarpsPerCta / WPR;
+    __shared__ float red[kRowsPerCta][WPR > 1 ? WPR : 1];
+
+    int const lane = threadIdx.x & 31;
+    int const warp = threadIdx.x >> 5;
+    int const rowInCta = warp / WPR;
+    int const wInRow = warp % WPR;
+    int const chunksPerRow = ld / E;
+    float const rld = 1.f / static_cast<float>(ld);
+
+    int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
+         row += static_cast<int64_t>(gridDim.x) * kRowsPerCta)
+    {
+        bool const rowOk = row < rows;
+        uint4 a[CPL], b[CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            bool const ok = rowOk && c < chunksPerRow;
+            a[i] = ok ? ldgStream(in + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+            b[i] = ok ? ldgStream(skip + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+        }
+        float x[CPL][E];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
+            uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+                float fa[4], fb[4];
+                unpackChar4(aw[w], fa);
+                unpackChar4(bw[w], fb);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    x[i][4 * w + j] = dqIn * fa[j] + dqSkip * fb[j];
+            }
+            if (HAS_BIAS && c < chunksPerRow)
+            {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    float fb[8];
+                    unpackHalf8(ldgKeep(bias + c * E + 8 * h), fb);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        x[i][8 * h + j] += fb[j];
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < E; ++j)
+                s += x[i][j];
+        }
+        float const mu = rowSum<WPR>(s, red[rowInCta], wInRow, lane) * rld;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            if (c < chunksPerRow)
+            {
+#pragma unroll
+                for (int j = 0; j < E; ++j)
+                {
+                    float const d = x[i][j] - mu;
+                    q += d * d;
+                }
+            }
+        }
+        float const rsigma = rsqrtf(rowSum<WPR>(q, red[rowInCta], wInRow, lane) * rld + eps);
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            if (rowOk && c < chunksPerRow)
+            {
+                uint4 o;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    float g[8], bt[8], y[8];
+                    unpackHalf8(ldgKeep(gamma + c * E + 8 * h), g);
+                    unpackHalf8(ldgKeep(beta + c * E + 8 * h), bt);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        y[j] = (g[j] * (x[i][8 * h + j] - mu) * rsigma + bt[j]) * qScale;
+                    ow[2 * h] = packChar4(y[0], y[1], y[2], y[3]);
+                    ow[2 * h + 1] = packChar4(y[4], y[5], y[6], y[7]);
+                }
+                stgStream(out + row * ld + c * E, o);
+            }
+        }
+    }
+}
+
+// INT8 CHW32-interleaved tokens: element (token t, channel c) lives at ((c/32)*total + t)*32 + c%32.
+// A CTA owns 8 consecutive tokens, i.e. 256 contiguous bytes in each of the ld/32 channel groups.
+// Thread -> 16-byte unit u = tid%16 (token u/2, half u%2) of channel group (tid/16 + 16*i), so a
+// quarter warp reads 256 contiguous bytes. Per-token statistics are reduced over lane bits 0 and 4
+// by shuffles and over the 8 warps through shared memory.
+constexpr int kIlTokens = 8;
+
+template <int NI, bool PRELN>
+__global__ void __launch_bounds__(kThreads) skipLnInterleavedKernel(int32_t const ld, int32_t const total,
+    int8_t const* __restrict__ in, int8_t const* __restrict__ skip, __half const* __restrict__ beta,
+    __half const* __restrict__ gamma, int8_t* __restrict__ out, int8_t* __restrict__ preln, float const dqIn,
+    float const dqSkip, float const qScale, float const qSkipScale, float const eps)
+{
+    __shared__ float red[2][kWarpsPerCta][kIlTokens];
+    int const tid = threadIdx.x;
+    int const lane = tid & 31;
+    int const warp = tid >> 5;
+    int const unit = tid & 15;
+    int const tokInCta = unit >> 1;
+    int const half = unit & 1;
+    int const groups = ld / 32;
+    float const rld = 1.f / static_cast<float>(ld);
+    int const numTiles = (total + kIlTokens - 1) / kIlTokens;
+
+    for (int tile = blockIdx.x; tile < numTiles; tile += gridDim.x)
+    {
+        int const tok = tile * kIlTokens + tokInCta;
+        bool const tokOk = tok < total;
+        uint4 a[NI], b[NI];
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            int const g = (tid >> 4) + 16 * i;
+            bool const ok = tokOk && g < groups;
+            int64_t const off = (static_cast<int64_t>(g) * total + tok) * 32 + half * 16;
+            a[i] = ok ? ldgStream(in + off) : make_uint4(0, 0, 0, 0);
+            b[i] = ok ? ldgStream(skip + off) : make_uint4(0, 0, 0, 0);
+        }
+        float x[NI][16];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
+            uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+                float fa[4], fb[4];
+                unpackChar4(aw[w], fa);
+                unpackChar4(bw[w], fb);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                {
+                    x[i][4 * w + j] = dqIn * fa[j] + dqSkip * fb[j];
+                    s += x[i][4 * w + j];
+                }
+            }
+        }
+        // lanes with equal token: differ in lane bit 0 (half) and bit 4 (group parity)
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 16);
+        if ((lane & 17) == 0)
+            red[0][warp][tokInCta] = s;
+        __syncthreads();
+        float mu = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerCta; ++w)
+            mu += red[0][w][tokInCta];
+        mu *= rld;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            int const g = (tid >> 4) + 16 * i;
+            if (g < groups)
+            {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                {
+                    float const d = x[i][j] - mu;
+                    q += d * d;
+                }
+            }
+        }
+        q += __shfl_xor_sync(0xffffffffu, q, 1);
+        q += __shfl_xor_sync(0xffffffffu, q, 16);
+        if ((lane & 17) == 0)
+            red[1][warp][tokInCta] = q;
+        __syncthreads();
+        float var = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerCta; ++w)
+            var += red[1][w][tokInCta];
+        float const rsigma = rsqrtf(var * rld + eps);
+
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            int const g = (tid >> 4) + 16 * i;
+            if (tokOk && g < groups)
+            {
+                int64_t const off = (static_cast<int64_t>(g) * total + tok) * 32 + half * 16;
+                int const ch = g * 32 + half * 16;
+                uint4 o, p;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&p);
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    float gm[8], bt[8], y[8];
+                    unpackHalf8(ldgKeep(gamma + ch + 8 * h), gm);
+                    unpackHalf8(ldgKeep(beta + ch + 8 * h), bt);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        y[j] = (gm[j] * (x[i][8 * h + j] - mu) * rsigma + bt[j]) * qScale;
+                    ow[2 * h] = packChar4(y[0], y[1], y[2], y[3]);
+                    ow[2 * h + 1] = packChar4(y[4], y[5], y[6], y[7]);
+                    if (PRELN)
+                    {
+                        pw[2 * h] = packChar4(x[i][8 * h] * qSkipScale, x[i][8 * h + 1] * qSkipScale,
+                            x[i][8 * h + 2] * qSkipScale, x[i][8 * h + 3] * qSkipScale);
+                        pw[2 * h + 1] = packChar4(x[i][8 * h + 4] * qSkipScale, x[i][8 * h + 5] * qSkipScale,
+                            x[i][8 * h + 6] * qSkipScale, x[i][8 * h + 7] * qSkipScale);
+                    }
+                }
+                stgStream(out + off, o);
+                if (PRELN)
+                    stgStream(preln + off, p);
+            }
+        }
+        // red[] is rewritten in the next iteration only after both barriers of that iteration's
+        // first phase, and all reads of this iteration precede the next write of the same array
+        // by at least one barrier (red[0] read before barrier 2; red[1] read before next barrier 1).
+    }
+}
+
+inline int gridFor(int64_t ctasNeeded, int ctasPerSm)
+{
+    int64_t const cap = static_cast<int64_t>(smCount()) * ctasPerSm;
+    return static_cast<int>(ctasNeeded < cap ? (ctasNeeded > 0 ? ctasNeeded : 1) : cap);
+}
+
+template <typename T, int CPL, int WPR>
+int32_t launchSkipLn(cudaStream_t stream, int32_t ld, int64_t rows, T const* in, T const* skip, T const* beta,
+    T const* gamma, T const* bias, T* out, float eps)
+{
+    int const rowsPerCta = kWarpsPerCta / WPR;
+    int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 8);
+    if (bias)
+        skipLnKernel<T, CPL, WPR, true><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+    else
+        skipLnKernel<T, CPL, WPR, false><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+    return checkLaunch("skipLnKernel");
+}
+
+template <typename T>
+int32_t dispatchSkipLn(cudaStream_t stream, int32_t ld, int64_t rows, T const* in, T const* skip, T const* beta,
+    T const* gamma, T const* bias, T* out)
+{
+    // FP16: the reference adds numeric_limits<half>::epsilon(), which is value-initialised (0) because no
+    // specialisation for __half exists; FP32 adds 1.19e-7 (plugin/skipLayerNormPlugin/skipLayerNormKernel.cu:149).
+    float const eps = sizeof(T) == 4 ? std::numeric_limits<float>::epsilon() : 0.f;
+    constexpr int E = 16 / sizeof(T);
+    bool const vec = (ld % E == 0) && ld / E <= 32 * 4 * 8 && aligned16(in) && aligned16(skip) && aligned16(out)
+        && aligned16(beta) && aligned16(gamma) && (!bias || aligned16(bias));
+    if (!vec)
+    {
+        int const grid = gridFor((rows + kWarpsPerCta - 1) / kWarpsPerCta, 8);
+        if (bias)
+            skipLnScalarKernel<T, true><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+        else
+            skipLnScalarKernel<T, false><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+        return checkLaunch("skipLnScalarKernel");
+    }
+    int const chunks = ld / E;
+    // Smallest number of warps per row that leaves at most 4 chunks per lane.
+    int wpr = 1;
+    while (chunks > 32 * 4 * wpr)
+        wpr *= 2;
+    int const cpl = (chunks + 32 * wpr - 1) / (32 * wpr);
+#define B200_SKIPLN_CASE(C, W)                                                                                         \
+    if (cpl == C && wpr == W)                                                                                          \
+        return launchSkipLn<T, C, W>(stream, ld, rows, in, skip, beta, gamma, bias, out, eps);
+    B200_SKIPLN_CASE(1, 1)
+    B200_SKIPLN_CASE(2, 1)
+    B200_SKIPLN_CASE(3, 1)
+    B200_SKIPLN_CASE(4, 1)
+    B200_SKIPLN_CASE(3, 2)
+    B200_SKIPLN_CASE(4, 2)
+    B200_SKIPLN_CASE(3, 4)
+    B200_SKIPLN_CASE(4, 4)
+    B200_SKIPLN_CASE(3, 8)
+    B200_SKIPLN_CASE(4, 8)
+#undef B200_SKIPLN_CASE
+    B200_FAIL(BERT_B200_NOT_SUPPORTED, "skip_layer_norm: no kernel for ld=%d", ld);
+}
+
+template <int CPL, int WPR>
+int32_t launchDqq(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* in, int8_t const* skip,
+    __half const* beta, __half const* gamma, __half const* bias, int8_t* out, float dqIn, float dqSkip, float qScale)
+{
+    int const rowsPerCta = kWarpsPerCta / WPR;
+    int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 8);
+    if (bias)
+        skipLnDqqKernel<CPL, WPR, true>
+            <<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+    else
+        skipLnDqqKernel<CPL, WPR, false>
+            <<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+    return checkLaunch("skipLnDqqKernel");
+}
+
+template <bool PRELN>
+int32_t launchInterleaved(cudaStream_t stream, int32_t ld, int32_t total, int8_t const* in, int8_t const* skip,
+    __half const* beta, __half const* gamma, int8_t* out, int8_t* preln, float dqIn, float dqSkip, float qScale,
+    float qSkipScale)
+{
+    int const groups = ld / 32;
+    int const ni = (groups + 15) / 16;
+    int const tiles = (total + kIlTokens - 1) / kIlTokens;
+    int const grid = gridFor(tiles, 8);
+    // The large interleaved reference kernels add FP32 epsilon
+    // (plugin/skipLayerNormPlugin/skipLayerNormInt8InterleavedKernelHFace.cu:178).
+    float const eps = std::numeric_limits<float>::epsilon();
+#define B200_IL_CASE(N)                                                                                                \
+    if (ni == N)                                                                                                       \
+    {                                                                                                                  \
+        skipLnInterleavedKernel<N, PRELN><<<grid, kThreads, 0, stream>>>(                                              \
+            ld, total, in, skip, beta, gamma, out, preln, dqIn, dqSkip, qScale, qSkipScale, eps);                      \
+        return checkLaunch("skipLnInterleavedKernel");                                                                 \
+    }
+    B200_IL_CASE(1)
+    B200_IL_CASE(2)
+    B200_IL_CASE(3)
+    B200_IL_CASE(4)
+    B200_IL_CASE(6)
+    B200_IL_CASE(8)
+#undef B200_IL_CASE
+    B200_FAIL(BERT_B200_NOT_SUPPORTED, "interleaved skip_layer_norm: unsupported ld=%d", ld);
+}
+
+} // namespace
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int32_t bert_b200_skip_layer_norm(void* stream, int32_t type_id, int32_t ld, int64_t n, void const* input,
+    void const* skip, void const* beta, void const* gamma, void* output, void const* bias)
+{
+    B200_REQUIRE(ld > 0 && n >= 0 && n % ld == 0, "skip_layer_norm: n=%lld is not a multiple of ld=%d",
+        static_cast<long long>(n), ld);
+    B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm: null pointer");
+    if (n == 0)
+        return BERT_B200_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (type_id == BERT_B200_FP16)
+        return dispatchSkipLn<__half>(s, ld, n / ld, static_cast<__half const*>(input), static_cast<__half const*>(skip),
+            static_cast<__half const*>(beta), static_cast<__half const*>(gamma), static_cast<__half const*>(bias),
+            static_cast<__half*>(output));
+    if (type_id == BERT_B200_FP32)
+        return dispatchSkipLn<float>(s, ld, n / ld, static_cast<float const*>(input), static_cast<float const*>(skip),
+            static_cast<float const*>(beta), static_cast<float const*>(gamma), static_cast<float const*>(bias),
+            static_cast<float*>(output));
+    B200_FAIL(BERT_B200_NOT_SUPPORTED, "skip_layer_norm: type_id %d (INT8 uses bert_b200_skip_layer_norm_dqq)", type_id);
+}
+
+extern "C" int32_t bert_b200_skip_layer_norm_dqq(void* stream, int32_t ld, int64_t n, int8_t const* input,
+    int8_t const* skip, void const* beta, void const* gamma, int8_t* output, void const* bias, float dq_scale_in,
+    float dq_scale_skip, float q_scale)
+{
+    B200_REQUIRE(ld > 0 && n >= 0 && n % ld == 0, "skip_layer_norm_dqq: n=%lld is not a multiple of ld=%d",
+        static_cast<long long>(n), ld);
+    B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm_dqq: null pointer");
+    B200_REQUIRE(ld % 16 == 0 && ld <= 16 * 32 * 4 * 8, "skip_layer_norm_dqq: ld=%d must be a multiple of 16, <= 16384", ld);
+    B200_REQUIRE(aligned16(input) && aligned16(skip) && aligned16(output) && aligned16(beta) && aligned16(gamma)
+            && (!bias || aligned16(bias)),
+        "skip_layer_norm_dqq: pointers must be 16-byte aligned");
+    if (n == 0)
+        return BERT_B200_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    int const chunks = ld / 16;
+    int wpr = 1;
+    while (chunks > 32 * 4 * wpr)
+        wpr *= 2;
+    // Prefer <= 2 chunks per lane: 16 INT8 values expand to 16 FP32 registers per chunk.
+    while (wpr < 8 && chunks > 32 * 2 * wpr)
+        wpr *= 2;
+    int const cpl = (chunks + 32 * wpr - 1) / (32 * wpr);
+    auto const* b = static_cast<__half const*>(beta);
+    auto const* g = static_cast<__half const*>(gamma);
+    auto const* bi = static_cast<__half const*>(bias);
+#define B200_DQQ_CASE(C, W)                                                                                            \
+    if (cpl == C && wpr == W)                                                                                          \
+        return launchDqq<C, W>(s, ld, n / ld, input, skip, b, g, bi, output, dq_scale_in, dq_scale_skip, q_scale);
+    B200_DQQ_CASE(1, 1)
+    B200_DQQ_CASE(2, 1)
+    B200_DQQ_CASE(2, 2)
+    B200_DQQ_CASE(2, 4)
+    B200_DQQ_CASE(2, 8)
+    B200_DQQ_CASE(3, 8)
+    B200_DQQ_CASE(4, 8)
+#undef B200_DQQ_CASE
+    B200_FAIL(BERT_B200_NOT_SUPPORTED, "skip_layer_norm_dqq: no kernel for ld=%d", ld);
+}
+
+static int32_t checkInterleaved(char const* name, int32_t ld, int32_t total, void const* a, void const* b,
+    void const* c, void const* d, void const* e)
+{
+    B200_REQUIRE(ld > 0 && ld % 32 == 0 && ld <= 4096, "%s: ld=%d must be a multiple of 32, <= 4096", name, ld);
+    B200_REQUIRE(total >= 0, "%s: total=%d", name, total);
+    B200_REQUIRE(a && b && c && d && e, "%s: null pointer", name);
+    B200_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d) && aligned16(e),
+        "%s: pointers must be 16-byte aligned", name);
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_skip_layer_norm_interleaved_hface(void* stream, int32_t ld, int32_t total,
+    int8_t const* input, int8_t const* skip, void const* beta, void const* gamma, int8_t* output, float dq_scale_in,
+    float dq_scale_skip, float q_scale)
+{
+    int32_t const st = checkInterleaved("skip_layer_norm_interleaved_hface", ld, total, input, skip, beta, gamma, output);
+    if (st != BERT_B200_OK || total == 0)
+        return st;
+    return launchInterleaved<false>(static_cast<cudaStream_t>(stream), ld, total, input, skip,
+        static_cast<__half const*>(beta), static_cast<__half const*>(gamma), output, nullptr, dq_scale_in, dq_scale_skip,
+        q_scale, 0.f);
+}
+
+extern "C" int32_t bert_b200_skip_layer_norm_interleaved_mtron(void* stream, int32_t ld, int32_t total,
+    int8_t const* input, int8_t const* skip, void const* beta, void const* gamma, int8_t* output, int8_t* preln,
+    float dq_scale_in, float dq_scale_skip, float q_scale, float q_skip_scale)
+{
+    int32_t const st = checkInterleaved("skip_layer_norm_interleaved_mtron", ld, total, input, skip, beta, gamma, output);
+    if (st != BERT_B200_OK)
+        return st;
+    B200_REQUIRE(preln && aligned16(preln), "skip_layer_norm_interleaved_mtron: preln must be a 16-byte aligned pointer");
+    if (total == 0)
+        return st;
+    return launchInterleaved<true>(static_cast<cudaStream_t>(stream), ld, total, input, skip,
+        static_cast<__half const*>(beta), static_cast<__half const*>(gamma), output, preln, dq_scale_in, dq_scale_skip,
+        q_scale, q_skip_scale);
+}

@@ -1,0 +1,158 @@
+"""torch-tensor front end of the C ABI (include/bert_b200.h).
+
+torch is used only to own device memory and streams; every function forwards raw pointers to
+libbert_b200.so. Names follow the reference free functions they replace
+(embSkipLayerNorm, computeSkipLayerNorm, computeMaskIdx, convertMask, MHARunner::run, FC enqueue).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import check, lib
+
+FP32, FP16, INT8 = 0, 1, 2
+ACT_NONE, ACT_GELU_ERF = 0, 1
+
+_TYPE_ID = {torch.float32: FP32, torch.float16: FP16, torch.int8: INT8}
+
+
+def _ptr(t: torch.Tensor | None):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("tensorrt_b200 kernels need CUDA tensors; there is no CPU path")
+    if not t.is_contiguous():
+        raise ValueError("tensor must be contiguous")
+    return C.c_void_p(t.data_ptr())
+
+
+def _stream():
+    if not torch.cuda.is_available():
+        raise ValueError("tensorrt_b200 kernels need a CUDA device; there is no CPU path")
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def skip_layer_norm(x, skip, gamma, beta, bias=None, out=None):
+    """FP32/FP16 residual + bias + LayerNorm over the last dimension."""
+    ld = x.shape[-1]
+    out = torch.empty_like(x) if out is None else out
+    check(lib.bert_b200_skip_layer_norm(_stream(), _TYPE_ID[x.dtype], ld, x.numel(), _ptr(x), _ptr(skip), _ptr(beta),
+                                        _ptr(gamma), _ptr(out), _ptr(bias)), "skip_layer_norm")
+    return out
+
+
+def skip_layer_norm_dqq(x, skip, gamma, beta, bias, dq_in, dq_skip, q_scale, out=None):
+    """INT8 in/out residual + bias + LayerNorm (linear layout); gamma/beta/bias FP16."""
+    ld = x.shape[-1]
+    out = torch.empty_like(x) if out is None else out
+    check(lib.bert_b200_skip_layer_norm_dqq(_stream(), ld, x.numel(), _ptr(x), _ptr(skip), _ptr(beta), _ptr(gamma),
+                                            _ptr(out), _ptr(bias), dq_in, dq_skip, q_scale), "skip_layer_norm_dqq")
+    return out
+
+
+def skip_layer_norm_interleaved(x, skip, gamma, beta, dq_in, dq_skip, q_scale, q_skip_scale=None):
+    """INT8 CHW32 [ld/32, total, 32]; returns out, or (out, preln) when q_skip_scale is given (MTron)."""
+    g, total, _ = x.shape
+    ld = g * 32
+    out = torch.empty_like(x)
+    if q_skip_scale is None:
+        check(lib.bert_b200_skip_layer_norm_interleaved_hface(_stream(), ld, total, _ptr(x), _ptr(skip), _ptr(beta),
+                                                              _ptr(gamma), _ptr(out), dq_in, dq_skip, q_scale),
+              "skip_layer_norm_interleaved_hface")
+        return out
+    preln = torch.empty_like(x)
+    check(lib.bert_b200_skip_layer_norm_interleaved_mtron(_stream(), ld, total, _ptr(x), _ptr(skip), _ptr(beta),
+                                                          _ptr(gamma), _ptr(out), _ptr(preln), dq_in, dq_skip, q_scale,
+                                                          q_skip_scale), "skip_layer_norm_interleaved_mtron")
+    return out, preln
+
+
+def emb_layer_norm(input_ids, token_ids, word_emb, pos_emb, tok_emb, gamma, beta, q_scale=None):
+    """Fixed layout: ids [S, B] int32 -> [S, B, E]; optional fused INT8 copy when q_scale is given."""
+    S, B = input_ids.shape
+    ld = word_emb.shape[1]
+    out = torch.empty((S, B, ld), dtype=word_emb.dtype, device=word_emb.device)
+    out_i8 = torch.empty((S, B, ld), dtype=torch.int8, device=word_emb.device) if q_scale is not None else None
+    check(lib.bert_b200_emb_layer_norm(_stream(), _TYPE_ID[word_emb.dtype], ld, B, S, _ptr(input_ids), _ptr(token_ids),
+                                       _ptr(beta), _ptr(gamma), _ptr(word_emb), _ptr(pos_emb), _ptr(tok_emb),
+                                       word_emb.shape[0], tok_emb.shape[0], _ptr(out), _ptr(out_i8),
+                                       q_scale or 0.0), "emb_layer_norm")
+    return out if q_scale is None else (out, out_i8)
+
+
+def emb_layer_norm_var_seqlen(input_ids, token_ids, cu_seqlens, max_seqlen, word_emb, pos_emb, tok_emb, gamma, beta,
+                              with_skip=False, q_scale=None):
+    """Packed layout: ids [total] -> [total, E] (+ pre-LN sum when with_skip, + INT8 copy when q_scale)."""
+    total = input_ids.shape[0]
+    B = cu_seqlens.shape[0] - 1
+    ld = word_emb.shape[1]
+    out = torch.empty((total, ld), dtype=word_emb.dtype, device=word_emb.device)
+    skip = torch.empty_like(out) if with_skip else None
+    out_i8 = torch.empty((total, ld), dtype=torch.int8, device=word_emb.device) if q_scale is not None else None
+    check(lib.bert_b200_emb_layer_norm_var_seqlen(_stream(), _TYPE_ID[word_emb.dtype], ld, B, max_seqlen, total,
+                                                  _ptr(input_ids), _ptr(token_ids), _ptr(cu_seqlens), _ptr(beta),
+                                                  _ptr(gamma), _ptr(word_emb), _ptr(pos_emb), _ptr(tok_emb),
+                                                  word_emb.shape[0], tok_emb.shape[0], _ptr(out), _ptr(skip),
+                                                  _ptr(out_i8), q_scale or 0.0), "emb_layer_norm_var_seqlen")
+    res = [out]
+    if with_skip:
+        res.append(skip)
+    if q_scale is not None:
+        res.append(out_i8)
+    return res[0] if len(res) == 1 else tuple(res)
+
+
+def compute_mask_idx(mask_sb):
+    S, B = mask_sb.shape
+    out = torch.empty((B,), dtype=torch.int32, device=mask_sb.device)
+    check(lib.bert_b200_compute_mask_idx(_stream(), S, B, _ptr(mask_sb), _ptr(out)), "compute_mask_idx")
+    return out
+
+
+def convert_mask(mask_sb, warps_m, warps_n, warps_k=1):
+    S, B = mask_sb.shape
+    xm = (S + 16 * warps_m - 1) // (16 * warps_m)
+    out = torch.empty((B, xm, warps_m * warps_n * warps_k * 32), dtype=torch.int32, device=mask_sb.device)
+    check(lib.bert_b200_convert_mask(S, B, warps_m, warps_n, warps_k, _ptr(mask_sb), _ptr(out), _stream()),
+          "convert_mask")
+    return out
+
+
+def lengths_to_cu_seqlens(lengths):
+    B = lengths.shape[0]
+    out = torch.empty((B + 1,), dtype=torch.int32, device=lengths.device)
+    check(lib.bert_b200_lengths_to_cu_seqlens(_stream(), B, _ptr(lengths), _ptr(out)), "lengths_to_cu_seqlens")
+    return out
+
+
+def fc(a, wt, bias=None, activation=ACT_NONE, alpha=1.0, out_dtype=None, out_scale=1.0, status=None, out=None):
+    """C[m, n] = epilogue(A[m, k] . Wt[n, k]); Wt is the [n, k] (transposed) weight."""
+    m, k = a.shape
+    n = wt.shape[0]
+    out_dtype = a.dtype if out_dtype is None else out_dtype
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device) if out is None else out
+    p = _lib.FcParams(_TYPE_ID[a.dtype], _TYPE_ID[out_dtype], m, n, k, _ptr(a), a.stride(0), _ptr(wt), _ptr(out),
+                      out.stride(0), _ptr(bias), activation, alpha, out_scale, _ptr(status))
+    check(lib.bert_b200_fc(C.byref(p), _stream()), "fc")
+    return out
+
+
+def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scale_bmm1=None, scale_softmax=1.0,
+        scale_bmm2=1.0, status=None):
+    """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None) or packed [total, 3*N*d]."""
+    E = num_heads * head_size
+    if cu_seqlens is None:
+        out = torch.empty((S, B, E), dtype=qkv.dtype, device=qkv.device)
+        total = 0
+    else:
+        total = qkv.shape[0]
+        out = torch.empty((total, E), dtype=qkv.dtype, device=qkv.device)
+    if scale_bmm1 is None:
+        scale_bmm1 = head_size ** -0.5
+    p = _lib.MhaParams(_TYPE_ID[qkv.dtype], B, S, num_heads, head_size, total, _ptr(qkv), _ptr(out), _ptr(cu_seqlens),
+                       _ptr(mask_idx), 0, scale_bmm1, scale_softmax, scale_bmm2, _ptr(status))
+    check(lib.bert_b200_mha(C.byref(p), _stream()), "mha")
+    return out

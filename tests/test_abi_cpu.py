@@ -1,0 +1,68 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/bert_b200.h declares; argument
+validation (host code) returns error statuses instead of touching the device."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _declared():
+    text = (ROOT / "include" / "bert_b200.h").read_text()
+    return sorted(set(re.findall(r"BERT_B200_API\s+[\w\s\*]+?\b(bert_b200_\w+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    from tensorrt_b200 import _lib
+
+    names = _declared()
+    assert len(names) >= 20
+    for n in names:
+        assert hasattr(_lib.lib, n), f"{n} declared in bert_b200.h but not exported"
+    assert sorted(_lib.SIGNATURES) == names, "ctypes signature table and header disagree"
+
+
+def test_version_and_error_text():
+    from tensorrt_b200 import _lib
+
+    assert _lib.lib.bert_b200_version() >= 100
+    st = _lib.lib.bert_b200_skip_layer_norm(None, 1, 768, 100, None, None, None, None, None, None)
+    assert st == 2  # BERT_B200_BAD_PARAM: n is not a multiple of ld
+    assert b"multiple" in _lib.lib.bert_b200_last_error()
+    st = _lib.lib.bert_b200_skip_layer_norm(None, 1, 768, 768, None, None, None, None, None, None)
+    assert st == 2 and b"null" in _lib.lib.bert_b200_last_error()
+
+
+def test_fc_and_mha_validation():
+    from tensorrt_b200 import _lib
+
+    p = _lib.FcParams()
+    p.type_id, p.out_type_id, p.m, p.n, p.k = 1, 1, 8, 16, 0
+    assert _lib.lib.bert_b200_fc(C.byref(p), None) == 2
+    assert _lib.lib.bert_b200_fc(None, None) == 2
+    m = _lib.MhaParams()
+    m.type_id, m.B, m.S, m.num_heads, m.head_size = 1, 1, 1024, 2, 64
+    m.qkv = m.out = C.c_void_p(0x1000)
+    assert _lib.lib.bert_b200_mha(C.byref(m), None) == 3  # BERT_B200_NOT_SUPPORTED: S > 512
+    m.S, m.head_size = 128, 80
+    assert _lib.lib.bert_b200_mha(C.byref(m), None) == 3
+
+
+def test_encoder_config_validation():
+    from tensorrt_b200 import _lib
+
+    cfg = _lib.EncoderConfig()
+    assert _lib.lib.bert_b200_encoder_workspace_size(C.byref(cfg), 128, 1) == -1
+    h = C.c_void_p()
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 2
+
+
+def test_no_cpu_fallback():
+    import torch
+
+    import tensorrt_b200 as T
+
+    with pytest.raises(ValueError):
+        T.skip_layer_norm(torch.zeros(2, 8), torch.zeros(2, 8), torch.ones(8), torch.zeros(8))

@@ -1,0 +1,141 @@
+"""Parity of fused attention (tcgen05 FP16 / INT8, SIMT FP32) with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bert_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _status(cuda):
+    return torch.zeros(4, dtype=torch.int32, device=cuda)
+
+
+@pytest.mark.parametrize("S,B,N", [(128, 8, 12), (64, 2, 12), (96, 3, 4), (384, 2, 16), (512, 1, 2), (256, 2, 3),
+                                   (200, 2, 2), (16, 1, 1)])
+def test_mha_fixed_fp16(cuda, S, B, N):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S + B + N)
+    d = 64
+    qkv = rng.standard_normal((S, B, 3 * N * d)).astype(np.float16)
+    lengths = rng.integers(1, S + 1, size=B).astype(np.int32)
+    lengths[0] = S
+    if B > 1:
+        lengths[1] = 0 if S == 128 else lengths[1]  # a sequence without valid keys gives zero rows
+    ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+    st = _status(cuda)
+    out = T.mha(_t(qkv, cuda), B, S, N, mask_idx=_t(lengths, cuda), status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+
+
+@pytest.mark.parametrize("lengths,N", [([384, 32, 129, 1, 0, 257, 128], 16), ([17], 12), ([512, 500], 2)])
+def test_mha_packed_fp16(cuda, lengths, N):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(len(lengths) + N)
+    d = 64
+    lengths = np.array(lengths, dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, B, S = int(cu[-1]), len(lengths), int(max(lengths.max(), 1))
+    qkv = rng.standard_normal((total, 3 * N * d)).astype(np.float16)
+    ref = O.mha(qkv, B, S, N, d, cu=cu)
+    st = _status(cuda)
+    out = T.mha(_t(qkv, cuda), B, S, N, cu_seqlens=_t(cu, cuda), status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+
+
+def _int8_case(rng, rows, N, d):
+    x = rng.standard_normal((rows, 3 * N * d))
+    s_qkv = O.amax_scale(x)
+    return O.quantize(x, 1.0 / s_qkv), s_qkv
+
+
+@pytest.mark.parametrize("lengths,N", [([384, 32, 129, 1, 0, 257, 128], 16), ([64], 2), ([512, 300], 2)])
+def test_mha_packed_int8(cuda, lengths, N):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(len(lengths) + N + 7)
+    d = 64
+    lengths = np.array(lengths, dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, B, S = int(cu[-1]), len(lengths), int(max(lengths.max(), 1))
+    q8, s_qkv = _int8_case(rng, total, N, d)
+    dq_probs = 1.0 / 127.0
+    s_ctx = s_qkv * 0.5
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    s2 = dq_probs * s_qkv / s_ctx
+    ref = O.mha_int8(q8, B, S, N, d, s1, 1.0 / dq_probs, s2, cu=cu)
+    st = _status(cuda)
+    out = T.mha(_t(q8, cuda), B, S, N, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs,
+                scale_bmm2=s2, status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.int8_within_lsb(out.cpu().numpy(), ref)
+    assert ok, (worst, bad)
+
+
+@pytest.mark.parametrize("S,B,N", [(128, 4, 12), (384, 2, 16)])
+def test_mha_fixed_int8(cuda, S, B, N):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S)
+    d = 64
+    q8, s_qkv = _int8_case(rng, S * B, N, d)
+    q8 = q8.reshape(S, B, -1)
+    lengths = rng.integers(1, S + 1, size=B).astype(np.int32)
+    dq_probs = 1.0 / 127.0
+    s_ctx = s_qkv * 0.5
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    s2 = dq_probs * s_qkv / s_ctx
+    ref = O.mha_int8(q8, B, S, N, d, s1, 1.0 / dq_probs, s2, lengths=lengths)
+    st = _status(cuda)
+    out = T.mha(_t(q8, cuda), B, S, N, mask_idx=_t(lengths, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs,
+                scale_bmm2=s2, status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.int8_within_lsb(out.cpu().numpy(), ref)
+    assert ok, (worst, bad)
+
+
+@pytest.mark.parametrize("d", [32, 64])
+def test_mha_fp32(cuda, d):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(d)
+    S, B, N = 40, 3, 3   # the reference FP32 configuration uses tiny hidden sizes with has_mask
+    qkv = rng.standard_normal((S, B, 3 * N * d)).astype(np.float32)
+    lengths = np.array([40, 13, 0], dtype=np.int32)
+    ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+    out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, mask_idx=_t(lengths, cuda))
+    assert O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-5, 1e-5)[0]
+
+
+def test_mha_full_size_properties(cuda):
+    """BERT-large S=384, B=64, N=16: with V = const per head the context equals that constant (rows of the
+    softmax sum to one), and attention is invariant to a permutation of the keys."""
+    import tensorrt_b200 as T
+
+    S, B, N, d = 384, 64, 16, 64
+    gen = torch.Generator(device=cuda).manual_seed(0)
+    qkv = torch.randn((S * B, N, 3, d), device=cuda, generator=gen).half()
+    const = torch.randn((N, d), device=cuda, generator=gen).half()
+    qkv[:, :, 2, :] = const[None]
+    cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=cuda)
+    out = T.mha(qkv.reshape(S * B, -1), B, S, N, cu_seqlens=cu).reshape(S * B, N, d)
+    assert (out.float() - const.float()[None]).abs().max().item() < 5e-3
+    qkv2 = torch.randn((S, N, 3, d), device=cuda, generator=gen).half()
+    perm = torch.randperm(S, device=cuda, generator=gen)
+    shuffled = qkv2.clone()
+    shuffled[:, :, 1:, :] = qkv2[perm][:, :, 1:, :]
+    cu1 = torch.tensor([0, S], dtype=torch.int32, device=cuda)
+    o1 = T.mha(qkv2.reshape(S, -1), 1, S, N, cu_seqlens=cu1).float()
+    o2 = T.mha(shuffled.reshape(S, -1), 1, S, N, cu_seqlens=cu1).float()
+    assert (o1 - o2).abs().max().item() < 5e-3
