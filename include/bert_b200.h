@@ -310,6 +310,36 @@ BERT_B200_API int32_t bert_b200_encoder_destroy(bert_b200_encoder* enc);
 BERT_B200_API int32_t bert_b200_encoder_last_launch_count(bert_b200_encoder const* enc);
 
 /*
+ * Per-kernel timing: when enabled, every launch of the forward is bracketed by CUDA events on the
+ * caller's stream. bert_b200_encoder_read_timing synchronises those events and ADDS, per kernel kind,
+ * the elapsed milliseconds and launch counts of the last forward to ms[kind] / launches[kind]
+ * (arrays of BERT_B200_KIND_COUNT entries owned by the caller).
+ */
+enum
+{
+    BERT_B200_KIND_EMB = 0,
+    BERT_B200_KIND_FC = 1,
+    BERT_B200_KIND_MHA = 2,
+    BERT_B200_KIND_SKIPLN = 3,
+    BERT_B200_KIND_OTHER = 4,
+    BERT_B200_KIND_COUNT = 5
+};
+BERT_B200_API int32_t bert_b200_encoder_enable_timing(bert_b200_encoder* enc, int32_t on);
+BERT_B200_API int32_t bert_b200_encoder_read_timing(bert_b200_encoder* enc, float* ms, int32_t* launches);
+
+/*
+ * Max calibration on the FP16 encoder: runs one packed forward and returns, per layer, the largest
+ * magnitude of the eight tensors that carry a scale in INT8 mode, in the order
+ * { layer input, qkv, ctx, attention-out projection, ln1 output, ffn1 output, ffn2 output, layer output }
+ * into amax_host[num_layers][8]. The dequantisation step of a tensor is amax / 127
+ * (ref: tools/pytorch-quantization/pytorch_quantization/calib/max.py and tensor_quant.py:511-556).
+ * `amax_dev` is a caller-provided device buffer of num_layers*8 floats. Synchronises the stream.
+ */
+BERT_B200_API int32_t bert_b200_encoder_calibrate(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids, int32_t const* segment_ids, int32_t const* cu_seqlens,
+    void* workspace, int64_t workspace_bytes, void* output, float* amax_dev, float* amax_host);
+
+/*
  * Packed forward on device buffers: ids/segment ids [total], cu_seqlens [B+1] (device),
  * output FP16 [total][E] (INT8 mode: the last layer's INT8 tensor is dequantised into it).
  * max_seqlen bounds every sequence length (<= 512).

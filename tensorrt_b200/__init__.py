@@ -1,7 +1,7 @@
 """B200 (sm_100a) implementation of the TensorRT-OSS BERT encoder plugin hot path.
 
 The native library is mandatory: importing the package loads tensorrt_b200/libbert_b200.so and raises if
-it is missing (build it with `python -m tensorrt_b200.build`). There is no CPU or PyTorch fallback.
+it is missing (build it with `python tensorrt_b200/csrc/build.py`). There is no CPU or PyTorch fallback.
 """
 from . import _lib  # noqa: F401  (loads the shared library, fails loudly when absent)
 from .ops import (ACT_GELU_ERF, ACT_NONE, FP16, FP32, INT8, compute_mask_idx, convert_mask, emb_layer_norm,

@@ -12,7 +12,7 @@ LIB_PATH = _PKG / "libbert_b200.so"
 
 if not LIB_PATH.exists():
     raise ImportError(
-        f"{LIB_PATH} is missing: build it with `python -m tensorrt_b200.build` (needs nvcc). "
+        f"{LIB_PATH} is missing: build it with `python tensorrt_b200/csrc/build.py` (needs nvcc). "
         "tensorrt_b200 has no CPU or PyTorch fallback.")
 
 lib = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
@@ -70,6 +70,9 @@ SIGNATURES = {
     "bert_b200_encoder_create": (i32, [C.POINTER(EncoderConfig), C.POINTER(vp)]),
     "bert_b200_encoder_destroy": (i32, [vp]),
     "bert_b200_encoder_last_launch_count": (i32, [vp]),
+    "bert_b200_encoder_enable_timing": (i32, [vp, i32]),
+    "bert_b200_encoder_read_timing": (i32, [vp, C.POINTER(f32), C.POINTER(i32)]),
+    "bert_b200_encoder_calibrate": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, C.POINTER(f32)]),
     "bert_b200_encoder_forward": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp]),
     "bert_b200_encoder_forward_host": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp]),
 }

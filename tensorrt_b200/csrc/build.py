@@ -1,7 +1,9 @@
 """Builds the in-tree native libraries with nvcc for sm_100a.
 
-    python -m tensorrt_b200.build            # build what is out of date
-    python -m tensorrt_b200.build --force
+    python tensorrt_b200/csrc/build.py            # build what is out of date
+    python tensorrt_b200/csrc/build.py --force
+
+(run as a file, not through the package: importing tensorrt_b200 needs the library this script builds)
 
 Outputs (git-ignored, kept next to the sources so they travel with the tree):
     tensorrt_b200/libbert_b200.so          kernels + C ABI (include/bert_b200.h)
@@ -16,9 +18,9 @@ import subprocess
 import sys
 from pathlib import Path
 
-PKG = Path(__file__).resolve().parent
+CSRC = Path(__file__).resolve().parent
+PKG = CSRC.parent
 ROOT = PKG.parent
-CSRC = PKG / "csrc"
 OBJ = PKG / "build"
 LIB = PKG / "libbert_b200.so"
 PLUGIN_LIB = PKG / "libbert_b200_plugin.so"

@@ -18,6 +18,19 @@ struct bert_b200_encoder
     bert_b200_encoder_config cfg;
     std::vector<bert_b200_layer_weights> layers;
     int32_t lastLaunches = 0;
+    // optional per-launch timing: events[2*i], events[2*i+1] bracket launch i of kind kinds[i]
+    bool timing = false;
+    std::vector<cudaEvent_t> events;
+    std::vector<int32_t> kinds;
+    int32_t timedLaunches = 0;
+    // optional calibration: device array [num_layers][8] receiving |x| maxima
+    float* amaxDev = nullptr;
+
+    ~bert_b200_encoder()
+    {
+        for (cudaEvent_t e : events)
+            cudaEventDestroy(e);
+    }
 };
 
 namespace b200
@@ -115,6 +128,25 @@ __global__ void dequantKernel(int64_t const n16, int8_t const* __restrict__ in, 
     }
 }
 
+// |x| maximum of `n8` groups of eight FP16 values, folded into *dst with an integer max
+// (non-negative floats order like their bit patterns).
+__global__ void amaxKernel(int64_t const n8, __half const* __restrict__ in, float* __restrict__ dst)
+{
+    float m = 0.f;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n8;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    {
+        float f[8];
+        unpackHalf8(ldgStream(in + i * 8), f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            m = fmaxf(m, fabsf(f[j]));
+    }
+    m = warpMax(m);
+    if ((threadIdx.x & 31) == 0)
+        atomicMax(reinterpret_cast<unsigned int*>(dst), __float_as_uint(m));
+}
+
 int32_t checkConfig(bert_b200_encoder_config const* c)
 {
     B200_REQUIRE(c != nullptr, "encoder: null config");
@@ -186,10 +218,46 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
     int64_t const T = total;
     int32_t launches = 0;
     int32_t st;
-#define B200_STEP(call)                                                                                                \
+    enc->timedLaunches = 0;
+    auto mark = [&](int32_t kind, bool begin) -> int32_t {
+        if (!enc->timing)
+            return BERT_B200_OK;
+        size_t const idx = static_cast<size_t>(enc->timedLaunches) * 2 + (begin ? 0 : 1);
+        while (enc->events.size() <= idx)
+        {
+            cudaEvent_t e;
+            if (cudaEventCreate(&e) != cudaSuccess)
+                B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward: cudaEventCreate failed");
+            enc->events.push_back(e);
+        }
+        if (begin)
+        {
+            if (enc->kinds.size() <= static_cast<size_t>(enc->timedLaunches))
+                enc->kinds.resize(enc->timedLaunches + 1);
+            enc->kinds[enc->timedLaunches] = kind;
+        }
+        if (cudaEventRecord(enc->events[idx], stream) != cudaSuccess)
+            B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward: cudaEventRecord failed");
+        if (!begin)
+            ++enc->timedLaunches;
+        return BERT_B200_OK;
+    };
+    // calibration: fold max|t| of an FP16 tensor of n elements into amaxDev[layer][slot]
+    auto amax = [&](void const* t, int64_t n, int32_t layer, int32_t slot) {
+        if (!enc->amaxDev)
+            return;
+        int64_t const n8 = n / 8;
+        int const grid = static_cast<int>(n8 / 256 + 1 < smCount() * 8 ? n8 / 256 + 1 : smCount() * 8);
+        amaxKernel<<<grid, 256, 0, stream>>>(n8, static_cast<__half const*>(t), enc->amaxDev + layer * 8 + slot);
+    };
+#define B200_STEP(kind, call)                                                                                          \
     do                                                                                                                 \
     {                                                                                                                  \
-        st = (call);                                                                                                   \
+        st = mark(kind, true);                                                                                         \
+        if (st == BERT_B200_OK)                                                                                        \
+            st = (call);                                                                                               \
+        if (st == BERT_B200_OK)                                                                                        \
+            st = mark(kind, false);                                                                                    \
         if (st != BERT_B200_OK)                                                                                        \
             return st;                                                                                                 \
         ++launches;                                                                                                    \
@@ -198,7 +266,7 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
     if (cudaMemsetAsync(w.status, 0, sizeof(uint32_t), stream) != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward: clearing the status word failed");
     // FP16: embedding output is the first layer input. INT8: additionally quantised with the first layer's input scale.
-    B200_STEP(bert_b200_emb_layer_norm_var_seqlen(stream, BERT_B200_FP16, E, B, maxSeqlen, total, ids, seg, cu, c.emb_beta,
+    B200_STEP(BERT_B200_KIND_EMB, bert_b200_emb_layer_norm_var_seqlen(stream, BERT_B200_FP16, E, B, maxSeqlen, total, ids, seg, cu, c.emb_beta,
         c.emb_gamma, c.word_emb, c.pos_emb, c.tok_emb, c.vocab_size, c.type_vocab_size, i8 ? static_cast<void*>(w.xf16) : w.x,
         nullptr, i8 ? reinterpret_cast<int8_t*>(w.x) : nullptr, i8 ? 1.f / enc->layers[0].s_in : 0.f));
 
@@ -224,7 +292,9 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         fc.activation = BERT_B200_ACT_NONE;
         fc.alpha = i8 ? l.s_in * l.s_wqkv : 1.f;
         fc.out_scale = i8 ? 1.f / l.s_qkv : 1.f;
-        B200_STEP(bert_b200_fc(&fc, stream));
+        amax(w.x, T * E, li, 0);
+        B200_STEP(BERT_B200_KIND_FC, bert_b200_fc(&fc, stream));
+        amax(w.qkv, T * 3 * E, li, 1);
 
         bert_b200_mha_params mha{};
         mha.type_id = c.type_id;
@@ -240,7 +310,8 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         mha.scale_softmax = i8 ? 1.f / c.dq_probs : 1.f;
         mha.scale_bmm2 = i8 ? c.dq_probs * l.s_qkv / l.s_ctx : 1.f;
         mha.status_word = w.status;
-        B200_STEP(bert_b200_mha(&mha, stream));
+        B200_STEP(BERT_B200_KIND_MHA, bert_b200_mha(&mha, stream));
+        amax(w.ctx, T * E, li, 2);
 
         // attention output projection (bias is applied by the SkipLayerNorm that follows)
         fc.n = E;
@@ -253,16 +324,18 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         fc.bias = nullptr;
         fc.alpha = i8 ? l.s_ctx * l.s_wout : 1.f;
         fc.out_scale = i8 ? 1.f / l.s_attn_out : 1.f;
-        B200_STEP(bert_b200_fc(&fc, stream));
+        B200_STEP(BERT_B200_KIND_FC, bert_b200_fc(&fc, stream));
+        amax(w.ao, T * E, li, 3);
 
         if (i8)
-            B200_STEP(bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
+            B200_STEP(BERT_B200_KIND_SKIPLN, bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
                 reinterpret_cast<int8_t*>(w.x), l.ln1_beta, l.ln1_gamma, reinterpret_cast<int8_t*>(w.h1), l.b_out,
                 l.s_attn_out, l.s_in, 1.f / l.s_ln1));
         else
-            B200_STEP(bert_b200_skip_layer_norm(
+            B200_STEP(BERT_B200_KIND_SKIPLN, bert_b200_skip_layer_norm(
                 stream, BERT_B200_FP16, E, T * E, w.ao, w.x, l.ln1_beta, l.ln1_gamma, w.h1, l.b_out));
 
+        amax(w.h1, T * E, li, 4);
         // FFN up projection + bias + erf-GELU
         fc.n = F;
         fc.k = E;
@@ -275,7 +348,8 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         fc.activation = BERT_B200_ACT_GELU_ERF;
         fc.alpha = i8 ? l.s_ln1 * l.s_wffn1 : 1.f;
         fc.out_scale = i8 ? 1.f / l.s_ffn1 : 1.f;
-        B200_STEP(bert_b200_fc(&fc, stream));
+        B200_STEP(BERT_B200_KIND_FC, bert_b200_fc(&fc, stream));
+        amax(w.f1, T * F, li, 5);
 
         // FFN down projection
         fc.n = E;
@@ -289,24 +363,30 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         fc.activation = BERT_B200_ACT_NONE;
         fc.alpha = i8 ? l.s_ffn1 * l.s_wffn2 : 1.f;
         fc.out_scale = i8 ? 1.f / l.s_ffn2 : 1.f;
-        B200_STEP(bert_b200_fc(&fc, stream));
+        B200_STEP(BERT_B200_KIND_FC, bert_b200_fc(&fc, stream));
+        amax(w.ao, T * E, li, 6);
 
         bool const last = li + 1 == c.num_layers;
         if (i8)
-            B200_STEP(bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
+            B200_STEP(BERT_B200_KIND_SKIPLN, bert_b200_skip_layer_norm_dqq(stream, E, T * E, reinterpret_cast<int8_t*>(w.ao),
                 reinterpret_cast<int8_t*>(w.h1), l.ln2_beta, l.ln2_gamma, reinterpret_cast<int8_t*>(w.x), l.b_ffn2, l.s_ffn2,
                 l.s_ln1, 1.f / l.s_out));
         else
-            B200_STEP(bert_b200_skip_layer_norm(stream, BERT_B200_FP16, E, T * E, w.ao, w.h1, l.ln2_beta, l.ln2_gamma,
+            B200_STEP(BERT_B200_KIND_SKIPLN, bert_b200_skip_layer_norm(stream, BERT_B200_FP16, E, T * E, w.ao, w.h1, l.ln2_beta, l.ln2_gamma,
                 last ? output : static_cast<void*>(w.x), l.b_ffn2));
+        if (!i8)
+            amax(last ? output : static_cast<void*>(w.x), T * E, li, 7);
     }
     if (i8)
     {
         int64_t const n16 = T * E / 16;
         int const grid = static_cast<int>(n16 / 256 + 1 < smCount() * 8 ? n16 / 256 + 1 : smCount() * 8);
-        dequantKernel<<<grid, 256, 0, stream>>>(
-            n16, reinterpret_cast<int8_t const*>(w.x), static_cast<__half*>(output), enc->layers.back().s_out);
-        B200_STEP(checkLaunch("dequantKernel"));
+        auto dequant = [&]() -> int32_t {
+            dequantKernel<<<grid, 256, 0, stream>>>(
+                n16, reinterpret_cast<int8_t const*>(w.x), static_cast<__half*>(output), enc->layers.back().s_out);
+            return checkLaunch("dequantKernel");
+        };
+        B200_STEP(BERT_B200_KIND_OTHER, dequant());
     }
 #undef B200_STEP
     enc->lastLaunches = launches;
@@ -369,5 +449,59 @@ extern "C" int32_t bert_b200_encoder_forward_host(bert_b200_encoder* enc, void* 
         e = cudaStreamSynchronize(s);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host: D2H copy: %s", cudaGetErrorString(e));
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_enable_timing(bert_b200_encoder* enc, int32_t on)
+{
+    B200_REQUIRE(enc != nullptr, "encoder_enable_timing: null encoder");
+    enc->timing = on != 0;
+    enc->timedLaunches = 0;
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_read_timing(bert_b200_encoder* enc, float* ms, int32_t* launches)
+{
+    B200_REQUIRE(enc && ms && launches, "encoder_read_timing: null pointer");
+    for (int32_t i = 0; i < enc->timedLaunches; ++i)
+    {
+        cudaError_t e = cudaEventSynchronize(enc->events[2 * i + 1]);
+        float t = 0.f;
+        if (e == cudaSuccess)
+            e = cudaEventElapsedTime(&t, enc->events[2 * i], enc->events[2 * i + 1]);
+        if (e != cudaSuccess)
+            B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_read_timing: %s", cudaGetErrorString(e));
+        int32_t const k = enc->kinds[i];
+        ms[k] += t;
+        launches[k] += 1;
+    }
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_calibrate(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids, int32_t const* segment_ids, int32_t const* cu_seqlens, void* workspace,
+    int64_t workspace_bytes, void* output, float* amax_dev, float* amax_host)
+{
+    Workspace w{};
+    int32_t st
+        = checkForward(enc, B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, workspace, workspace_bytes, output, &w);
+    if (st != BERT_B200_OK)
+        return st;
+    B200_REQUIRE(enc->cfg.type_id == BERT_B200_FP16, "encoder_calibrate: needs the FP16 encoder");
+    B200_REQUIRE(amax_dev && amax_host, "encoder_calibrate: null pointer");
+    auto s = static_cast<cudaStream_t>(stream);
+    size_t const bytes = sizeof(float) * 8 * static_cast<size_t>(enc->cfg.num_layers);
+    if (cudaMemsetAsync(amax_dev, 0, bytes, s) != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_calibrate: memset failed");
+    enc->amaxDev = amax_dev;
+    st = forwardImpl(enc, s, B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, w, output);
+    enc->amaxDev = nullptr;
+    if (st != BERT_B200_OK)
+        return st;
+    cudaError_t e = cudaMemcpyAsync(amax_host, amax_dev, bytes, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess)
+        e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_calibrate: %s", cudaGetErrorString(e));
     return BERT_B200_OK;
 }

@@ -3,14 +3,15 @@
 // Replaces the cublasLtMatmul call of the reference FC plugin (plugin/fcPlugin/fcPlugin.cpp:551-610)
 // and the separate bias / GELU / quantise layers that follow it in the reference graph.
 //
-// Design (one persistent CTA per SM, 6 warps, warp specialised):
+// Design (one persistent CTA per SM, 10 warps, warp specialised):
 //   warp 0  : TMA producer - A[128 x 128B] and Wt[BLOCK_N x 128B] tiles, 128-byte swizzle, into a
 //             STAGES-deep shared-memory ring guarded by full/empty mbarriers.
 //   warp 1  : allocates all 512 TMEM columns, then one lane issues tcgen05.mma (UMMA 128 x BLOCK_N x 16
 //             for FP16 / x 32 for INT8) with the accumulator in TMEM; tcgen05.commit releases ring
 //             stages and publishes finished accumulators.
-//   warps 2-5: epilogue - tcgen05.ld the accumulator (double buffered, so tile i+1's main loop
-//             overlaps tile i's epilogue), scale / bias / erf-GELU / quantise, 128-bit stores.
+//   warps 2-9: epilogue (two warps per TMEM lane quadrant, each owning alternate 64-column groups) -
+//             tcgen05.ld the accumulator (double buffered, so tile i+1's main loop overlaps tile i's
+//             epilogue), scale / bias / erf-GELU / quantise, 128-bit stores.
 // Every mbarrier wait is bounded (see sm100.cuh); on expiry the CTA drains, frees TMEM and exits,
 // and the status word tells the host.
 #include "sm100.cuh"
@@ -28,7 +29,8 @@ namespace
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128; // one swizzle span = BLOCK_K * sizeof(In)
 constexpr int kTmemCols = 512;
-constexpr int kFcThreads = 192;
+constexpr int kFcThreads = 320;
+constexpr int kEpilogueThreads = 256;
 
 struct FcArgs
 {
@@ -55,24 +57,25 @@ struct FcSmem
     static constexpr int kDynamic = kTotal + 1024; // slack for 1024-byte alignment of the ring
 };
 
-// erf by Abramowitz-Stegun 7.1.26 (|error| <= 1.5e-7), two MUFU ops (rcp, ex2) per value.
-__device__ __forceinline__ float fastErf(float x)
-{
-    float const ax = fabsf(x);
-    float const t = __frcp_rn(fmaf(0.3275911f, ax, 1.f));
-    float p = fmaf(1.061405429f, t, -1.453152027f);
-    p = fmaf(p, t, 1.421413741f);
-    p = fmaf(p, t, -0.284496736f);
-    p = fmaf(p, t, 0.254829592f);
-    p *= t;
-    float const e = exp2f(-1.4426950408889634f * ax * ax);
-    float const r = fmaf(-p, e, 1.f);
-    return copysignf(r, x);
-}
-
+// erf-GELU with one MUFU op per value: for z = |x|/sqrt(2), erfc(z) = (1 + a1 z + ... + a6 z^6)^-16
+// (Abramowitz-Stegun 7.1.28, |error| <= 3e-7), so gelu(x) = x - h for x >= 0 and h for x < 0 with h = x/2 * erfc(z).
 __device__ __forceinline__ float geluErf(float x)
 {
-    return 0.5f * x * (1.f + fastErf(x * 0.70710678118654752440f));
+    float const z = fabsf(x) * 0.70710678118654752440f;
+    float p = fmaf(0.0000430638f, z, 0.0002765672f);
+    p = fmaf(p, z, 0.0001520143f);
+    p = fmaf(p, z, 0.0092705272f);
+    p = fmaf(p, z, 0.0422820123f);
+    p = fmaf(p, z, 0.0705230784f);
+    p = fmaf(p, z, 1.f);
+    p *= p;
+    p *= p;
+    p *= p;
+    p *= p; // overflows to +inf for large |x|: erfc -> 0
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(p));
+    float const h = 0.5f * x * r;
+    return x >= 0.f ? x - h : h;
 }
 
 template <typename Out>
@@ -149,7 +152,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
         for (int i = 0; i < 2; ++i)
         {
             mbarInit(&accFull[i], 1);
-            mbarInit(&accEmpty[i], 128);
+            mbarInit(&accEmpty[i], kEpilogueThreads);
         }
         *abortFlag = 0;
         fenceBarrierInit();
@@ -262,7 +265,8 @@ __global__ void __launch_bounds__(kFcThreads, 1)
     }
     else
     {
-        int const quad = warp & 3; // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        int const quad = warp & 3;        // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
+        int const colHalf = (warp - 2) >> 2; // warps 2-5 take even 64-column groups, warps 6-9 the odd ones
         int acc = 0;
         uint32_t accPhase = 0;
         Out* const C = static_cast<Out*>(args.C);
@@ -276,8 +280,9 @@ __global__ void __launch_bounds__(kFcThreads, 1)
             int64_t const row = m0 + quad * 32 + lane;
             uint32_t const taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c)
+            for (int cc = 0; cc < BLOCK_N / 64; ++cc)
             {
+                int const c = (cc >> 1) * 4 + colHalf * 2 + (cc & 1); // 32-column chunk index inside the tile
                 uint32_t r[32];
                 tmemLoad32(taddr + c * 32, r);
                 tmemLoadWait();

@@ -561,9 +561,9 @@ extern "C" int32_t bert_b200_skip_layer_norm(void* stream, int32_t type_id, int3
 {
     B200_REQUIRE(ld > 0 && n >= 0 && n % ld == 0, "skip_layer_norm: n=%lld is not a multiple of ld=%d",
         static_cast<long long>(n), ld);
-    B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm: null pointer");
     if (n == 0)
         return BERT_B200_OK;
+    B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm: null pointer");
     auto s = static_cast<cudaStream_t>(stream);
     if (type_id == BERT_B200_FP16)
         return dispatchSkipLn<__half>(s, ld, n / ld, static_cast<__half const*>(input), static_cast<__half const*>(skip),
@@ -582,6 +582,8 @@ extern "C" int32_t bert_b200_skip_layer_norm_dqq(void* stream, int32_t ld, int64
 {
     B200_REQUIRE(ld > 0 && n >= 0 && n % ld == 0, "skip_layer_norm_dqq: n=%lld is not a multiple of ld=%d",
         static_cast<long long>(n), ld);
+    if (n == 0)
+        return BERT_B200_OK;
     B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm_dqq: null pointer");
     B200_REQUIRE(ld % 16 == 0 && ld <= 16 * 32 * 4 * 8, "skip_layer_norm_dqq: ld=%d must be a multiple of 16, <= 16384", ld);
     B200_REQUIRE(aligned16(input) && aligned16(skip) && aligned16(output) && aligned16(beta) && aligned16(gamma)

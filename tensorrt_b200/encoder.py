@@ -15,8 +15,13 @@ from ._lib import check, lib
 from .ops import FP16, INT8
 
 
-def _dev(a, dtype, device):
-    return torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dtype).contiguous()
+def _dev(a, dtype, device, transpose=False):
+    """numpy array or torch tensor -> contiguous device tensor of `dtype` (optionally transposed)."""
+    t = a if isinstance(a, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(a))
+    t = t.to(device=device)
+    if transpose:
+        t = t.t()
+    return t.to(dtype).contiguous()
 
 
 class BertEncoder:
@@ -50,14 +55,14 @@ class BertEncoder:
             lw = self._layers[i]
             if type_id == INT8:
                 s = lp.scales
-                wq = lambda name: keep(_dev(np.ascontiguousarray(s["q_" + name].T), torch.int8, d))
+                wq = lambda name: keep(_dev(s["q_" + name], torch.int8, d, transpose=True))
                 lw.wt_qkv, lw.wt_out, lw.wt_ffn1, lw.wt_ffn2 = wq("w_qkv"), wq("w_out"), wq("w_ffn1"), wq("w_ffn2")
                 lw.s_in, lw.s_wqkv, lw.s_qkv, lw.s_ctx = s["s_in"], s["s_w_qkv"], s["s_qkv"], s["s_ctx"]
                 lw.s_wout, lw.s_attn_out, lw.s_ln1 = s["s_w_out"], s["s_attn_out"], s["s_ln1"]
                 lw.s_wffn1, lw.s_ffn1, lw.s_wffn2, lw.s_ffn2, lw.s_out = (s["s_w_ffn1"], s["s_ffn1"], s["s_w_ffn2"],
                                                                           s["s_ffn2"], s["s_out"])
             else:
-                wt = lambda a: keep(_dev(np.ascontiguousarray(np.asarray(a).T), torch.float16, d))
+                wt = lambda a: keep(_dev(a, torch.float16, d, transpose=True))
                 lw.wt_qkv, lw.wt_out, lw.wt_ffn1, lw.wt_ffn2 = wt(lp.w_qkv), wt(lp.w_out), wt(lp.w_ffn1), wt(lp.w_ffn2)
             lw.b_qkv = keep(_dev(lp.b_qkv, torch.float32, d))
             lw.b_ffn1 = keep(_dev(lp.b_ffn1, torch.float32, d))
@@ -126,6 +131,36 @@ class BertEncoder:
                                                  C.c_void_p(out_dev.data_ptr()), C.c_void_p(out_h.data_ptr())),
               "encoder_forward_host")
         return out_h
+
+    def enable_timing(self, on=True):
+        """Bracket every kernel of forward() with CUDA events (see read_timing)."""
+        check(lib.bert_b200_encoder_enable_timing(self._h, 1 if on else 0), "encoder_enable_timing")
+
+    def read_timing(self, ms=None, launches=None):
+        """Adds the last forward's per-kind milliseconds / launch counts to the given ctypes arrays
+        (kinds: 0 emb, 1 fc, 2 mha, 3 skipln, 4 other) and returns them."""
+        ms = (C.c_float * 5)() if ms is None else ms
+        launches = (C.c_int32 * 5)() if launches is None else launches
+        check(lib.bert_b200_encoder_read_timing(self._h, ms, launches), "encoder_read_timing")
+        return ms, launches
+
+    def calibrate(self, ids, seg, cu, max_seqlen):
+        """Max calibration (FP16 encoder only): returns a float32 array [layers, 8] of |tensor| maxima in the order
+        layer input, qkv, ctx, attention-out projection, ln1 output, ffn1 output, ffn2 output, layer output."""
+        total, B = ids.shape[0], cu.shape[0] - 1
+        ws = self._workspace(total, B)
+        self._last = (total, B)
+        n_layers = self.cfg.num_layers
+        out = torch.empty((total, self.hidden), dtype=torch.float16, device=self.device)
+        amax_dev = torch.zeros((n_layers, 8), dtype=torch.float32, device=self.device)
+        amax_host = np.zeros((n_layers, 8), dtype=np.float32)
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        check(lib.bert_b200_encoder_calibrate(self._h, s, B, total, max_seqlen, C.c_void_p(ids.data_ptr()),
+                                              C.c_void_p(seg.data_ptr()), C.c_void_p(cu.data_ptr()),
+                                              C.c_void_p(ws.data_ptr()), self._ws_bytes, C.c_void_p(out.data_ptr()),
+                                              C.c_void_p(amax_dev.data_ptr()),
+                                              amax_host.ctypes.data_as(C.POINTER(C.c_float))), "encoder_calibrate")
+        return amax_host
 
     def status_word(self):
         """Non-zero if a bounded device wait expired in the last forward (see bert_b200.h)."""
