@@ -117,14 +117,14 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, timing=True):
-    """Device-resident timing: W warm-up forwards, then K forwards between two CUDA events on the launching stream."""
-    import torch
-
+def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, profile_steps=3):
+    """Device-resident timing: W warm-up forwards, then K forwards between two CUDA events on the launching stream.
+    Afterwards `profile_steps` more forwards run with every kernel bracketed by CUDA events (same inputs, same stream)
+    to split the step by kernel kind; those instrumented steps are not part of the reported step time."""
     import ctypes as C
 
-    kind_ms, kind_n = (C.c_float * 5)(), (C.c_int32 * 5)()
-    enc.enable_timing(timing)  # on during warm-up too, so the events exist before the timed region
+    import torch
+
     for _ in range(warmup):
         enc.forward(ids, seg, cu, SEQ, out=out)
     torch.cuda.synchronize()
@@ -138,13 +138,17 @@ def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, timing=True
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    if timing:
-        # per-kind split of the LAST timed forward (events are re-used by every forward)
-        enc.read_timing(kind_ms, kind_n)
-    enc.enable_timing(False)
     if world > 1:
         dist.barrier()
-    return ms, list(kind_ms), list(kind_n)
+    kind_ms, kind_n = (C.c_float * 5)(), (C.c_int32 * 5)()
+    enc.enable_timing(True)
+    enc.forward(ids, seg, cu, SEQ, out=out)  # creates the events
+    torch.cuda.synchronize()
+    for _ in range(profile_steps):
+        enc.forward(ids, seg, cu, SEQ, out=out)
+        enc.read_timing(kind_ms, kind_n)  # synchronises, then adds this forward's per-kind times
+    enc.enable_timing(False)
+    return ms, [v / profile_steps for v in kind_ms], [v // profile_steps for v in kind_n]
 
 
 def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
