@@ -147,6 +147,16 @@ BERT_B200_API int32_t bert_b200_convert_mask(uint32_t S, uint32_t B, uint32_t wa
     uint32_t warps_k, int32_t const* input_mask_sb, uint32_t* input_mask_x, void* stream);
 
 /*
+ * Recovers lengths[b] (first masked key position, S if none) from a packed mask written by
+ * bert_b200_convert_mask; row_words is the uint32 stride between sequences in `packed_mask`.
+ * The sm_100a attention kernel consumes lengths, so the QKVToContext plugin converts the packed mask
+ * it receives from the embedding plugin with this helper. No counterpart in the reference, whose fused
+ * kernels read the packed mask directly (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860).
+ */
+BERT_B200_API int32_t bert_b200_packed_mask_to_lengths(void* stream, int32_t S, int32_t B, uint32_t warps_m,
+    uint32_t warps_n, uint32_t row_words, uint32_t const* packed_mask, int32_t* lengths);
+
+/*
  * cu_seqlens[0] = 0, cu_seqlens[b+1] = cu_seqlens[b] + lengths[b] (int32, B <= 65536).
  * No counterpart in the reference, where the caller prepares cu_seqlens on the host
  * (plugin/embLayerNormPlugin/embLayerNormVarSeqlenPlugin.cpp:370-396 consumes it as an input).

@@ -63,6 +63,7 @@ SIGNATURES = {
     "bert_b200_emb_layer_norm_var_seqlen": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, f32]),
     "bert_b200_compute_mask_idx": (i32, [vp, i32, i32, vp, vp]),
     "bert_b200_convert_mask": (i32, [u32, u32, u32, u32, u32, vp, vp, vp]),
+    "bert_b200_packed_mask_to_lengths": (i32, [vp, i32, i32, u32, u32, u32, vp, vp]),
     "bert_b200_lengths_to_cu_seqlens": (i32, [vp, i32, vp, vp]),
     "bert_b200_fc": (i32, [C.POINTER(FcParams), vp]),
     "bert_b200_mha": (i32, [C.POINTER(MhaParams), vp]),

@@ -321,6 +321,38 @@ __global__ void packMaskKernel(uint32_t const warpsM, uint32_t const warpsN, uin
     maskX[(static_cast<size_t>(bi) * xmmasM + mi) * threadsPerCta + tidx] = bits;
 }
 
+// Inverse of packMaskKernel for prefix masks: lengths[b] = first key position whose bit is clear (S if none).
+// Key s lives in row mi = 0, thread ((s % (16*warpsN)) / 16 * warpsM) * 32 + ((s % 8) / 2),
+// bit 8 * (s / (16*warpsN)) + ((s % 16) >= 8 ? 4 : 0) + (s % 2).
+__global__ void __launch_bounds__(kThreads) packedMaskToLengthsKernel(uint32_t const warpsM, uint32_t const warpsN,
+    uint32_t const rowWords, int32_t const S, int32_t const B, uint32_t const* __restrict__ maskX, int32_t* __restrict__ lengths)
+{
+    int const lane = threadIdx.x & 31;
+    int const b = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (b >= B)
+        return;
+    int first = S;
+    for (int base = 0; base < S && first == S; base += 32)
+    {
+        int const s = base + lane;
+        bool zero = false;
+        if (s < S)
+        {
+            uint32_t const span = 16 * warpsN;
+            uint32_t const ni = s / span;
+            uint32_t const rem = s % span;
+            uint32_t const t = (rem / 16) * warpsM * 32 + ((rem % 8) / 2);
+            uint32_t const bit = 8 * ni + ((rem % 16) >= 8 ? 4u : 0u) + (rem % 2);
+            zero = ((maskX[static_cast<size_t>(b) * rowWords + t] >> bit) & 1u) == 0u;
+        }
+        uint32_t const ballot = __ballot_sync(0xffffffffu, zero);
+        if (ballot)
+            first = base + __ffs(ballot) - 1;
+    }
+    if (lane == 0)
+        lengths[b] = first;
+}
+
 // Single-CTA exclusive scan of up to 65536 lengths.
 __global__ void __launch_bounds__(1024) cuSeqlensKernel(int32_t const B, int32_t const* __restrict__ lengths,
     int32_t* __restrict__ cu)
@@ -502,6 +534,20 @@ extern "C" int32_t bert_b200_convert_mask(uint32_t S, uint32_t B, uint32_t warps
     packMaskKernel<<<dim3(xmmasM, B), threads, smem, static_cast<cudaStream_t>(stream)>>>(
         warps_m, warps_n, S, input_mask_sb, input_mask_x);
     return checkLaunch("packMaskKernel");
+}
+
+extern "C" int32_t bert_b200_packed_mask_to_lengths(void* stream, int32_t S, int32_t B, uint32_t warps_m, uint32_t warps_n,
+    uint32_t row_words, uint32_t const* packed_mask, int32_t* lengths)
+{
+    B200_REQUIRE(S > 0 && B >= 0 && warps_m > 0 && warps_n > 0, "packed_mask_to_lengths: bad sizes");
+    B200_REQUIRE((S + 16 * warps_n - 1) / (16 * warps_n) <= 4, "packed_mask_to_lengths: S=%d needs more than 32 mask bits", S);
+    B200_REQUIRE(row_words >= warps_m * warps_n * 32, "packed_mask_to_lengths: row_words smaller than one CTA row");
+    B200_REQUIRE(packed_mask && lengths, "packed_mask_to_lengths: null pointer");
+    if (B == 0)
+        return BERT_B200_OK;
+    packedMaskToLengthsKernel<<<(B + kWarpsPerCta - 1) / kWarpsPerCta, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        warps_m, warps_n, row_words, S, B, packed_mask, lengths);
+    return checkLaunch("packedMaskToLengthsKernel");
 }
 
 extern "C" int32_t bert_b200_lengths_to_cu_seqlens(void* stream, int32_t B, int32_t const* lengths, int32_t* cu_seqlens)

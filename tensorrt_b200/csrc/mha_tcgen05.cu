@@ -99,14 +99,19 @@ __device__ __forceinline__ void tmemStoreWait()
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-template <typename T>
+// IL (INT8 only): CHW32-interleaved tensors. Q, K and V tiles then arrive as two 32-channel sub-tiles of
+// [128 tokens][32 B] (32-byte swizzle); the head dimension is covered by one MMA per sub-tile.
+template <typename T, bool IL>
 __global__ void __launch_bounds__(kMhaThreads, 1)
     mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, MhaArgs const args)
 {
     using L = MhaSmem<T>;
     constexpr bool kInt8 = sizeof(T) == 1;
-    constexpr uint64_t kSwz = kInt8 ? kSwizzle64B : kSwizzle128B; // Q, K, V rows are 64 B (INT8) or 128 B (FP16)
-    constexpr uint32_t kAtomBytes = 8 * L::kRowBytes;             // 8 rows of a swizzle atom: SBO
+    static_assert(!IL || kInt8, "the interleaved layout is INT8 only");
+    // Q, K, V rows are 128 B (FP16), 64 B (INT8) or 32 B (interleaved INT8 sub-tiles)
+    constexpr uint64_t kSwz = IL ? kSwizzle32B : (kInt8 ? kSwizzle64B : kSwizzle128B);
+    constexpr uint32_t kAtomBytes = IL ? 256u : 8 * L::kRowBytes; // 8 rows of a swizzle atom: SBO
+    constexpr uint32_t kSubTile = L::kTileBytes / 2;              // interleaved: bytes of one 32-channel sub-tile
     constexpr int kQkMmas = kInt8 ? 2 : 4;                        // head size 64 = 2 x 32 (INT8) or 4 x 16 (FP16)
     constexpr int kPvMmas = kInt8 ? 4 : 8;                        // 128 keys = 4 x 32 or 8 x 16
     constexpr uint32_t kIdescQk = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, 128u, 128u);
@@ -137,18 +142,31 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         return;
     int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
     T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(head) * kHeadSize;
+    // linear layouts: the 64 values of (token, head) are contiguous. Interleaved: see outPtrIl below.
     auto outRow = [&](int q) -> T* {
         int64_t const r = args.fixedLayout ? static_cast<int64_t>(q) * args.B + b : static_cast<int64_t>(rowBase) + q;
         return outBase + r * outRowStride;
     };
+    // interleaved output [N][2][total][32]: 32-channel group `grp` of (token, head)
+    auto outPtrIl = [&](int q, int grp) -> T* {
+        return static_cast<T*>(args.out)
+            + ((static_cast<int64_t>(head) * 2 + grp) * args.total + rowBase + q) * 32;
+    };
     if (len == 0)
     {
         // no valid key: every probability is zero and so is the context row
-        for (int i = threadIdx.x; i < kQTile * (L::kRowBytes / 16); i += kMhaThreads)
+        constexpr int kChunks = L::kRowBytes / 16;
+        for (int i = threadIdx.x; i < kQTile * kChunks; i += kMhaThreads)
         {
-            int const q = q0 + i / (L::kRowBytes / 16);
+            int const q = q0 + i / kChunks;
+            int const c = i % kChunks;
             if (q < rows)
-                reinterpret_cast<uint4*>(outRow(q))[i % (L::kRowBytes / 16)] = make_uint4(0, 0, 0, 0);
+            {
+                if (IL)
+                    reinterpret_cast<uint4*>(outPtrIl(q, c / 2))[c % 2] = make_uint4(0, 0, 0, 0);
+                else
+                    reinterpret_cast<uint4*>(outRow(q))[c] = make_uint4(0, 0, 0, 0);
+            }
         }
         return;
     }
@@ -199,22 +217,27 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     {
         if (lane == 0)
         {
-            int32_t const c1 = args.fixedLayout ? b : 0;
             int32_t const rowQ = args.fixedLayout ? q0 : rowBase + q0;
             int32_t const rowK = args.fixedLayout ? 0 : rowBase;
-            int32_t const colQ = head * 3 * kHeadSize;
+            // linear: (column of the token row, batch, row). interleaved: (0, row, 32-channel group of [3][N][2])
+            auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
+                if (IL)
+                    tmaLoad3d(dst, &mapQkv, bar, 0, row, (which * args.N + head) * 2);
+                else
+                    tmaLoad3d(dst, &mapQkv, bar, (head * 3 + which) * kHeadSize, args.fixedLayout ? b : 0, row);
+            };
             mbarArriveExpectTx(&qkFull[0], 2 * L::kTileBytes);
-            tmaLoad3d(sQ, &mapQkv, &qkFull[0], colQ, c1, rowQ);
-            tmaLoad3d(sK, &mapQkv, &qkFull[0], colQ + kHeadSize, c1, rowK);
+            load(sQ, &qkFull[0], 0, rowQ);
+            load(sK, &qkFull[0], 1, rowK);
             for (int j = 1; j < nb; ++j)
             {
                 mbarArriveExpectTx(&qkFull[j], L::kTileBytes);
-                tmaLoad3d(sK + j * L::kTileBytes, &mapQkv, &qkFull[j], colQ + kHeadSize, c1, rowK + j * kKeyBlock);
+                load(sK + j * L::kTileBytes, &qkFull[j], 1, rowK + j * kKeyBlock);
             }
             for (int j = 0; j < nb; ++j)
             {
                 mbarArriveExpectTx(&vFull[j], L::kTileBytes);
-                tmaLoad3d(sV + j * L::kTileBytes, &mapQkv, &vFull[j], colQ + 2 * kHeadSize, c1, rowK + j * kKeyBlock);
+                load(sV + j * L::kTileBytes, &vFull[j], 2, rowK + j * kKeyBlock);
             }
         }
     }
@@ -234,8 +257,9 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k)
                 {
-                    uint64_t const aDesc = makeSmemDesc(qAddr + k * 32, 16, kAtomBytes, kSwz);
-                    uint64_t const bDesc = makeSmemDesc(kAddr + k * 32, 16, kAtomBytes, kSwz);
+                    uint32_t const kOff = IL ? k * kSubTile : k * 32; // next 32 bytes of the head dimension
+                    uint64_t const aDesc = makeSmemDesc(qAddr + kOff, 16, kAtomBytes, kSwz);
+                    uint64_t const bDesc = makeSmemDesc(kAddr + kOff, 16, kAtomBytes, kSwz);
                     if (kInt8)
                         mmaI8(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
                     else
@@ -258,7 +282,9 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
                     uint64_t const aDesc = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
                     // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
-                    uint64_t const bDesc = makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
+                    // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
+                    uint64_t const bDesc = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
+                                              : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
                     if (kInt8)
                         mmaI8(tmemBase, aDesc, bDesc, kIdescPv, (j | k) != 0);
                     else
@@ -425,7 +451,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             int const q = q0 + r;
             if (q < rows)
             {
-                T* dst = outRow(q) + half * 32;
+                T* dst = IL ? outPtrIl(q, half) : outRow(q) + half * 32;
                 if (kInt8)
                 {
                     float const s2 = args.scaleBmm2;
@@ -479,13 +505,25 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     }
 }
 
-template <typename T>
+template <typename T, bool IL>
 int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
 {
     using L = MhaSmem<T>;
     bool const fixedLayout = p.cu_seqlens == nullptr;
     int64_t const rowElems = static_cast<int64_t>(3) * p.num_heads * kHeadSize;
     CUtensorMap map;
+    if (IL)
+    {
+        // [3][N][2][total][32]: dim0 the 32 channels of a group, dim1 the token, dim2 the group
+        uint64_t const dims[3] = {32, static_cast<uint64_t>(p.total), static_cast<uint64_t>(6) * p.num_heads};
+        uint64_t const strides[2] = {32, static_cast<uint64_t>(p.total) * 32};
+        uint32_t const box[3] = {32, kKeyBlock, 2};
+        int32_t const st = makeTensorMap(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p.qkv, dims, strides, box,
+            CU_TENSOR_MAP_SWIZZLE_32B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    else
     {
         // dim0: the 3*N*d values of one token; dim1: batch (fixed layout only); dim2: sequence position / packed row
         uint64_t const dims[3] = {static_cast<uint64_t>(rowElems), fixedLayout ? static_cast<uint64_t>(p.B) : 1ull,
@@ -500,7 +538,7 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     }
     int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
     int const smem = L::dynamicBytes(nbMax);
-    auto kernel = mhaTcgen05Kernel<T>;
+    auto kernel = mhaTcgen05Kernel<T, IL>;
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -535,10 +573,14 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: the tensor-core path needs head_size 64 (got %d)", p.head_size);
     if (p.S > kMaxBlocks * kKeyBlock)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: S=%d exceeds %d", p.S, kMaxBlocks * kKeyBlock);
-    if (p.interleaved)
-        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: the interleaved (CHW32) layout is not implemented yet");
     B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
+    if (p.interleaved)
+    {
+        B200_REQUIRE(p.type_id == BERT_B200_INT8 && p.cu_seqlens != nullptr,
+            "mha: the interleaved (CHW32) layout needs INT8 and the packed (cu_seqlens) form");
+        return launchMha<int8_t, true>(p, s);
+    }
     if (p.type_id == BERT_B200_FP16)
-        return launchMha<__half>(p, s);
-    return launchMha<int8_t>(p, s);
+        return launchMha<__half, false>(p, s);
+    return launchMha<int8_t, false>(p, s);
 }

@@ -121,6 +121,16 @@ def convert_mask(mask_sb, warps_m, warps_n, warps_k=1):
     return out
 
 
+def packed_mask_to_lengths(packed, S, warps_m, warps_n):
+    """packed: [B, words] int32/uint32 as written by convert_mask -> lengths [B] int32."""
+    B = packed.shape[0]
+    row_words = packed[0].numel()
+    out = torch.empty((B,), dtype=torch.int32, device=packed.device)
+    check(lib.bert_b200_packed_mask_to_lengths(_stream(), S, B, warps_m, warps_n, row_words, _ptr(packed), _ptr(out)),
+          "packed_mask_to_lengths")
+    return out
+
+
 def lengths_to_cu_seqlens(lengths):
     B = lengths.shape[0]
     out = torch.empty((B + 1,), dtype=torch.int32, device=lengths.device)
@@ -141,10 +151,14 @@ def fc(a, wt, bias=None, activation=ACT_NONE, alpha=1.0, out_dtype=None, out_sca
 
 
 def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scale_bmm1=None, scale_softmax=1.0,
-        scale_bmm2=1.0, status=None):
-    """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None) or packed [total, 3*N*d]."""
+        scale_bmm2=1.0, status=None, interleaved=False):
+    """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None), packed [total, 3*N*d], or with
+    interleaved=True the INT8 CHW32 form [3*N*d/32, total, 32] (output [N*d/32, total, 32])."""
     E = num_heads * head_size
-    if cu_seqlens is None:
+    if interleaved:
+        total = qkv.shape[1]
+        out = torch.empty((E // 32, total, 32), dtype=qkv.dtype, device=qkv.device)
+    elif cu_seqlens is None:
         out = torch.empty((S, B, E), dtype=qkv.dtype, device=qkv.device)
         total = 0
     else:
@@ -153,6 +167,6 @@ def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scal
     if scale_bmm1 is None:
         scale_bmm1 = head_size ** -0.5
     p = _lib.MhaParams(_TYPE_ID[qkv.dtype], B, S, num_heads, head_size, total, _ptr(qkv), _ptr(out), _ptr(cu_seqlens),
-                       _ptr(mask_idx), 0, scale_bmm1, scale_softmax, scale_bmm2, _ptr(status))
+                       _ptr(mask_idx), 1 if interleaved else 0, scale_bmm1, scale_softmax, scale_bmm2, _ptr(status))
     check(lib.bert_b200_mha(C.byref(p), _stream()), "mha")
     return out

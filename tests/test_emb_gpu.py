@@ -111,8 +111,12 @@ def test_packed_mask_bit_exact(cuda, S, wm, wn):
     B = 4
     lengths = rng.integers(1, S + 1, size=B)
     mask = (np.arange(S)[:, None] < lengths[None, :]).astype(np.int32)
-    out = T.convert_mask(_t(mask, cuda), wm, wn).cpu().numpy().view(np.uint32)
+    packed = T.convert_mask(_t(mask, cuda), wm, wn)
+    out = packed.cpu().numpy().view(np.uint32)
     assert np.array_equal(out, O.packed_mask(mask, wm, wn))
+    # and back: the attention plugin recovers the lengths from the packed form
+    back = T.packed_mask_to_lengths(packed, S, wm, wn).cpu().numpy()
+    assert np.array_equal(back, lengths.astype(np.int32))
 
 
 @pytest.mark.parametrize("B", [0, 1, 31, 256, 1024, 5000])

@@ -105,6 +105,32 @@ def test_mha_fixed_int8(cuda, S, B, N):
     assert ok, (worst, bad)
 
 
+@pytest.mark.parametrize("lengths,N", [([384, 32, 129, 1, 0, 257, 128], 16), ([100], 2)])
+def test_mha_interleaved_int8(cuda, lengths, N):
+    """CHW32-interleaved I/O of plugin version 6: qkv [3][N][d/32][total][32], out [N][d/32][total][32]."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(len(lengths) + N + 11)
+    d = 64
+    lengths = np.array(lengths, dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, B, S = int(cu[-1]), len(lengths), int(max(lengths.max(), 1))
+    q8, s_qkv = _int8_case(rng, total, N, d)           # linear [total, N, 3, d]
+    dq_probs = 1.0 / 127.0
+    s_ctx = s_qkv * 0.5
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    s2 = dq_probs * s_qkv / s_ctx
+    ref = O.mha_int8(q8, B, S, N, d, s1, 1.0 / dq_probs, s2, cu=cu)            # [total, N*d]
+    il = np.ascontiguousarray(q8.reshape(total, N, 3, 2, 32).transpose(2, 1, 3, 0, 4)).reshape(3 * N * 2, total, 32)
+    st = _status(cuda)
+    out = T.mha(_t(il, cuda), B, S, N, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs,
+                scale_bmm2=s2, status=st, interleaved=True)
+    assert int(st[0]) == 0
+    lin = out.cpu().numpy().reshape(N, 2, total, 32).transpose(2, 0, 1, 3).reshape(total, N * d)
+    ok, worst, bad = O.int8_within_lsb(lin, ref)
+    assert ok, (worst, bad)
+
+
 @pytest.mark.parametrize("d", [32, 64])
 def test_mha_fp32(cuda, d):
     import tensorrt_b200 as T
