@@ -359,8 +359,10 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
 #pragma unroll
                 for (int i = 0; i < 32; ++i)
                 {
-                    float const v = kInt8 ? static_cast<float>(static_cast<int32_t>(x[i])) : __uint_as_float(x[i]);
-                    float const e = ex2Approx(fmaf(v, sl2, -mOff));
+                    // INT8: accumulators and their maximum are exact integers in FP32, so the difference is exact
+                    // and the exponent carries a single rounding; FP16: one fused multiply-add.
+                    float const e = kInt8 ? ex2Approx((static_cast<float>(static_cast<int32_t>(x[i])) - mx) * sl2)
+                                          : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
                     p[i] = i < limit ? e : 0.f;
                     sum += p[i];
                 }

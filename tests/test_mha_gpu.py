@@ -54,6 +54,16 @@ def test_mha_packed_fp16(cuda, lengths, N):
     assert ok, (worst, bad)
 
 
+def _assert_int8_attention(out, ref):
+    """+-1 LSB, except where a rounding tie of a quantised probability P_q = rni(p * 127) falls the other way: one
+    such flip moves the INT32 accumulator by |v| <= 127, i.e. the output by up to scale_bmm2 * 127 = s_qkv / s_ctx
+    (= 2 LSB with the scales used here). At most 1e-5 of the values may therefore be off by 2."""
+    d = np.abs(out.astype(np.int32) - ref.astype(np.int32))
+    assert d.max() <= 2, int(d.max())
+    assert (d > 1).sum() <= max(1, int(1e-5 * d.size)), int((d > 1).sum())
+    assert (d == 0).mean() > 0.98
+
+
 def _int8_case(rng, rows, N, d):
     x = rng.standard_normal((rows, 3 * N * d))
     s_qkv = O.amax_scale(x)
@@ -79,8 +89,7 @@ def test_mha_packed_int8(cuda, lengths, N):
     out = T.mha(_t(q8, cuda), B, S, N, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs,
                 scale_bmm2=s2, status=st)
     assert int(st[0]) == 0
-    ok, worst, bad = O.int8_within_lsb(out.cpu().numpy(), ref)
-    assert ok, (worst, bad)
+    _assert_int8_attention(out.cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("S,B,N", [(128, 4, 12), (384, 2, 16)])
@@ -101,8 +110,7 @@ def test_mha_fixed_int8(cuda, S, B, N):
     out = T.mha(_t(q8, cuda), B, S, N, mask_idx=_t(lengths, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs,
                 scale_bmm2=s2, status=st)
     assert int(st[0]) == 0
-    ok, worst, bad = O.int8_within_lsb(out.cpu().numpy(), ref)
-    assert ok, (worst, bad)
+    _assert_int8_attention(out.cpu().numpy(), ref)
 
 
 @pytest.mark.parametrize("lengths,N", [([384, 32, 129, 1, 0, 257, 128], 16), ([100], 2)])
@@ -127,8 +135,7 @@ def test_mha_interleaved_int8(cuda, lengths, N):
                 scale_bmm2=s2, status=st, interleaved=True)
     assert int(st[0]) == 0
     lin = out.cpu().numpy().reshape(N, 2, total, 32).transpose(2, 0, 1, 3).reshape(total, N * d)
-    ok, worst, bad = O.int8_within_lsb(lin, ref)
-    assert ok, (worst, bad)
+    _assert_int8_attention(lin, ref)
 
 
 @pytest.mark.parametrize("d", [32, 64])

@@ -15,6 +15,12 @@ def _t(a, cuda):
     return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
 
 
+def _int8_attention_ok(out, ref):
+    """+-1 LSB except for rare rounding ties of the quantised probabilities (see tests/test_mha_gpu.py)."""
+    d = np.abs(out.astype(np.int32) - ref.astype(np.int32))
+    return d.max() <= 2 and (d > 1).sum() <= max(1, int(1e-5 * d.size))
+
+
 def _run(p, H, ins, outs, in_descs, out_descs, workspace=None):
     st = p.enqueue(in_descs, out_descs, [t.data_ptr() for t in ins], [t.data_ptr() for t in outs],
                    workspace.data_ptr() if workspace is not None else None, torch.cuda.current_stream().cuda_stream)
@@ -142,7 +148,7 @@ def test_qkv_v5_var_seqlen(cuda, type_id):
     if type_id == 1:
         assert O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)[0]
     else:
-        assert O.int8_within_lsb(out.cpu().numpy(), ref)[0]
+        assert _int8_attention_ok(out.cpu().numpy(), ref)
     p.close()
 
 
@@ -169,7 +175,7 @@ def test_qkv_v6_interleaved(cuda):
     outd = [H.make_desc((1, E, total, 1), H.INT8, H.CHW32, 456.0)]  # descriptor scales are ignored with use_explicit_int8
     _run(p, H, [_t(il, cuda), _t(cu, cuda), torch.zeros(S, dtype=torch.int32, device=cuda)], [out], ind, outd)
     lin = out.cpu().numpy().reshape(N, 2, total, 32).transpose(2, 0, 1, 3).reshape(total, E)
-    assert O.int8_within_lsb(lin, ref)[0]
+    assert _int8_attention_ok(lin, ref)
     p.close()
 
 
