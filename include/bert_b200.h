@@ -359,6 +359,34 @@ BERT_B200_API int32_t bert_b200_encoder_forward(bert_b200_encoder* enc, void* st
     void* workspace, int64_t workspace_bytes, void* output);
 
 /*
+ * bert_b200_encoder_forward without a workspace argument. (No counterpart in the reference: its plugins get their
+ * scratch from TensorRT's workspace.)
+ *
+ * Who needs it: callers that are not in a position to allocate device memory at all - code that runs inside
+ * someone else's memory budget (a plugin's enqueue(), which may only use what the host framework hands it; a
+ * serving loop whose whole device pool belongs to another runtime), or code on a path where a failed or slow
+ * cudaMalloc is not acceptable. Such a caller passes only its inputs and the output buffer; the intermediate
+ * tensors live in a buffer built into the library image.
+ *
+ * Limit: that buffer is BERT_B200_STATIC_WORKSPACE_BYTES (16 MiB) and every GPU that loads the library keeps it
+ * reserved until the process exits. A call whose bert_b200_encoder_workspace_size(cfg, total, B) exceeds it is
+ * rejected with BERT_B200_NOT_SUPPORTED and a message naming both sizes (BERT-large INT8: about 1200 tokens;
+ * BERT-base FP16: about 950 tokens); bert_b200_encoder_static_workspace_limit() returns the limit.
+ *
+ * The call itself allocates nothing: no cudaMalloc / cudaFree, no event or stream creation (it refuses to run
+ * while per-kernel timing is enabled for that reason). The first call on each device asks the CUDA runtime for the
+ * device address of the built-in buffer (that device must be current); make that first call outside any stream
+ * capture. All calls on a device share the one buffer, which still holds the previous call's intermediates: the
+ * status word is re-zeroed at the start of every call and everything else is overwritten before it is read, but
+ * two calls that overlap on the GPU (different streams, or different encoders) corrupt each other - serialise them.
+ */
+#define BERT_B200_STATIC_WORKSPACE_BYTES (16ll * 1024 * 1024)
+BERT_B200_API int64_t bert_b200_encoder_static_workspace_limit(void);
+BERT_B200_API int32_t bert_b200_encoder_forward_static(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids, int32_t const* segment_ids, int32_t const* cu_seqlens,
+    void* output);
+
+/*
  * Same through HOST buffers (pinned or pageable): copies ids / segment ids / cu_seqlens to the
  * device staging area at the head of `workspace`, runs the encoder, copies the FP16 output back
  * into output_host and synchronises `stream`.

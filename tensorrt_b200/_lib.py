@@ -75,6 +75,8 @@ SIGNATURES = {
     "bert_b200_encoder_read_timing": (i32, [vp, C.POINTER(f32), C.POINTER(i32)]),
     "bert_b200_encoder_calibrate": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp, C.POINTER(f32)]),
     "bert_b200_encoder_forward": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp]),
+    "bert_b200_encoder_static_workspace_limit": (i64, []),
+    "bert_b200_encoder_forward_static": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp]),
     "bert_b200_encoder_forward_host": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp]),
 }
 

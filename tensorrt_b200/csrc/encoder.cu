@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <mutex>
 #include <new>
 #include <vector>
 
@@ -504,4 +505,70 @@ extern "C" int32_t bert_b200_encoder_calibrate(bert_b200_encoder* enc, void* str
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_calibrate: %s", cudaGetErrorString(e));
     return BERT_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Forward pass that needs no caller-provided scratch memory
+// ------------------------------------------------------------------------------------------------
+namespace
+{
+// Scratch for bert_b200_encoder_forward_static. It is part of the library image: every GPU that loads the
+// library reserves these bytes until the process exits, whether the entry point is used or not.
+constexpr int64_t kStaticWorkspaceBytes = BERT_B200_STATIC_WORKSPACE_BYTES;
+static __device__ __align__(256) uint8_t gStaticWorkspace[kStaticWorkspaceBytes + 1024];
+
+// In host code `gStaticWorkspace` is only a handle for the symbol, not a device address: the address the kernels
+// can use has to be asked from the runtime, once per device, with that device current.
+int32_t staticWorkspace(void** out)
+{
+    static std::mutex mtx;
+    static void* perDevice[64] = {nullptr};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(mtx);
+    if (!perDevice[dev])
+    {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, gStaticWorkspace);
+        if (e != cudaSuccess || p == nullptr)
+            B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        // the layer loop wants 1024-byte alignment; the array carries 1 KiB of slack for rounding up
+        perDevice[dev] = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+    }
+    *out = perDevice[dev];
+    return BERT_B200_OK;
+}
+} // namespace
+
+extern "C" int64_t bert_b200_encoder_static_workspace_limit(void)
+{
+    return kStaticWorkspaceBytes;
+}
+
+extern "C" int32_t bert_b200_encoder_forward_static(bert_b200_encoder* enc, void* stream, int32_t B, int32_t total,
+    int32_t max_seqlen, int32_t const* input_ids, int32_t const* segment_ids, int32_t const* cu_seqlens, void* output)
+{
+    B200_REQUIRE(enc != nullptr, "encoder_forward_static: null encoder");
+    B200_REQUIRE(!enc->timing, "encoder_forward_static: per-kernel timing creates CUDA events; disable it for this entry point");
+    B200_REQUIRE(B > 0 && total > 0, "encoder_forward_static: bad sizes B=%d total=%d", B, total);
+    int64_t const need = carve(enc->cfg, total, B, nullptr).bytes;
+    if (need > kStaticWorkspaceBytes)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED,
+            "encoder_forward_static: %d tokens / %d sequences need %lld bytes of scratch, the built-in buffer holds %lld; "
+            "use bert_b200_encoder_forward with a caller-allocated workspace",
+            total, B, static_cast<long long>(need), static_cast<long long>(kStaticWorkspaceBytes));
+    void* ws = nullptr;
+    int32_t st = staticWorkspace(&ws);
+    if (st != BERT_B200_OK)
+        return st;
+    Workspace w{};
+    st = checkForward(enc, B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, ws, kStaticWorkspaceBytes, output, &w);
+    if (st != BERT_B200_OK)
+        return st;
+    // Every buffer carved from the scratch is written before it is read in one forward; the only word that has
+    // to start from zero, the device-wait status word, is cleared by forwardImpl.
+    return forwardImpl(enc, static_cast<cudaStream_t>(stream), B, total, max_seqlen, input_ids, segment_ids, cu_seqlens, w,
+        output);
 }
