@@ -3,12 +3,15 @@
 Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / --impl reference legs may import this
 module; the product path (tensorrt_b200/) never does and has no CPU fallback.
 
-PARITY UNPINNED by reference fixtures: the reference tree ships no golden I/O for these plugins (the
-`*_PluginGoldenIO.json` / `*_PluginReference.py` files named by the plugin YAMLs are absent), and its
-attention arithmetic lives in precompiled kernels and cuBLAS. Each function below therefore restates the
-reference's *source-visible* algorithm in NumPy (float64 statistics, exact integer accumulation) and
-cites the file:line it follows; tests/golden/ holds known-answer vectors produced by this module so that
-regressions in the oracle itself are caught.
+PARITY PINNED against outputs of the reference itself: the reference tree ships no golden I/O for these plugins
+(the `*_PluginGoldenIO.json` / `*_PluginReference.py` files named by the plugin YAMLs are absent), so the reference's
+own kernels - its SIMT LayerNorm / embedding / mask kernels compiled from source and the precompiled sm100 attention
+kernels it ships - were run on a B200 (oracle/build_ref.py -> oracle/_ref/libref_bert.so, tests/golden/make_golden.py)
+and their outputs are committed as tests/golden/reference_kernels.npz. tests/test_golden_cpu.py checks every function
+below against them (index outputs and the INT8 attention output bit-exact, FP32 1e-5, FP16 1e-2, INT8 LayerNorm
++-1 LSB); tests/test_reference_pin_gpu.py repeats the comparison live on larger inputs. Each function restates the
+reference's source-visible algorithm in NumPy (float64 statistics, exact integer accumulation) and cites the
+file:line it follows. The FC plugin's cuBLASLt GEMM and the whole-encoder wiring have no reference output here.
 
 Paths are relative to the TensorRT-OSS tree.
 """
