@@ -1,16 +1,20 @@
 // Fused multi-head attention on the sm_100a tensor cores (head size 64, sequence length <= 512),
-// FP16 and INT8, fixed [S,B,N,3,d] and packed [total,N,3,d] layouts.
+// FP16 and INT8, fixed [S,B,N,3,d], packed [total,N,3,d] and INT8 CHW32-interleaved layouts.
 //
 // Replaces the precompiled fused attention kernels the reference launches through
 // FusedMHARunnerFP16/Int8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265) and the
 // unfused cuBLAS + softmax path (mhaRunner.cu:533-601).
 //
-// One CTA = one (sequence, head, 128-query tile); 10 warps:
-//   warp 0    : TMA - Q tile and every 128-key K / V block of the sequence (swizzled, own mbarrier each).
-//   warp 1    : TMEM allocation; one lane issues tcgen05.mma:
+// One CTA = one (sequence, head); it loops over the 128-query tiles of that sequence so that K and V are loaded
+// once and the tensor pipe works on the next tile while the softmax warps finish the current one. 18 warps:
+//   warp 0    : TMA - every 128-key K / V block of the sequence once, then the Q tile of each iteration
+//               (swizzled shared-memory tiles, one mbarrier each).
+//   warp 1    : TMEM allocation (512 columns); one lane issues tcgen05.mma:
 //                 S_j = Q K_j^T           (128 x 128 per key block, accumulators in TMEM columns 128j..)
-//                 O  += P_j V_j           (128 x 64, accumulator in TMEM columns 0..63, re-using S_0's columns)
-//   warps 2-9 : softmax, two threads per query row (each owns 64 of every 128 key columns):
+//                 O  += P_j V_j           (128 x 64, accumulator in TMEM columns 384..447; for S > 384 it re-uses
+//                                          the columns of S_0, which serialises consecutive tiles)
+//               and, right after P_j V_j of tile t, the scores S_j of tile t+1.
+//   warps 2-17: softmax, four threads per query row (each owns 32 of every 128 key columns):
 //                 pass A  row maximum over all key blocks straight from TMEM,
 //                 pass B  p = exp2(x*scale*log2e - max) -> FP16 P_j into swizzled shared memory for the PV product
 //                         (INT8: exp values go back to TMEM, pass C quantises p/sum*scale_softmax to INT8 P_j),
@@ -31,8 +35,10 @@ constexpr int kQTile = 128;
 constexpr int kKeyBlock = 128;
 constexpr int kHeadSize = 64;
 constexpr int kMaxBlocks = 4; // S <= 512
-constexpr int kMhaThreads = 320;
-constexpr int kSoftmaxThreads = 256;
+constexpr int kMhaThreads = 576;     // TMA warp, MMA warp, 16 softmax warps
+constexpr int kSoftmaxThreads = 512;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kOColumn = 384;   // context accumulator when the scores need at most 384 columns
 
 struct MhaArgs
 {
@@ -52,17 +58,25 @@ struct MhaSmem
     static constexpr int kRowBytes = kHeadSize * kElem;           // 128 (FP16) or 64 (INT8)
     static constexpr int kTileBytes = kQTile * kRowBytes;         // Q tile, one K block, one V block
     static constexpr int kPBytes = kQTile * kKeyBlock * kElem;    // one P block: 32 KB (FP16) or 16 KB (INT8)
-    // [ P ring (2 blocks), overlaying Q and K once the scores are complete ][ V blocks ][ barriers ]
+    // [ Q ][ K blocks ][ V blocks ][ P ring (2 blocks) ][ barriers, reduction scratch ]
+    static __host__ __device__ constexpr int kOffset()
+    {
+        return kTileBytes;
+    }
     static __host__ __device__ constexpr int vOffset(int nb)
     {
-        int const qk = (1 + nb) * kTileBytes;
-        return qk > 2 * kPBytes ? qk : 2 * kPBytes;
+        return (1 + nb) * kTileBytes;
+    }
+    static __host__ __device__ constexpr int pOffset(int nb)
+    {
+        return (1 + 2 * nb) * kTileBytes;
     }
     static __host__ __device__ constexpr int barrierOffset(int nb)
     {
-        return vOffset(nb) + nb * kTileBytes;
+        return pOffset(nb) + 2 * kPBytes;
     }
-    static constexpr int kBarrierBytes = (kMaxBlocks * 4 + 2 + 1) * 8 + 16 + 2 * kQTile * 4 * 2;
+    // kFull[4] vFull[4] sFull[4] pReady[4] pFree[2] qFull qFree oFull oFree, tmem slot + abort flag, max / sum scratch
+    static constexpr int kBarrierBytes = (4 * kMaxBlocks + 6) * 8 + 16 + 8 * kQTile * 4;
     static __host__ __device__ constexpr int dynamicBytes(int nb)
     {
         return barrierOffset(nb) + kBarrierBytes + 1024;
@@ -78,7 +92,7 @@ __device__ __forceinline__ float ex2Approx(float x)
 
 __device__ __forceinline__ void softmaxBarrier()
 {
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, 512;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmemStore32(uint32_t taddr, uint32_t const (&r)[32])
@@ -117,9 +131,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     constexpr uint32_t kIdescQk = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, 128u, 128u);
     constexpr uint32_t kIdescPv = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 1u, 128u, 64u);
 
-    int const qTile = blockIdx.x;
-    int const head = blockIdx.y;
-    int const b = blockIdx.z;
+    int const head = blockIdx.x;
+    int const b = blockIdx.y;
     int const warp = threadIdx.x >> 5;
     int const lane = threadIdx.x & 31;
 
@@ -137,8 +150,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         len = min(max(__ldg(args.cu + b + 1) - rowBase, 0), args.S);
         rows = len;
     }
-    int const q0 = qTile * kQTile;
-    if (q0 >= rows)
+    if (rows <= 0)
         return;
     int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
     T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(head) * kHeadSize;
@@ -149,65 +161,70 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     };
     // interleaved output [N][2][total][32]: 32-channel group `grp` of (token, head)
     auto outPtrIl = [&](int q, int grp) -> T* {
-        return static_cast<T*>(args.out)
-            + ((static_cast<int64_t>(head) * 2 + grp) * args.total + rowBase + q) * 32;
+        return static_cast<T*>(args.out) + ((static_cast<int64_t>(head) * 2 + grp) * args.total + rowBase + q) * 32;
     };
     if (len == 0)
     {
         // no valid key: every probability is zero and so is the context row
         constexpr int kChunks = L::kRowBytes / 16;
-        for (int i = threadIdx.x; i < kQTile * kChunks; i += kMhaThreads)
+        for (int i = threadIdx.x; i < rows * kChunks; i += kMhaThreads)
         {
-            int const q = q0 + i / kChunks;
+            int const q = i / kChunks;
             int const c = i % kChunks;
-            if (q < rows)
-            {
-                if (IL)
-                    reinterpret_cast<uint4*>(outPtrIl(q, c / 2))[c % 2] = make_uint4(0, 0, 0, 0);
-                else
-                    reinterpret_cast<uint4*>(outRow(q))[c] = make_uint4(0, 0, 0, 0);
-            }
+            if (IL)
+                reinterpret_cast<uint4*>(outPtrIl(q, c / 2))[c % 2] = make_uint4(0, 0, 0, 0);
+            else
+                reinterpret_cast<uint4*>(outRow(q))[c] = make_uint4(0, 0, 0, 0);
         }
         return;
     }
-    int const nb = (len + kKeyBlock - 1) / kKeyBlock;
-    uint32_t const tmemCols = nb <= 1 ? 128u : (nb == 2 ? 256u : 512u);
+    int const nb = (len + kKeyBlock - 1) / kKeyBlock;   // key blocks
+    int const nq = (rows + kQTile - 1) / kQTile;        // query tiles
+    // S > 384: the context accumulator has to share TMEM columns with the scores of key block 0
+    bool const oAliasesScores = nb > 3;
+    uint32_t const oCol = oAliasesScores ? 0u : kOColumn;
 
     extern __shared__ uint8_t smemRaw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* sP = smem;                          // 2 x kPBytes, valid once all scores are complete
     uint8_t* sQ = smem;                          // kTileBytes
-    uint8_t* sK = smem + L::kTileBytes;          // nb x kTileBytes
+    uint8_t* sK = smem + L::kOffset();           // nb x kTileBytes
     uint8_t* sV = smem + L::vOffset(nb);         // nb x kTileBytes
+    uint8_t* sP = smem + L::pOffset(nb);         // 2 x kPBytes
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::barrierOffset(nb));
-    uint64_t* qkFull = bars;                     // [4] Q+K_0, K_1, ...
-    uint64_t* vFull = bars + kMaxBlocks;         // [4]
-    uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete
-    uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written (256 arrivals)
-    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [2] PV product consumed ring slot
-    uint64_t* oFull = pFree + 2;                 // [1]
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(oFull + 1);
+    uint64_t* kFull = bars;                      // [4] K_j landed
+    uint64_t* vFull = bars + kMaxBlocks;         // [4] V_j landed
+    uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete       (once per query tile)
+    uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written, 512 arrivals        (once per query tile)
+    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [2] PV product consumed P ring slot
+    uint64_t* qFull = pFree + 2;                 // Q tile landed                        (once per query tile)
+    uint64_t* qFree = qFull + 1;                 // all score MMAs of the tile done: Q slot reusable
+    uint64_t* oFull = qFree + 1;                 // context accumulator complete         (once per query tile)
+    uint64_t* oFree = oFull + 1;                 // epilogue has read it, 512 arrivals   (once per query tile)
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(oFree + 1);
     volatile uint32_t* abortFlag = tmemSlot + 1;
-    float* rowRed = reinterpret_cast<float*>(tmemSlot + 4); // [2][2][128]: max then sum, per half
+    float* rowRed = reinterpret_cast<float*>(tmemSlot + 4); // [2][4][128]: max then sum, per 32-column owner
 
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < kMaxBlocks; ++i)
         {
-            mbarInit(&qkFull[i], 1);
+            mbarInit(&kFull[i], 1);
             mbarInit(&vFull[i], 1);
             mbarInit(&sFull[i], 1);
             mbarInit(&pReady[i], kSoftmaxThreads);
         }
         mbarInit(&pFree[0], 1);
         mbarInit(&pFree[1], 1);
+        mbarInit(qFull, 1);
+        mbarInit(qFree, 1);
         mbarInit(oFull, 1);
+        mbarInit(oFree, kSoftmaxThreads);
         *abortFlag = 0;
         fenceBarrierInit();
         prefetchTensorMap(&mapQkv);
     }
     if (warp == 1)
-        tmemAlloc(tmemSlot, tmemCols);
+        tmemAlloc(tmemSlot, kTmemCols);
     tcFenceBefore();
     __syncthreads();
     tcFenceAfter();
@@ -217,7 +234,6 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     {
         if (lane == 0)
         {
-            int32_t const rowQ = args.fixedLayout ? q0 : rowBase + q0;
             int32_t const rowK = args.fixedLayout ? 0 : rowBase;
             // linear: (column of the token row, batch, row). interleaved: (0, row, 32-channel group of [3][N][2])
             auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
@@ -226,18 +242,24 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 else
                     tmaLoad3d(dst, &mapQkv, bar, (head * 3 + which) * kHeadSize, args.fixedLayout ? b : 0, row);
             };
-            mbarArriveExpectTx(&qkFull[0], 2 * L::kTileBytes);
-            load(sQ, &qkFull[0], 0, rowQ);
-            load(sK, &qkFull[0], 1, rowK);
-            for (int j = 1; j < nb; ++j)
+            mbarArriveExpectTx(qFull, L::kTileBytes);
+            load(sQ, qFull, 0, rowK);
+            for (int j = 0; j < nb; ++j)
             {
-                mbarArriveExpectTx(&qkFull[j], L::kTileBytes);
-                load(sK + j * L::kTileBytes, &qkFull[j], 1, rowK + j * kKeyBlock);
+                mbarArriveExpectTx(&kFull[j], L::kTileBytes);
+                load(sK + j * L::kTileBytes, &kFull[j], 1, rowK + j * kKeyBlock);
             }
             for (int j = 0; j < nb; ++j)
             {
                 mbarArriveExpectTx(&vFull[j], L::kTileBytes);
                 load(sV + j * L::kTileBytes, &vFull[j], 2, rowK + j * kKeyBlock);
+            }
+            for (int t = 1; t < nq; ++t)
+            {
+                if (!mbarWait(qFree, (t - 1) & 1, abortFlag, kWaitStageFree))
+                    break;
+                mbarArriveExpectTx(qFull, L::kTileBytes);
+                load(sQ, qFull, 0, rowK + t * kQTile);
             }
         }
     }
@@ -247,12 +269,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         {
             bool ok = true;
             uint32_t const qAddr = smemAddr(sQ);
-            for (int j = 0; j < nb && ok; ++j)
-            {
-                ok = mbarWait(&qkFull[j], 0, abortFlag, kWaitTmaFull);
-                if (!ok)
-                    break;
-                tcFenceAfter();
+            // scores of key block j for the query tile whose Q is in shared memory
+            auto issueScores = [&](int j) {
                 uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k)
@@ -266,58 +284,113 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         mmaF16(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
                 }
                 tcCommit(&sFull[j]);
-            }
+                if (j == nb - 1)
+                    tcCommit(qFree);
+            };
+            ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
             for (int j = 0; j < nb && ok; ++j)
             {
-                ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull) && mbarWait(&pReady[j], 0, abortFlag, kWaitSoftmax);
-                if (!ok)
-                    break;
-                tcFenceAfter();
-                uint32_t const pAddr = smemAddr(sP + (j & 1) * L::kPBytes);
-                uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
-#pragma unroll
-                for (int k = 0; k < kPvMmas; ++k)
+                ok = mbarWait(&kFull[j], 0, abortFlag, kWaitTmaFull);
+                if (ok)
                 {
-                    // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
-                    uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
-                    uint64_t const aDesc = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
-                    // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
-                    // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
-                    uint64_t const bDesc = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
-                                              : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
-                    if (kInt8)
-                        mmaI8(tmemBase, aDesc, bDesc, kIdescPv, (j | k) != 0);
-                    else
-                        mmaF16(tmemBase, aDesc, bDesc, kIdescPv, (j | k) != 0);
+                    tcFenceAfter();
+                    issueScores(j);
                 }
-                if (j + 1 < nb)
-                    tcCommit(&pFree[j & 1]);
-                else
-                    tcCommit(oFull);
             }
+            uint32_t pUse[2] = {0, 0};
+            for (int t = 0; t < nq && ok; ++t)
+            {
+                bool const more = t + 1 < nq;
+                for (int j = 0; j < nb && ok; ++j)
+                {
+                    ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull)
+                        && mbarWait(&pReady[j], t & 1, abortFlag, kWaitSoftmax);
+                    if (ok && j == 0 && t > 0) // the previous tile's context must have been read out
+                        ok = mbarWait(oFree, (t - 1) & 1, abortFlag, kWaitAccFree);
+                    if (!ok)
+                        break;
+                    tcFenceAfter();
+                    int const slot = j & 1;
+                    uint32_t const pAddr = smemAddr(sP + slot * L::kPBytes);
+                    uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
+#pragma unroll
+                    for (int k = 0; k < kPvMmas; ++k)
+                    {
+                        // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
+                        uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
+                        uint64_t const aDesc = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
+                        // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
+                        // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
+                        uint64_t const bDesc = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
+                                                  : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
+                        if (kInt8)
+                            mmaI8(tmemBase + oCol, aDesc, bDesc, kIdescPv, (j | k) != 0);
+                        else
+                            mmaF16(tmemBase + oCol, aDesc, bDesc, kIdescPv, (j | k) != 0);
+                    }
+                    tcCommit(&pFree[slot]);
+                    ++pUse[slot];
+                    if (j == nb - 1)
+                        tcCommit(oFull);
+                    // scores of the next tile for this key block: its columns were released by pReady[j]
+                    if (more && !oAliasesScores)
+                    {
+                        if (j == 0)
+                            ok = mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
+                        if (ok)
+                        {
+                            tcFenceAfter();
+                            issueScores(j);
+                        }
+                    }
+                }
+                if (ok && more && oAliasesScores)
+                {
+                    // the context accumulator occupies score columns: wait until the epilogue has read it
+                    ok = mbarWait(oFree, t & 1, abortFlag, kWaitAccFree) && mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
+                    if (ok)
+                    {
+                        tcFenceAfter();
+                        for (int j = 0; j < nb; ++j)
+                            issueScores(j);
+                    }
+                }
+            }
+            (void) pUse;
         }
     }
     else
     {
-        int const quad = warp & 3;
-        int const half = (warp - 2) >> 2; // which 64 of every 128 key columns this thread owns
+        int const quad = warp & 3;        // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
+        int const sub = (warp - 2) >> 2;  // which 32 of every 128 key columns this thread owns (4 warps per quadrant)
         int const r = quad * 32 + lane;   // query row inside the tile = TMEM lane
         uint32_t const tRow = tmemBase + (static_cast<uint32_t>(quad * 32) << 16);
         float const sl2 = args.scaleBmm1 * 1.4426950408889634f;
         bool ok = true;
+        uint32_t pUse[2] = {0, 0};        // how often each P ring slot has been filled so far
+        // Before refilling a P slot its previous contents must have been consumed by the PV product.
+        auto acquireP = [&](int slot) -> bool {
+            bool good = true;
+            if (pUse[slot] > 0)
+                good = mbarWait(&pFree[slot], (pUse[slot] - 1) & 1, abortFlag, kWaitSoftmax);
+            ++pUse[slot];
+            return good;
+        };
 
-        // ---- pass A: row maximum ----
-        float mx = -INFINITY;
-        for (int j = 0; j < nb && ok; ++j)
+        for (int t = 0; t < nq; ++t)
         {
-            ok = mbarWait(&sFull[j], 0, abortFlag, kWaitSoftmax);
-            if (!ok)
-                break;
-            tcFenceAfter();
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
+            int const q0 = t * kQTile;
+            uint32_t const tilePhase = t & 1;
+
+            // ---- pass A: row maximum ----
+            float mx = -INFINITY;
+            for (int j = 0; j < nb && ok; ++j)
             {
-                int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                ok = mbarWait(&sFull[j], tilePhase, abortFlag, kWaitSoftmax);
+                if (!ok)
+                    break;
+                tcFenceAfter();
+                int const col0 = j * kKeyBlock + sub * 32;
                 uint32_t x[32];
                 tmemLoad32(tRow + col0, x);
                 tmemLoadWait();
@@ -330,27 +403,22 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         mx = fmaxf(mx, v);
                 }
             }
-        }
-        rowRed[half * kQTile + r] = mx;
-        softmaxBarrier();
-        mx = fmaxf(rowRed[r], rowRed[kQTile + r]);
-        float const mOff = mx * sl2;
+            rowRed[sub * kQTile + r] = mx;
+            softmaxBarrier();
+            mx = fmaxf(fmaxf(rowRed[r], rowRed[kQTile + r]), fmaxf(rowRed[2 * kQTile + r], rowRed[3 * kQTile + r]));
+            float const mOff = mx * sl2;
 
-        // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
-        float sum = 0.f;
-        for (int j = 0; j < nb && ok; ++j)
-        {
-            if (!kInt8 && j >= 2)
+            // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
+            float sum = 0.f;
+            for (int j = 0; j < nb && ok; ++j)
             {
-                ok = mbarWait(&pFree[j & 1], ((j >> 1) - 1) & 1, abortFlag, kWaitSoftmax);
-                if (!ok)
-                    break;
-            }
-            uint8_t* pRow = sP + (j & 1) * L::kPBytes + half * (kQTile * 128) + r * 128;
-#pragma unroll
-            for (int c = 0; c < 2; ++c)
-            {
-                int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                if (!kInt8)
+                {
+                    ok = acquireP(j & 1);
+                    if (!ok)
+                        break;
+                }
+                int const col0 = j * kKeyBlock + sub * 32;
                 uint32_t x[32];
                 tmemLoad32(tRow + col0, x);
                 tmemLoadWait();
@@ -375,6 +443,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 }
                 else
                 {
+                    // FP16 P block = two [128 rows][64 keys] tiles of 128-byte rows; this thread owns 4 chunks of one row
+                    uint8_t* pRow = sP + (j & 1) * L::kPBytes + (sub >> 1) * (kQTile * 128) + r * 128;
 #pragma unroll
                     for (int g = 0; g < 4; ++g)
                     {
@@ -382,42 +452,32 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
 #pragma unroll
                         for (int i = 0; i < 8; ++i)
                             f[i] = p[g * 8 + i];
-                        int const chunk = c * 4 + g; // 16-byte chunk inside the 128-byte row of this 64-key tile
+                        int const chunk = (sub & 1) * 4 + g;
                         *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
                     }
+                    fenceProxyAsync();
+                    tcFenceBefore();
+                    mbarArrive(&pReady[j]);
                 }
             }
-            if (!kInt8)
-            {
-                fenceProxyAsync();
-                tcFenceBefore();
-                mbarArrive(&pReady[j]);
-            }
-        }
-        if (kInt8)
-            tmemStoreWait();
-        rowRed[2 * kQTile + half * kQTile + r] = sum;
-        softmaxBarrier();
-        sum = rowRed[2 * kQTile + r] + rowRed[3 * kQTile + r];
-        float const inv = 1.f / sum;
+            if (kInt8)
+                tmemStoreWait();
+            rowRed[4 * kQTile + sub * kQTile + r] = sum;
+            softmaxBarrier();
+            sum = (rowRed[4 * kQTile + r] + rowRed[5 * kQTile + r]) + (rowRed[6 * kQTile + r] + rowRed[7 * kQTile + r]);
+            float const inv = 1.f / sum;
 
-        if (kInt8)
-        {
-            // ---- pass C (INT8): P_q = sat8(rni(p / sum * scale_softmax)) ----
-            float const pq = inv * args.scaleSoftmax;
-            for (int j = 0; j < nb && ok; ++j)
+            if (kInt8)
             {
-                if (j >= 2)
+                // ---- pass C (INT8): P_q = sat8(rni(p / sum * scale_softmax)) ----
+                float const pq = inv * args.scaleSoftmax;
+                for (int j = 0; j < nb && ok; ++j)
                 {
-                    ok = mbarWait(&pFree[j & 1], ((j >> 1) - 1) & 1, abortFlag, kWaitSoftmax);
+                    ok = acquireP(j & 1);
                     if (!ok)
                         break;
-                }
-                uint8_t* pRow = sP + (j & 1) * L::kPBytes + r * 128;
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                {
-                    int const col0 = j * kKeyBlock + half * 64 + c * 32;
+                    uint8_t* pRow = sP + (j & 1) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
+                    int const col0 = j * kKeyBlock + sub * 32;
                     uint32_t x[32];
                     tmemLoad32(tRow + col0, x);
                     tmemLoadWait();
@@ -428,59 +488,56 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-                            w[i] = packChar4(__uint_as_float(x[g * 16 + 4 * i]) * pq,
-                                __uint_as_float(x[g * 16 + 4 * i + 1]) * pq, __uint_as_float(x[g * 16 + 4 * i + 2]) * pq,
-                                __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
-                        int const chunk = half * 4 + c * 2 + g; // 16 keys per 16-byte chunk, 128 keys per row
+                            w[i] = packChar4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
+                                __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                        int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
                         *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
                     }
+                    fenceProxyAsync();
+                    tcFenceBefore();
+                    mbarArrive(&pReady[j]);
                 }
-                fenceProxyAsync();
-                tcFenceBefore();
-                mbarArrive(&pReady[j]);
             }
-        }
 
-        // ---- epilogue: normalise / requantise the context row ----
-        if (ok)
-            ok = mbarWait(oFull, 0, abortFlag, kWaitAccFull);
-        if (ok)
-        {
-            tcFenceAfter();
-            uint32_t x[32];
-            tmemLoad32(tRow + half * 32, x);
-            tmemLoadWait();
-            int const q = q0 + r;
-            if (q < rows)
+            // ---- epilogue: normalise / requantise 16 of the 64 context values of the row ----
+            if (ok)
+                ok = mbarWait(oFull, tilePhase, abortFlag, kWaitAccFull);
+            if (ok)
             {
-                T* dst = IL ? outPtrIl(q, half) : outRow(q) + half * 32;
-                if (kInt8)
+                tcFenceAfter();
+                uint32_t x[16];
+                tmemLoad16(tRow + oCol + sub * 16, x);
+                tmemLoadWait();
+                tcFenceBefore();
+                mbarArrive(oFree);
+                int const q = q0 + r;
+                if (q < rows)
                 {
-                    float const s2 = args.scaleBmm2;
-#pragma unroll
-                    for (int g = 0; g < 2; ++g)
+                    T* dst = IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16;
+                    if (kInt8)
                     {
+                        float const s2 = args.scaleBmm2;
                         uint4 o;
                         uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
                         for (int i = 0; i < 4; ++i)
-                            w[i] = packChar4(static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 1])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 2])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[g * 16 + 4 * i + 3])) * s2);
-                        reinterpret_cast<uint4*>(dst)[g] = o;
+                            w[i] = packChar4(static_cast<float>(static_cast<int32_t>(x[4 * i])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[4 * i + 1])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[4 * i + 2])) * s2,
+                                static_cast<float>(static_cast<int32_t>(x[4 * i + 3])) * s2);
+                        *reinterpret_cast<uint4*>(dst) = o;
                     }
-                }
-                else
-                {
-#pragma unroll
-                    for (int g = 0; g < 4; ++g)
+                    else
                     {
-                        float f[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            f[i] = __uint_as_float(x[g * 8 + i]) * inv;
-                        reinterpret_cast<uint4*>(dst)[g] = packHalf8(f);
+                        for (int g = 0; g < 2; ++g)
+                        {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                f[i] = __uint_as_float(x[g * 8 + i]) * inv;
+                            reinterpret_cast<uint4*>(dst)[g] = packHalf8(f);
+                        }
                     }
                 }
             }
@@ -503,7 +560,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     {
         __syncwarp();
         tcFenceAfter();
-        tmemFree(tmemBase, tmemCols);
+        tmemFree(tmemBase, kTmemCols);
     }
 }
 
@@ -546,7 +603,7 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     MhaArgs args{p.B, p.S, p.num_heads, p.total, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
         p.scale_softmax, p.scale_bmm2, p.status_word};
-    dim3 const grid((p.S + kQTile - 1) / kQTile, p.num_heads, p.B);
+    dim3 const grid(p.num_heads, p.B);
     kernel<<<grid, kMhaThreads, smem, stream>>>(map, args);
     return checkLaunch("mhaTcgen05Kernel");
 }
