@@ -117,6 +117,43 @@ __device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&
     }
 }
 
+// alpha / bias / activation / quantise for 32 accumulator columns of one row, then 128-bit stores.
+template <bool kInt8, typename Out>
+__device__ __forceinline__ void fcEpilogueChunk(uint32_t const (&r)[32], FcArgs const& args, Out* C, int64_t row, int64_t col,
+    int validCols)
+{
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+    {
+        float const a = kInt8 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
+        v[j] = a * args.alpha;
+    }
+    if (args.bias)
+    {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+        {
+            if (j < validCols)
+            {
+                float4 const b = __ldg(reinterpret_cast<float4 const*>(args.bias + col + j));
+                v[j] += b.x;
+                v[j + 1] += b.y;
+                v[j + 2] += b.z;
+                v[j + 3] += b.w;
+            }
+        }
+    }
+    if (args.act == BERT_B200_ACT_GELU_ERF)
+    {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            v[j] = geluErf(v[j]);
+    }
+    if (row < args.M)
+        storeChunk32<Out>(C + row * args.ldc + col, v, args.outScale, validCols);
+}
+
 template <typename In, int BLOCK_N, typename Out>
 __global__ void __launch_bounds__(kFcThreads, 1)
     fcTcgen05Kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, FcArgs const args)
@@ -290,36 +327,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
                 int const validCols = static_cast<int>(args.N - col < 32 ? args.N - col : 32);
                 if (validCols <= 0)
                     continue; // warp-uniform
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                {
-                    float const a = kInt8 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
-                    v[j] = a * args.alpha;
-                }
-                if (args.bias)
-                {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                    {
-                        if (j < validCols)
-                        {
-                            float4 const b = __ldg(reinterpret_cast<float4 const*>(args.bias + col + j));
-                            v[j] += b.x;
-                            v[j + 1] += b.y;
-                            v[j + 2] += b.z;
-                            v[j + 3] += b.w;
-                        }
-                    }
-                }
-                if (args.act == BERT_B200_ACT_GELU_ERF)
-                {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        v[j] = geluErf(v[j]);
-                }
-                if (row < args.M)
-                    storeChunk32<Out>(C + row * args.ldc + col, v, args.outScale, validCols);
+                fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
             }
             tcFenceBefore();
             mbarArrive(&accEmpty[acc]);
@@ -383,6 +391,275 @@ int32_t launchFc(bert_b200_fc_params const& p, cudaStream_t stream)
     return checkLaunch("fcTcgen05Kernel");
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Two-CTA variant: a cluster of two CTAs (neighbouring SMs) computes one 256 x BLOCK_N tile with
+// tcgen05.mma.cta_group::2. Each CTA loads its own 128 rows of A and its own BLOCK_N/2 rows of Wt, so a pair
+// moves (256 + BLOCK_N) rows per k-block instead of 2 x (128 + BLOCK_N): the shared-memory fill bandwidth per SM,
+// which bounds the one-CTA kernel, drops by a third and the ring gets deeper (6-8 stages).
+//   Leader (cluster rank 0): its MMA lane issues every MMA; its "full" barriers collect the TMA bytes of both
+//   CTAs; its "accEmpty" barriers collect the epilogue arrivals of both CTAs. tcgen05.commit multicasts the
+//   "stage free" and "accumulator ready" arrivals to both CTAs.
+// ------------------------------------------------------------------------------------------------
+template <int BLOCK_N>
+struct FcPairSmem
+{
+    static constexpr int kABytes = kBlockM * kRowBytes;            // this CTA's 128 rows of A
+    static constexpr int kBBytes = (BLOCK_N / 2) * kRowBytes;      // this CTA's half of the Wt rows
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStages = BLOCK_N == 256 ? 6 : 8;
+    static constexpr int kBarrierOff = kStages * kStageBytes;
+    static constexpr int kTotal = kBarrierOff + (2 * kStages + 4) * 8 + 16;
+    static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <typename In, int BLOCK_N, typename Out>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFcThreads, 1)
+    fcTcgen05PairKernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, FcArgs const args)
+{
+    using L = FcPairSmem<BLOCK_N>;
+    constexpr bool kInt8 = sizeof(In) == 1;
+    constexpr int kBlockK = kRowBytes / sizeof(In);
+    constexpr int kUmmaKBytes = 32;
+    constexpr int kPairM = 2 * kBlockM;
+    constexpr uint32_t kIdesc
+        = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, static_cast<uint32_t>(kPairM), static_cast<uint32_t>(BLOCK_N));
+
+    extern __shared__ uint8_t smemRaw[];
+    // the dynamic shared memory window starts at the same offset in both CTAs, so this rounding agrees too
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sA = smem;
+    uint8_t* sB = smem + L::kStages * L::kABytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::kBarrierOff);
+    uint64_t* empty = full + L::kStages;
+    uint64_t* accFull = empty + L::kStages;
+    uint64_t* accEmpty = accFull + 2;
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(accEmpty + 2);
+    volatile uint32_t* abortFlag = tmemSlot + 1;
+
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+    uint32_t const rank = clusterCtaRank();
+    bool const leader = rank == 0;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < L::kStages; ++i)
+        {
+            mbarInit(&full[i], 1);  // the leader's producer arrives (with the byte count of both CTAs)
+            mbarInit(&empty[i], 1); // one multicast commit from the leader
+        }
+        for (int i = 0; i < 2; ++i)
+        {
+            mbarInit(&accFull[i], 1);
+            mbarInit(&accEmpty[i], 2 * kEpilogueThreads); // epilogue threads of both CTAs (used in the leader only)
+        }
+        *abortFlag = 0;
+        fenceBarrierInit();
+        prefetchTensorMap(&mapA);
+        prefetchTensorMap(&mapB);
+    }
+    if (warp == 1)
+        tmemAllocPair(tmemSlot, kTmemCols);
+    tcFenceBefore();
+    __syncthreads();
+    clusterSync(); // both CTAs' barriers are initialised before any remote arrival or TMA signal
+    tcFenceAfter();
+    uint32_t const tmemBase = *tmemSlot;
+
+    int64_t const mBlocks = (args.M + kPairM - 1) / kPairM;
+    int64_t const nBlocks = (args.N + BLOCK_N - 1) / BLOCK_N;
+    int64_t const numTiles = mBlocks * nBlocks;
+    int const kBlocks = static_cast<int>((args.K + kBlockK - 1) / kBlockK);
+    int64_t const firstTile = blockIdx.x / 2;
+    int64_t const tileStride = gridDim.x / 2;
+
+    if (warp == 0)
+    {
+        if (lane == 0)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int64_t tile = firstTile; tile < numTiles && ok; tile += tileStride)
+            {
+                int32_t const m0 = static_cast<int32_t>(tile / nBlocks) * kPairM + static_cast<int32_t>(rank) * kBlockM;
+                int32_t const n0 = static_cast<int32_t>(tile % nBlocks) * BLOCK_N + static_cast<int32_t>(rank) * (BLOCK_N / 2);
+                for (int kb = 0; kb < kBlocks; ++kb)
+                {
+                    if (!mbarWait(&empty[stage], phase ^ 1u, abortFlag, kWaitStageFree))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    if (leader)
+                        mbarArriveExpectTx(&full[stage], 2 * L::kStageBytes);
+                    uint32_t const fullLeader = mapaShared(&full[stage], 0);
+                    tmaLoad2dPair(sA + stage * L::kABytes, &mapA, fullLeader, kb * kBlockK, m0);
+                    tmaLoad2dPair(sB + stage * L::kBBytes, &mapB, fullLeader, kb * kBlockK, n0);
+                    if (++stage == L::kStages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            // Tail: every stage released, i.e. no commit arrival is still on its way to this CTA.
+            for (int i = 0; i < L::kStages && ok; ++i)
+            {
+                ok = mbarWait(&empty[stage], phase ^ 1u, abortFlag, kWaitStageFree);
+                if (++stage == L::kStages)
+                {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    }
+    else if (warp == 1)
+    {
+        if (lane == 0 && leader)
+        {
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t accPhase = 0;
+            bool ok = true;
+            for (int64_t tile = firstTile; tile < numTiles && ok; tile += tileStride)
+            {
+                if (!mbarWait(&accEmpty[acc], accPhase ^ 1u, abortFlag, kWaitAccFree))
+                    break;
+                tcFenceAfter();
+                uint32_t const dTmem = tmemBase + static_cast<uint32_t>(acc * BLOCK_N);
+                for (int kb = 0; kb < kBlocks; ++kb)
+                {
+                    if (!mbarWait(&full[stage], phase, abortFlag, kWaitTmaFull))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tcFenceAfter();
+                    uint32_t const aBase = smemAddr(sA + stage * L::kABytes);
+                    uint32_t const bBase = smemAddr(sB + stage * L::kBBytes);
+#pragma unroll
+                    for (int k = 0; k < kRowBytes / kUmmaKBytes; ++k)
+                    {
+                        uint64_t const aDesc = makeSmemDesc(aBase + k * kUmmaKBytes, 16, 1024, kSwizzle128B);
+                        uint64_t const bDesc = makeSmemDesc(bBase + k * kUmmaKBytes, 16, 1024, kSwizzle128B);
+                        if (kInt8)
+                            mmaI8Pair(dTmem, aDesc, bDesc, kIdesc, (kb | k) != 0);
+                        else
+                            mmaF16Pair(dTmem, aDesc, bDesc, kIdesc, (kb | k) != 0);
+                    }
+                    tcCommitPair(&empty[stage], 3);
+                    if (++stage == L::kStages)
+                    {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok)
+                    break;
+                tcCommitPair(&accFull[acc], 3);
+                acc ^= 1;
+                if (acc == 0)
+                    accPhase ^= 1u;
+            }
+        }
+    }
+    else
+    {
+        int const quad = warp & 3;
+        int const colHalf = (warp - 2) >> 2;
+        int acc = 0;
+        uint32_t accPhase = 0;
+        Out* const C = static_cast<Out*>(args.C);
+        for (int64_t tile = firstTile; tile < numTiles; tile += tileStride)
+        {
+            int64_t const m0 = (tile / nBlocks) * kPairM + static_cast<int64_t>(rank) * kBlockM;
+            int64_t const n0 = (tile % nBlocks) * BLOCK_N;
+            if (!mbarWait(&accFull[acc], accPhase, abortFlag, kWaitAccFull))
+                break;
+            tcFenceAfter();
+            int64_t const row = m0 + quad * 32 + lane;
+            uint32_t const taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
+#pragma unroll 1
+            for (int cc = 0; cc < BLOCK_N / 64; ++cc)
+            {
+                int const c = (cc >> 1) * 4 + colHalf * 2 + (cc & 1);
+                uint32_t r[32];
+                tmemLoad32(taddr + c * 32, r);
+                tmemLoadWait();
+                int64_t const col = n0 + c * 32;
+                int const validCols = static_cast<int>(args.N - col < 32 ? args.N - col : 32);
+                if (validCols <= 0)
+                    continue;
+                fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
+            }
+            tcFenceBefore();
+            mbarArriveCluster(mapaShared(&accEmpty[acc], 0)); // the leader's barrier counts both CTAs
+            acc ^= 1;
+            if (acc == 0)
+                accPhase ^= 1u;
+        }
+    }
+
+    __syncthreads();
+    uint32_t const aborted = *abortFlag;
+    if (aborted != 0)
+    {
+        uint64_t const t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull)
+            __nanosleep(1000);
+        if (threadIdx.x == 0 && args.statusWord)
+            atomicMax(args.statusWord, aborted);
+        __syncthreads();
+    }
+    tcFenceBefore();
+    clusterSync(); // the peer no longer signals barriers of, or reads operands from, this CTA's shared memory
+    if (warp == 1)
+    {
+        __syncwarp();
+        tcFenceAfter();
+        tmemFreePair(tmemBase, kTmemCols);
+    }
+}
+
+template <typename In, int BLOCK_N, typename Out>
+int32_t launchFcPair(bert_b200_fc_params const& p, cudaStream_t stream)
+{
+    using L = FcPairSmem<BLOCK_N>;
+    constexpr int kBlockK = kRowBytes / sizeof(In);
+    CUtensorMapDataType const dt = sizeof(In) == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap mapA, mapB;
+    {
+        uint64_t const dims[2] = {static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.m)};
+        uint64_t const strides[1] = {static_cast<uint64_t>(p.lda) * sizeof(In)};
+        uint32_t const box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(kBlockM)};
+        int32_t const st = makeTensorMap(&mapA, dt, 2, p.a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    {
+        uint64_t const dims[2] = {static_cast<uint64_t>(p.k), static_cast<uint64_t>(p.n)};
+        uint64_t const strides[1] = {static_cast<uint64_t>(p.k) * sizeof(In)};
+        uint32_t const box[2] = {static_cast<uint32_t>(kBlockK), static_cast<uint32_t>(BLOCK_N / 2)};
+        int32_t const st = makeTensorMap(&mapB, dt, 2, p.wt, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    auto kernel = fcTcgen05PairKernel<In, BLOCK_N, Out>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "fc: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    int64_t const tiles = ((p.m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.n + BLOCK_N - 1) / BLOCK_N);
+    int64_t const pairs = smCount() / 2;
+    int const grid = static_cast<int>(2 * (tiles < pairs ? tiles : pairs));
+    FcArgs args{p.m, p.n, p.k, p.c, p.ldc, p.bias, p.activation, p.alpha, p.out_scale, p.status_word};
+    kernel<<<grid, kFcThreads, L::kDynamic, stream>>>(mapA, mapB, args);
+    return checkLaunch("fcTcgen05PairKernel");
+}
+
 // Tiles of 128 x BLOCK_N over the SMs: pick the BLOCK_N that wastes less of the last wave.
 int pickBlockN(int64_t m, int64_t n)
 {
@@ -394,6 +671,20 @@ int pickBlockN(int64_t m, int64_t n)
         int64_t const waves = (tiles + sms - 1) / sms;
         // time ~ waves * tile work; 128-wide tiles run the tensor pipe a little less efficiently
         return static_cast<double>(waves) * bn * (bn == 128 ? 1.06 : 1.0);
+    };
+    return cost(128) < cost(256) ? 128 : 256;
+}
+
+// Same for 256 x BLOCK_N pair tiles over the SM pairs.
+int pickBlockNPair(int64_t m, int64_t n)
+{
+    if (n <= 128)
+        return 128;
+    int const pairs = smCount() / 2;
+    auto cost = [&](int bn) {
+        int64_t const tiles = ((m + 2 * kBlockM - 1) / (2 * kBlockM)) * ((n + bn - 1) / bn);
+        int64_t const waves = (tiles + pairs - 1) / pairs;
+        return static_cast<double>(waves) * bn * (bn == 128 ? 1.15 : 1.0);
     };
     return cost(128) < cost(256) ? 128 : 256;
 }
@@ -472,14 +763,22 @@ extern "C" int32_t bert_b200_fc(bert_b200_fc_params const* params, void* stream)
     B200_REQUIRE(!p.bias || aligned16(p.bias), "fc: bias must be 16-byte aligned");
     int const outElem = p.out_type_id == BERT_B200_FP16 ? 2 : 1;
     B200_REQUIRE((p.ldc * outElem) % 16 == 0, "fc: row bytes of C must be a multiple of 16");
-    int const bn = pickBlockN(p.m, p.n);
+    // More than one 128-row block: two-CTA tiles of 256 rows; a single block would leave the peer CTA idle.
+    bool const pair = p.m > kBlockM;
+    int const bn = pair ? pickBlockNPair(p.m, p.n) : pickBlockN(p.m, p.n);
+#define B200_FC_DISPATCH(IN, OUT)                                                                                      \
+    return pair ? (bn == 128 ? launchFcPair<IN, 128, OUT>(p, s) : launchFcPair<IN, 256, OUT>(p, s))                     \
+                : (bn == 128 ? launchFc<IN, 128, OUT>(p, s) : launchFc<IN, 256, OUT>(p, s))
     if (p.type_id == BERT_B200_FP16)
     {
         B200_REQUIRE(p.out_type_id == BERT_B200_FP16, "fc: FP16 input needs FP16 output");
-        return bn == 128 ? launchFc<__half, 128, __half>(p, s) : launchFc<__half, 256, __half>(p, s);
+        B200_FC_DISPATCH(__half, __half);
     }
     if (p.out_type_id == BERT_B200_INT8)
-        return bn == 128 ? launchFc<int8_t, 128, int8_t>(p, s) : launchFc<int8_t, 256, int8_t>(p, s);
+    {
+        B200_FC_DISPATCH(int8_t, int8_t);
+    }
     B200_REQUIRE(p.out_type_id == BERT_B200_FP16, "fc: INT8 input needs INT8 or FP16 output");
-    return bn == 128 ? launchFc<int8_t, 128, __half>(p, s) : launchFc<int8_t, 256, __half>(p, s);
+    B200_FC_DISPATCH(int8_t, __half);
+#undef B200_FC_DISPATCH
 }

@@ -227,6 +227,93 @@ __device__ __forceinline__ void tmemLoadWait()
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- two-CTA (cta_group::2) variants ---------------------------------------------------------
+// A cluster of two CTAs on neighbouring SMs issues one MMA of M = 256: each CTA supplies its own 128 rows of A and its
+// own half of the B rows from its own shared memory and keeps its own 128 accumulator rows in its own TMEM. Only
+// the even ("leader") CTA issues MMAs and commits. None of the loads below uses multicast.
+__device__ __forceinline__ uint32_t clusterCtaRank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void clusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t mapaShared(void const* localPtr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smemAddr(localPtr)), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+
+// Tile into this CTA's shared memory; the transaction bytes are counted on the mbarrier at `barClusterAddr`,
+// which may live in the peer CTA (the leader's "full" barrier collects both CTAs' loads).
+__device__ __forceinline__ void tmaLoad2dPair(void* dst, CUtensorMap const* map, uint32_t barClusterAddr, int32_t c0, int32_t c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+// Executed by the same warp index in both CTAs of the pair.
+__device__ __forceinline__ void tmemAllocPair(uint32_t* dst, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemAddr(dst)), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmemFreePair(uint32_t addr, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns) : "memory");
+}
+
+// One arrival on the mbarrier at the same shared-memory offset in every CTA of `ctaMask`, once all MMAs issued
+// so far have completed.
+__device__ __forceinline__ void tcCommitPair(uint64_t* bar, uint16_t ctaMask)
+{
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smemAddr(bar)),
+        "h"(ctaMask)
+        : "memory");
+}
+
+__device__ __forceinline__ void mmaF16Pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(dTmem),
+        "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+
+__device__ __forceinline__ void mmaI8Pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}" ::"r"(dTmem),
+        "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+
 // ---- descriptors ----------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64 bit): start address, leading / stride byte offsets (all >> 4),
 // descriptor version 1 (Blackwell) in bits 46-47 and the swizzle mode in bits 61-63.
