@@ -58,7 +58,7 @@ struct MhaSmem
     static constexpr int kRowBytes = kHeadSize * kElem;           // 128 (FP16) or 64 (INT8)
     static constexpr int kTileBytes = kQTile * kRowBytes;         // Q tile, one K block, one V block
     static constexpr int kPBytes = kQTile * kKeyBlock * kElem;    // one P block: 32 KB (FP16) or 16 KB (INT8)
-    // [ Q ][ K blocks ][ V blocks ][ P ring (2 blocks) ][ barriers, reduction scratch ]
+    // [ Q ][ K blocks ][ V blocks ][ P slots ][ barriers, reduction scratch ]
     static __host__ __device__ constexpr int kOffset()
     {
         return kTileBytes;
@@ -71,12 +71,17 @@ struct MhaSmem
     {
         return (1 + 2 * nb) * kTileBytes;
     }
+    // one P slot per key block up to three blocks; four blocks share two slots (shared memory is full then)
+    static __host__ __device__ constexpr int pSlots(int nb)
+    {
+        return nb <= 3 ? nb : 2;
+    }
     static __host__ __device__ constexpr int barrierOffset(int nb)
     {
-        return pOffset(nb) + 2 * kPBytes;
+        return pOffset(nb) + pSlots(nb) * kPBytes;
     }
-    // kFull[4] vFull[4] sFull[4] pReady[4] pFree[2] qFull qFree oFull oFree, tmem slot + abort flag, max / sum scratch
-    static constexpr int kBarrierBytes = (4 * kMaxBlocks + 6) * 8 + 16 + 8 * kQTile * 4;
+    // kFull[4] vFull[4] sFull[4] pReady[4] pFree[4] qFull qFree oFull oFree, tmem slot + abort flag, max / sum scratch
+    static constexpr int kBarrierBytes = (5 * kMaxBlocks + 4) * 8 + 16 + 8 * kQTile * 4;
     static __host__ __device__ constexpr int dynamicBytes(int nb)
     {
         return barrierOffset(nb) + kBarrierBytes + 1024;
@@ -88,6 +93,17 @@ __device__ __forceinline__ float ex2Approx(float x)
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Four non-negative values -> round-to-nearest-even integers saturated at 127, packed into one word.
+// Adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits (the FP32 adder rounds to nearest even,
+// like cvt.rni); the clamp at 127 is the saturation of the reference's conversion for scale_softmax > 127.
+__device__ __forceinline__ uint32_t packProb4(float a, float b, float c, float d)
+{
+    constexpr float kMagic = 12582912.f;
+    uint32_t const ua = __float_as_uint(fminf(a, 127.f) + kMagic), ub = __float_as_uint(fminf(b, 127.f) + kMagic);
+    uint32_t const uc = __float_as_uint(fminf(c, 127.f) + kMagic), ud = __float_as_uint(fminf(d, 127.f) + kMagic);
+    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ void softmaxBarrier()
@@ -189,14 +205,14 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     uint8_t* sQ = smem;                          // kTileBytes
     uint8_t* sK = smem + L::kOffset();           // nb x kTileBytes
     uint8_t* sV = smem + L::vOffset(nb);         // nb x kTileBytes
-    uint8_t* sP = smem + L::pOffset(nb);         // 2 x kPBytes
+    uint8_t* sP = smem + L::pOffset(nb);         // pSlots(nb) x kPBytes
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::barrierOffset(nb));
     uint64_t* kFull = bars;                      // [4] K_j landed
     uint64_t* vFull = bars + kMaxBlocks;         // [4] V_j landed
     uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete       (once per query tile)
     uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written, 512 arrivals        (once per query tile)
-    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [2] PV product consumed P ring slot
-    uint64_t* qFull = pFree + 2;                 // Q tile landed                        (once per query tile)
+    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [4] PV product consumed P slot
+    uint64_t* qFull = pFree + kMaxBlocks;        // Q tile landed                        (once per query tile)
     uint64_t* qFree = qFull + 1;                 // all score MMAs of the tile done: Q slot reusable
     uint64_t* oFull = qFree + 1;                 // context accumulator complete         (once per query tile)
     uint64_t* oFree = oFull + 1;                 // epilogue has read it, 512 arrivals   (once per query tile)
@@ -213,8 +229,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             mbarInit(&sFull[i], 1);
             mbarInit(&pReady[i], kSoftmaxThreads);
         }
-        mbarInit(&pFree[0], 1);
-        mbarInit(&pFree[1], 1);
+        for (int i = 0; i < kMaxBlocks; ++i)
+            mbarInit(&pFree[i], 1);
         mbarInit(qFull, 1);
         mbarInit(qFree, 1);
         mbarInit(oFull, 1);
@@ -268,79 +284,98 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         if (lane == 0)
         {
             bool ok = true;
-            uint32_t const qAddr = smemAddr(sQ);
+            // All operand descriptors are fixed for the life of the CTA: build them once, outside the issue loops.
+            uint64_t qDesc[kQkMmas], kDesc[kMaxBlocks][kQkMmas], pDesc[kMaxBlocks][kPvMmas], vDesc[kMaxBlocks][kPvMmas];
+#pragma unroll
+            for (int k = 0; k < kQkMmas; ++k)
+                qDesc[k] = makeSmemDesc(smemAddr(sQ) + (IL ? k * kSubTile : k * 32), 16, kAtomBytes, kSwz);
+#pragma unroll
+            for (int j = 0; j < kMaxBlocks; ++j)
+            {
+                uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
+                uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
+                uint32_t const pAddr = smemAddr(sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes);
+#pragma unroll
+                for (int k = 0; k < kQkMmas; ++k) // next 32 bytes of the head dimension
+                    kDesc[j][k] = makeSmemDesc(kAddr + (IL ? k * kSubTile : k * 32), 16, kAtomBytes, kSwz);
+#pragma unroll
+                for (int k = 0; k < kPvMmas; ++k)
+                {
+                    // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
+                    uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
+                    pDesc[j][k] = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
+                    // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
+                    // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
+                    vDesc[j][k] = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
+                                     : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
+                }
+            }
             // scores of key block j for the query tile whose Q is in shared memory
             auto issueScores = [&](int j) {
-                uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k)
                 {
-                    uint32_t const kOff = IL ? k * kSubTile : k * 32; // next 32 bytes of the head dimension
-                    uint64_t const aDesc = makeSmemDesc(qAddr + kOff, 16, kAtomBytes, kSwz);
-                    uint64_t const bDesc = makeSmemDesc(kAddr + kOff, 16, kAtomBytes, kSwz);
                     if (kInt8)
-                        mmaI8(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
+                        mmaI8(tmemBase + j * kKeyBlock, qDesc[k], kDesc[j][k], kIdescQk, k != 0);
                     else
-                        mmaF16(tmemBase + j * kKeyBlock, aDesc, bDesc, kIdescQk, k != 0);
+                        mmaF16(tmemBase + j * kKeyBlock, qDesc[k], kDesc[j][k], kIdescQk, k != 0);
                 }
                 tcCommit(&sFull[j]);
                 if (j == nb - 1)
                     tcCommit(qFree);
             };
             ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
-            for (int j = 0; j < nb && ok; ++j)
+#pragma unroll
+            for (int j = 0; j < kMaxBlocks; ++j)
             {
-                ok = mbarWait(&kFull[j], 0, abortFlag, kWaitTmaFull);
-                if (ok)
+                if (j < nb && ok)
                 {
-                    tcFenceAfter();
-                    issueScores(j);
+                    ok = mbarWait(&kFull[j], 0, abortFlag, kWaitTmaFull);
+                    if (ok)
+                    {
+                        tcFenceAfter();
+                        issueScores(j);
+                    }
                 }
             }
-            uint32_t pUse[2] = {0, 0};
             for (int t = 0; t < nq && ok; ++t)
             {
                 bool const more = t + 1 < nq;
-                for (int j = 0; j < nb && ok; ++j)
-                {
-                    ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull)
-                        && mbarWait(&pReady[j], t & 1, abortFlag, kWaitSoftmax);
-                    if (ok && j == 0 && t > 0) // the previous tile's context must have been read out
-                        ok = mbarWait(oFree, (t - 1) & 1, abortFlag, kWaitAccFree);
-                    if (!ok)
-                        break;
-                    tcFenceAfter();
-                    int const slot = j & 1;
-                    uint32_t const pAddr = smemAddr(sP + slot * L::kPBytes);
-                    uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
 #pragma unroll
-                    for (int k = 0; k < kPvMmas; ++k)
+                for (int j = 0; j < kMaxBlocks; ++j)
+                {
+                    if (j < nb && ok)
                     {
-                        // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
-                        uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
-                        uint64_t const aDesc = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
-                        // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
-                        // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
-                        uint64_t const bDesc = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
-                                                  : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
-                        if (kInt8)
-                            mmaI8(tmemBase + oCol, aDesc, bDesc, kIdescPv, (j | k) != 0);
-                        else
-                            mmaF16(tmemBase + oCol, aDesc, bDesc, kIdescPv, (j | k) != 0);
-                    }
-                    tcCommit(&pFree[slot]);
-                    ++pUse[slot];
-                    if (j == nb - 1)
-                        tcCommit(oFull);
-                    // scores of the next tile for this key block: its columns were released by pReady[j]
-                    if (more && !oAliasesScores)
-                    {
-                        if (j == 0)
-                            ok = mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
+                        if (t == 0)
+                            ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull);
+                        if (ok && j == 0 && t > 0) // the previous tile's context must have been read out
+                            ok = mbarWait(oFree, (t - 1) & 1, abortFlag, kWaitAccFree);
+                        ok = ok && mbarWait(&pReady[j], t & 1, abortFlag, kWaitSoftmax);
                         if (ok)
                         {
                             tcFenceAfter();
-                            issueScores(j);
+#pragma unroll
+                            for (int k = 0; k < kPvMmas; ++k)
+                            {
+                                if (kInt8)
+                                    mmaI8(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                                else
+                                    mmaF16(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                            }
+                            tcCommit(&pFree[nb <= 3 ? j : (j & 1)]);
+                            if (j == nb - 1)
+                                tcCommit(oFull);
+                            // scores of the next tile for this key block: its columns were released by pReady[j]
+                            if (more && !oAliasesScores)
+                            {
+                                if (j == 0)
+                                    ok = mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
+                                if (ok)
+                                {
+                                    tcFenceAfter();
+                                    issueScores(j);
+                                }
+                            }
                         }
                     }
                 }
@@ -351,12 +386,13 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     if (ok)
                     {
                         tcFenceAfter();
-                        for (int j = 0; j < nb; ++j)
-                            issueScores(j);
+#pragma unroll
+                        for (int j = 0; j < kMaxBlocks; ++j)
+                            if (j < nb)
+                                issueScores(j);
                     }
                 }
             }
-            (void) pUse;
         }
     }
     else
@@ -366,98 +402,163 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         int const r = quad * 32 + lane;   // query row inside the tile = TMEM lane
         uint32_t const tRow = tmemBase + (static_cast<uint32_t>(quad * 32) << 16);
         float const sl2 = args.scaleBmm1 * 1.4426950408889634f;
+        constexpr float kMagic = 12582912.f;       // 1.5 * 2^23: as_float(0x4B400000 + v) == kMagic + v for |v| < 2^22
+        constexpr uint32_t kMagicBits = 0x4B400000u;
         bool ok = true;
-        uint32_t pUse[2] = {0, 0};        // how often each P ring slot has been filled so far
-        // Before refilling a P slot its previous contents must have been consumed by the PV product.
-        auto acquireP = [&](int slot) -> bool {
-            bool good = true;
-            if (pUse[slot] > 0)
-                good = mbarWait(&pFree[slot], (pUse[slot] - 1) & 1, abortFlag, kWaitSoftmax);
-            ++pUse[slot];
-            return good;
+        auto colOf = [&](int j) { return j * kKeyBlock + sub * 32; };
+        // Before a P slot is refilled, the PV product that read its previous contents must have completed.
+        auto acquireP = [&](int t, int j) -> bool {
+            int const fill = nb <= 3 ? t : 2 * t + (j >> 1); // how often this slot has been filled before
+            return fill == 0 || mbarWait(&pFree[nb <= 3 ? j : (j & 1)], (fill - 1) & 1, abortFlag, kWaitSoftmax);
         };
+        // Reads 16 of the 64 context values of this row, normalises / requantises and stores them.
+        auto epilogue = [&](int t, float inv) {
+            if (ok)
+                ok = mbarWait(oFull, t & 1, abortFlag, kWaitAccFull);
+            if (!ok)
+                return;
+            tcFenceAfter();
+            uint32_t x[16];
+            tmemLoad16(tRow + oCol + sub * 16, x);
+            tmemLoadWait16(x);
+            tcFenceBefore();
+            mbarArrive(oFree);
+            int const q = t * kQTile + r;
+            if (q >= rows)
+                return;
+            T* dst = IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16;
+            if (kInt8)
+            {
+                float const s2 = args.scaleBmm2;
+                uint4 o;
+                uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    w[i] = packChar4(static_cast<float>(static_cast<int32_t>(x[4 * i])) * s2,
+                        static_cast<float>(static_cast<int32_t>(x[4 * i + 1])) * s2,
+                        static_cast<float>(static_cast<int32_t>(x[4 * i + 2])) * s2,
+                        static_cast<float>(static_cast<int32_t>(x[4 * i + 3])) * s2);
+                *reinterpret_cast<uint4*>(dst) = o;
+            }
+            else
+            {
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+                {
+                    float f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        f[i] = __uint_as_float(x[g * 8 + i]) * inv;
+                    reinterpret_cast<uint4*>(dst)[g] = packHalf8(f);
+                }
+            }
+        };
+
+        // The epilogue of tile t runs after pass A of tile t+1: the last PV product of tile t then completes under
+        // useful work instead of a stall. Not possible when the context accumulator shares columns with the scores.
+        bool const deferEpilogue = !oAliasesScores;
+        float invPrev = 0.f;
 
         for (int t = 0; t < nq; ++t)
         {
-            int const q0 = t * kQTile;
             uint32_t const tilePhase = t & 1;
+            uint32_t x[32];
 
-            // ---- pass A: row maximum ----
+            // ---- pass A: row maximum (INT8: integer maximum, no conversions) ----
             float mx = -INFINITY;
-            for (int j = 0; j < nb && ok; ++j)
-            {
-                ok = mbarWait(&sFull[j], tilePhase, abortFlag, kWaitSoftmax);
-                if (!ok)
-                    break;
-                tcFenceAfter();
-                int const col0 = j * kKeyBlock + sub * 32;
-                uint32_t x[32];
-                tmemLoad32(tRow + col0, x);
-                tmemLoadWait();
-                int const limit = len - col0;
+            int32_t mxi = INT32_MIN;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
+            for (int j = 0; j < kMaxBlocks; ++j)
+            {
+                if (j < nb)
                 {
-                    float const v = kInt8 ? static_cast<float>(static_cast<int32_t>(x[i])) : __uint_as_float(x[i]);
-                    if (i < limit)
-                        mx = fmaxf(mx, v);
+                    ok = ok && mbarWait(&sFull[j], tilePhase, abortFlag, kWaitSoftmax);
+                    tcFenceAfter();
+                    tmemLoad32(tRow + colOf(j), x);
+                    tmemLoadWait32(x);
+                    int const limit = len - colOf(j);
+                    if (limit >= 32)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                        {
+                            if (kInt8)
+                                mxi = max(mxi, static_cast<int32_t>(x[i]));
+                            else
+                                mx = fmaxf(mx, __uint_as_float(x[i]));
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                        {
+                            if (i < limit)
+                            {
+                                if (kInt8)
+                                    mxi = max(mxi, static_cast<int32_t>(x[i]));
+                                else
+                                    mx = fmaxf(mx, __uint_as_float(x[i]));
+                            }
+                        }
+                    }
                 }
             }
+            if (kInt8)
+                mx = mxi == INT32_MIN ? -INFINITY : static_cast<float>(mxi);
+            if (deferEpilogue && t > 0)
+                epilogue(t - 1, invPrev);
             rowRed[sub * kQTile + r] = mx;
             softmaxBarrier();
             mx = fmaxf(fmaxf(rowRed[r], rowRed[kQTile + r]), fmaxf(rowRed[2 * kQTile + r], rowRed[3 * kQTile + r]));
             float const mOff = mx * sl2;
+            float const mxMagic = kMagic + mx; // exact: both are integers below 2^24
 
             // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
             float sum = 0.f;
-            for (int j = 0; j < nb && ok; ++j)
-            {
-                if (!kInt8)
-                {
-                    ok = acquireP(j & 1);
-                    if (!ok)
-                        break;
-                }
-                int const col0 = j * kKeyBlock + sub * 32;
-                uint32_t x[32];
-                tmemLoad32(tRow + col0, x);
-                tmemLoadWait();
-                int const limit = len - col0;
-                float p[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
+            for (int j = 0; j < kMaxBlocks; ++j)
+            {
+                if (j < nb)
                 {
-                    // INT8: accumulators and their maximum are exact integers in FP32, so the difference is exact
-                    // and the exponent carries a single rounding; FP16: one fused multiply-add.
-                    float const e = kInt8 ? ex2Approx((static_cast<float>(static_cast<int32_t>(x[i])) - mx) * sl2)
-                                          : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
-                    p[i] = i < limit ? e : 0.f;
-                    sum += p[i];
-                }
-                if (kInt8)
-                {
+                    tmemLoad32(tRow + colOf(j), x);
+                    tmemLoadWait32(x);
+                    int const limit = len - colOf(j);
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
-                        x[i] = __float_as_uint(p[i]);
-                    tmemStore32(tRow + col0, x);
-                }
-                else
-                {
-                    // FP16 P block = two [128 rows][64 keys] tiles of 128-byte rows; this thread owns 4 chunks of one row
-                    uint8_t* pRow = sP + (j & 1) * L::kPBytes + (sub >> 1) * (kQTile * 128) + r * 128;
-#pragma unroll
-                    for (int g = 0; g < 4; ++g)
                     {
-                        float f[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            f[i] = p[g * 8 + i];
-                        int const chunk = (sub & 1) * 4 + g;
-                        *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
+                        // INT8: (acc - max) is formed exactly (integers through the 2^23 trick, no conversion unit),
+                        // so the exponent carries a single rounding; FP16: one fused multiply-add.
+                        float e = kInt8 ? ex2Approx((__uint_as_float(x[i] + kMagicBits) - mxMagic) * sl2)
+                                        : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
+                        if (limit < 32 && i >= limit)
+                            e = 0.f;
+                        sum += e;
+                        x[i] = __float_as_uint(e);
                     }
-                    fenceProxyAsync();
-                    tcFenceBefore();
-                    mbarArrive(&pReady[j]);
+                    if (kInt8)
+                    {
+                        tmemStore32(tRow + colOf(j), x);
+                    }
+                    else
+                    {
+                        ok = ok && acquireP(t, j);
+                        // FP16 P block = two [128 rows][64 keys] tiles of 128-byte rows; this thread owns 4 chunks of a row
+                        uint8_t* pRow = sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes + (sub >> 1) * (kQTile * 128) + r * 128;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g)
+                        {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                f[i] = __uint_as_float(x[g * 8 + i]);
+                            int const chunk = (sub & 1) * 4 + g;
+                            *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
+                        }
+                        fenceProxyAsync();
+                        tcFenceBefore();
+                        mbarArrive(&pReady[j]);
+                    }
                 }
             }
             if (kInt8)
@@ -469,79 +570,42 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
 
             if (kInt8)
             {
-                // ---- pass C (INT8): P_q = sat8(rni(p / sum * scale_softmax)) ----
+                // ---- pass C (INT8): P_q = rni(p / sum * scale_softmax) ----
                 float const pq = inv * args.scaleSoftmax;
-                for (int j = 0; j < nb && ok; ++j)
+#pragma unroll
+                for (int j = 0; j < kMaxBlocks; ++j)
                 {
-                    ok = acquireP(j & 1);
-                    if (!ok)
-                        break;
-                    uint8_t* pRow = sP + (j & 1) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
-                    int const col0 = j * kKeyBlock + sub * 32;
-                    uint32_t x[32];
-                    tmemLoad32(tRow + col0, x);
-                    tmemLoadWait();
-#pragma unroll
-                    for (int g = 0; g < 2; ++g)
+                    if (j < nb)
                     {
-                        uint4 o;
-                        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            w[i] = packChar4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
-                                __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
-                        int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
-                        *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
-                    }
-                    fenceProxyAsync();
-                    tcFenceBefore();
-                    mbarArrive(&pReady[j]);
-                }
-            }
-
-            // ---- epilogue: normalise / requantise 16 of the 64 context values of the row ----
-            if (ok)
-                ok = mbarWait(oFull, tilePhase, abortFlag, kWaitAccFull);
-            if (ok)
-            {
-                tcFenceAfter();
-                uint32_t x[16];
-                tmemLoad16(tRow + oCol + sub * 16, x);
-                tmemLoadWait();
-                tcFenceBefore();
-                mbarArrive(oFree);
-                int const q = q0 + r;
-                if (q < rows)
-                {
-                    T* dst = IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16;
-                    if (kInt8)
-                    {
-                        float const s2 = args.scaleBmm2;
-                        uint4 o;
-                        uint32_t* w = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            w[i] = packChar4(static_cast<float>(static_cast<int32_t>(x[4 * i])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[4 * i + 1])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[4 * i + 2])) * s2,
-                                static_cast<float>(static_cast<int32_t>(x[4 * i + 3])) * s2);
-                        *reinterpret_cast<uint4*>(dst) = o;
-                    }
-                    else
-                    {
+                        tmemLoad32(tRow + colOf(j), x);
+                        tmemLoadWait32(x);
+                        ok = ok && acquireP(t, j);
+                        uint8_t* pRow = sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
 #pragma unroll
                         for (int g = 0; g < 2; ++g)
                         {
-                            float f[8];
+                            uint4 o;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                f[i] = __uint_as_float(x[g * 8 + i]) * inv;
-                            reinterpret_cast<uint4*>(dst)[g] = packHalf8(f);
+                            for (int i = 0; i < 4; ++i)
+                                w[i] = packProb4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
+                                    __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                            int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
+                            *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
                         }
+                        fenceProxyAsync();
+                        tcFenceBefore();
+                        mbarArrive(&pReady[j]);
                     }
                 }
             }
+            if (deferEpilogue)
+                invPrev = inv;
+            else
+                epilogue(t, inv);
         }
+        if (deferEpilogue)
+            epilogue(nq - 1, invPrev);
         tcFenceBefore();
     }
 
