@@ -3,13 +3,13 @@
 // Replaces the cublasLtMatmul call of the reference FC plugin (plugin/fcPlugin/fcPlugin.cpp:551-610)
 // and the separate bias / GELU / quantise layers that follow it in the reference graph.
 //
-// Design (one persistent CTA per SM, 10 warps, warp specialised):
+// Design (one persistent CTA per SM, 18 warps, warp specialised):
 //   warp 0  : TMA producer - A[128 x 128B] and Wt[BLOCK_N x 128B] tiles, 128-byte swizzle, into a
 //             STAGES-deep shared-memory ring guarded by full/empty mbarriers.
 //   warp 1  : allocates all 512 TMEM columns, then one lane issues tcgen05.mma (UMMA 128 x BLOCK_N x 16
 //             for FP16 / x 32 for INT8) with the accumulator in TMEM; tcgen05.commit releases ring
 //             stages and publishes finished accumulators.
-//   warps 2-9: epilogue (two warps per TMEM lane quadrant, each owning alternate 64-column groups) -
+//   warps 2-17: epilogue (four warps per TMEM lane quadrant, each owning every fourth 32-column chunk) -
 //             tcgen05.ld the accumulator (double buffered, so tile i+1's main loop overlaps tile i's
 //             epilogue), scale / bias / erf-GELU / quantise, 128-bit stores.
 // Every mbarrier wait is bounded (see sm100.cuh); on expiry the CTA drains, frees TMEM and exits,
@@ -29,8 +29,9 @@ namespace
 constexpr int kBlockM = 128;
 constexpr int kRowBytes = 128; // one swizzle span = BLOCK_K * sizeof(In)
 constexpr int kTmemCols = 512;
-constexpr int kFcThreads = 320;
-constexpr int kEpilogueThreads = 256;
+constexpr int kEpilogueWarps = 16;
+constexpr int kEpilogueThreads = kEpilogueWarps * 32;
+constexpr int kFcThreads = 64 + kEpilogueThreads;
 
 struct FcArgs
 {
@@ -57,25 +58,60 @@ struct FcSmem
     static constexpr int kDynamic = kTotal + 1024; // slack for 1024-byte alignment of the ring
 };
 
-// erf-GELU with one MUFU op per value: for z = |x|/sqrt(2), erfc(z) = (1 + a1 z + ... + a6 z^6)^-16
-// (Abramowitz-Stegun 7.1.28, |error| <= 3e-7), so gelu(x) = x - h for x >= 0 and h for x < 0 with h = x/2 * erfc(z).
-__device__ __forceinline__ float geluErf(float x)
+// erf-GELU through a fitted tanh form: gelu(x) = x/2 * (1 + tanh(x * (c1 + c3 x^2 + c5 x^4))), x^2 clamped at 64.
+// The three coefficients are a minimax fit against 0.5 x (1 + erf(x / sqrt 2)) on [-9, 9]: |error| <= 2.6e-5
+// (the classic 0.044715 cubic form is off by 4.7e-4). On top comes the error of the hardware tanh.approx
+// (about 2^-11 relative), i.e. at most ~2.5e-4 |x| absolute - below FP16 resolution of the result and about
+// 1 % of an INT8 step. Cost: 5 FMA-pipe operations and one MUFU operation per value.
+constexpr float kGeluC1 = 7.97507884e-01f;
+constexpr float kGeluC3 = 3.70056460e-02f;
+constexpr float kGeluC5 = -3.51516788e-04f;
+
+__device__ __forceinline__ float geluInner(float x)
 {
-    float const z = fabsf(x) * 0.70710678118654752440f;
-    float p = fmaf(0.0000430638f, z, 0.0002765672f);
-    p = fmaf(p, z, 0.0001520143f);
-    p = fmaf(p, z, 0.0092705272f);
-    p = fmaf(p, z, 0.0422820123f);
-    p = fmaf(p, z, 0.0705230784f);
-    p = fmaf(p, z, 1.f);
-    p *= p;
-    p *= p;
-    p *= p;
-    p *= p; // overflows to +inf for large |x|: erfc -> 0
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(p));
-    float const h = 0.5f * x * r;
-    return x >= 0.f ? x - h : h;
+    float const x2 = fminf(x * x, 64.f);
+    return x * fmaf(fmaf(kGeluC5, x2, kGeluC3), x2, kGeluC1);
+}
+
+__device__ __forceinline__ float tanhApprox(float x)
+{
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// scale * gelu(x); `halfScale` = scale / 2
+__device__ __forceinline__ float geluErf(float x, float halfScale)
+{
+    float const h = x * halfScale;
+    return fmaf(h, tanhApprox(geluInner(x)), h);
+}
+
+// Two values at once with the packed FP16 tanh (one MUFU operation per pair); used where the result is
+// quantised to INT8 right away, so FP16 precision of tanh (and of its argument) is ample.
+__device__ __forceinline__ void geluErfPair(float& a, float& b, float halfScale)
+{
+    float const ua = geluInner(a), ub = geluInner(b);
+    uint32_t packed, t;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(ub), "f"(ua));
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(packed));
+    float2 const tf = __half22float2(*reinterpret_cast<__half2 const*>(&t));
+    float const ha = a * halfScale, hb = b * halfScale;
+    a = fmaf(ha, tf.x, ha);
+    b = fmaf(hb, tf.y, hb);
+}
+
+// Round-to-nearest-even and saturate to [-128, 127] on the FMA pipe (clamp, then add 1.5 * 2^23 so that the
+// integer sits in the low mantissa bits), four results packed into one word: same values as cvt.rni.sat.s8.f32
+// without occupying the conversion unit, which the INT32 -> FP32 conversions of the accumulators already fill.
+__device__ __forceinline__ uint32_t quantPack4(float a, float b, float c, float d)
+{
+    constexpr float kMagic = 12582912.f;
+    uint32_t const ua = __float_as_uint(fminf(fmaxf(a, -128.f), 127.f) + kMagic);
+    uint32_t const ub = __float_as_uint(fminf(fmaxf(b, -128.f), 127.f) + kMagic);
+    uint32_t const uc = __float_as_uint(fminf(fmaxf(c, -128.f), 127.f) + kMagic);
+    uint32_t const ud = __float_as_uint(fminf(fmaxf(d, -128.f), 127.f) + kMagic);
+    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
 template <typename Out>
@@ -99,7 +135,7 @@ __device__ __forceinline__ void storeChunk32<__half>(__half* dst, float const (&
 }
 
 template <>
-__device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&v)[32], float outScale, int validCols)
+__device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&v)[32], float, int validCols)
 {
 #pragma unroll
     for (int g = 0; g < 2; ++g)
@@ -110,8 +146,7 @@ __device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&
             uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                w[j] = packChar4(v[g * 16 + 4 * j] * outScale, v[g * 16 + 4 * j + 1] * outScale,
-                    v[g * 16 + 4 * j + 2] * outScale, v[g * 16 + 4 * j + 3] * outScale);
+                w[j] = quantPack4(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3]);
             *reinterpret_cast<uint4*>(dst + g * 16) = o;
         }
     }
@@ -144,11 +179,30 @@ __device__ __forceinline__ void fcEpilogueChunk(uint32_t const (&r)[32], FcArgs 
             }
         }
     }
+    // INT8 results leave this function already multiplied by out_scale; FP16 results unscaled.
+    constexpr bool kQuant = sizeof(Out) == 1;
+    float const scale = kQuant ? args.outScale : 1.f;
     if (args.act == BERT_B200_ACT_GELU_ERF)
+    {
+        float const halfScale = 0.5f * scale;
+        if (kQuant)
+        {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+                geluErfPair(v[j], v[j + 1], halfScale);
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                v[j] = geluErf(v[j], halfScale);
+        }
+    }
+    else if (kQuant)
     {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-            v[j] = geluErf(v[j]);
+            v[j] *= scale;
     }
     if (row < args.M)
         storeChunk32<Out>(C + row * args.ldc + col, v, args.outScale, validCols);
@@ -303,7 +357,7 @@ __global__ void __launch_bounds__(kFcThreads, 1)
     else
     {
         int const quad = warp & 3;        // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may read
-        int const colHalf = (warp - 2) >> 2; // warps 2-5 take even 64-column groups, warps 6-9 the odd ones
+        int const part = (warp - 2) >> 2; // four warps share a quadrant; each takes every fourth 32-column chunk
         int acc = 0;
         uint32_t accPhase = 0;
         Out* const C = static_cast<Out*>(args.C);
@@ -317,17 +371,15 @@ __global__ void __launch_bounds__(kFcThreads, 1)
             int64_t const row = m0 + quad * 32 + lane;
             uint32_t const taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-            for (int cc = 0; cc < BLOCK_N / 64; ++cc)
+            for (int c = part; c < BLOCK_N / 32; c += kEpilogueWarps / 4) // this warp's 32-column chunks of the tile
             {
-                int const c = (cc >> 1) * 4 + colHalf * 2 + (cc & 1); // 32-column chunk index inside the tile
                 uint32_t r[32];
                 tmemLoad32(taddr + c * 32, r);
-                tmemLoadWait();
+                tmemLoadWait32(r);
                 int64_t const col = n0 + c * 32;
                 int const validCols = static_cast<int>(args.N - col < 32 ? args.N - col : 32);
-                if (validCols <= 0)
-                    continue; // warp-uniform
-                fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
+                if (validCols > 0) // warp-uniform
+                    fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
             }
             tcFenceBefore();
             mbarArrive(&accEmpty[acc]);
@@ -570,7 +622,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFcThreads, 1)
     else
     {
         int const quad = warp & 3;
-        int const colHalf = (warp - 2) >> 2;
+        int const part = (warp - 2) >> 2;
         int acc = 0;
         uint32_t accPhase = 0;
         Out* const C = static_cast<Out*>(args.C);
@@ -584,17 +636,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFcThreads, 1)
             int64_t const row = m0 + quad * 32 + lane;
             uint32_t const taddr = tmemBase + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-            for (int cc = 0; cc < BLOCK_N / 64; ++cc)
+            for (int c = part; c < BLOCK_N / 32; c += kEpilogueWarps / 4) // this warp's 32-column chunks of the tile
             {
-                int const c = (cc >> 1) * 4 + colHalf * 2 + (cc & 1);
                 uint32_t r[32];
                 tmemLoad32(taddr + c * 32, r);
-                tmemLoadWait();
+                tmemLoadWait32(r);
                 int64_t const col = n0 + c * 32;
                 int const validCols = static_cast<int>(args.N - col < 32 ? args.N - col : 32);
-                if (validCols <= 0)
-                    continue;
-                fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
+                if (validCols > 0) // warp-uniform
+                    fcEpilogueChunk<kInt8, Out>(r, args, C, row, col, validCols);
             }
             tcFenceBefore();
             mbarArriveCluster(mapaShared(&accEmpty[acc], 0)); // the leader's barrier counts both CTAs

