@@ -120,25 +120,32 @@ __device__ __forceinline__ uint4 packHalf8(float const (&f)[8])
     return v;
 }
 
+// INT8 <-> FP32 without the conversion unit. cvt.f32.s32 / cvt.rni.sat.s8.f32 run at a sixteenth of the FMA rate and
+// bound every INT8 kernel here; the same results come from the integer/FMA pipes:
+//   byte -> float : flip the sign bit (b + 128 in 0..255), drop it into the low mantissa byte of 2^23 (one PRMT per
+//                   value) and subtract 2^23 + 128 (exact).
+//   float -> byte : clamp to [-128, 127], add 1.5 * 2^23 (the FP32 adder rounds to nearest even, like cvt.rni), take
+//                   the low byte.
 __device__ __forceinline__ void unpackChar4(uint32_t w, float (&f)[4])
 {
-    f[0] = static_cast<float>(static_cast<int8_t>(w & 0xff));
-    f[1] = static_cast<float>(static_cast<int8_t>((w >> 8) & 0xff));
-    f[2] = static_cast<float>(static_cast<int8_t>((w >> 16) & 0xff));
-    f[3] = static_cast<float>(static_cast<int8_t>(w >> 24));
+    uint32_t const u = w ^ 0x80808080u;
+    constexpr float kBias = 8388736.f; // 2^23 + 128
+    f[0] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - kBias;
+    f[1] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - kBias;
+    f[2] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - kBias;
+    f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - kBias;
 }
 
 // Round-to-nearest-even, saturate to [-128,127], pack four values into one word
 // (same result as the reference's float4_to_char4, plugin/common/common.cuh:482-504).
 __device__ __forceinline__ uint32_t packChar4(float a, float b, float c, float d)
 {
-    int32_t ia, ib, ic, id;
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ia) : "f"(a));
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ib) : "f"(b));
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ic) : "f"(c));
-    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(id) : "f"(d));
-    return (static_cast<uint32_t>(ia) & 0xffu) | ((static_cast<uint32_t>(ib) & 0xffu) << 8)
-        | ((static_cast<uint32_t>(ic) & 0xffu) << 16) | ((static_cast<uint32_t>(id) & 0xffu) << 24);
+    constexpr float kMagic = 12582912.f; // 1.5 * 2^23
+    uint32_t const ua = __float_as_uint(fminf(fmaxf(a, -128.f), 127.f) + kMagic);
+    uint32_t const ub = __float_as_uint(fminf(fmaxf(b, -128.f), 127.f) + kMagic);
+    uint32_t const uc = __float_as_uint(fminf(fmaxf(c, -128.f), 127.f) + kMagic);
+    uint32_t const ud = __float_as_uint(fminf(fmaxf(d, -128.f), 127.f) + kMagic);
+    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
 __device__ __forceinline__ int8_t quantChar(float a)

@@ -101,19 +101,6 @@ __device__ __forceinline__ void geluErfPair(float& a, float& b, float halfScale)
     b = fmaf(hb, tf.y, hb);
 }
 
-// Round-to-nearest-even and saturate to [-128, 127] on the FMA pipe (clamp, then add 1.5 * 2^23 so that the
-// integer sits in the low mantissa bits), four results packed into one word: same values as cvt.rni.sat.s8.f32
-// without occupying the conversion unit, which the INT32 -> FP32 conversions of the accumulators already fill.
-__device__ __forceinline__ uint32_t quantPack4(float a, float b, float c, float d)
-{
-    constexpr float kMagic = 12582912.f;
-    uint32_t const ua = __float_as_uint(fminf(fmaxf(a, -128.f), 127.f) + kMagic);
-    uint32_t const ub = __float_as_uint(fminf(fmaxf(b, -128.f), 127.f) + kMagic);
-    uint32_t const uc = __float_as_uint(fminf(fmaxf(c, -128.f), 127.f) + kMagic);
-    uint32_t const ud = __float_as_uint(fminf(fmaxf(d, -128.f), 127.f) + kMagic);
-    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
-}
-
 template <typename Out>
 __device__ __forceinline__ void storeChunk32(Out* dst, float const (&v)[32], float outScale, int validCols);
 
@@ -146,7 +133,7 @@ __device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&
             uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j)
-                w[j] = quantPack4(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3]);
+                w[j] = packChar4(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3]);
             *reinterpret_cast<uint4*>(dst + g * 16) = o;
         }
     }
