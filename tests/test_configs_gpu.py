@@ -1,0 +1,144 @@
+"""The benchmark configurations as end-to-end parity cases.
+
+config 1: one BERT-base post-LN encoder layer (batch 8, seq 128, hidden 768, 12 heads x 64, FFN 3072, erf-GELU), FP32
+          oracle / FP16 target, all-valid mask - run through the PLUGIN OBJECTS in the fixed [S, B, E] layout, i.e. the
+          path a TensorRT engine would take: FC -> QKVToContext(v4, mask from EmbLayerNorm-style mask index) -> FC ->
+          SkipLayerNorm(v5, bias) -> FC(+bias+GELU) -> FC -> SkipLayerNorm(v5, bias).
+config 2: BERT-base front end: EmbLayerNorm v6 on B=32, S=128 with lengths in [64, 128] + two layers of the encoder.
+config 4: BERT-large packed variable-length path, lengths uniform in [32, 384] (seed 1), sharded by token count.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bert_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+EMB, QKV, SKIP, FC = ("CustomEmbLayerNormPluginDynamic", "CustomQKVToContextPluginDynamic",
+                      "CustomSkipLayerNormPluginDynamic", "CustomFCPluginDynamic")
+
+
+def _t(a, cuda):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+
+
+def _enqueue(p, ins, outs, in_descs, out_descs, ws=None):
+    st = p.enqueue(in_descs, out_descs, [t.data_ptr() for t in ins], [t.data_ptr() for t in outs],
+                   ws.data_ptr() if ws is not None else None, torch.cuda.current_stream().cuda_stream)
+    assert st == 0, st
+
+
+def test_config1_single_layer_through_plugins(cuda):
+    from tensorrt_b200 import plugin_harness as H
+
+    rng = np.random.default_rng(0)
+    B, S, E, N, F = 8, 128, 768, 12, 3072
+    n = lambda *s: (0.02 * rng.standard_normal(s)).astype(np.float32)
+    hidden = rng.standard_normal((S, B, E)).astype(np.float16)            # hidden states ~N(0, 1), layout [S, B, E]
+    lp = O.LayerParams(w_qkv=n(E, 3 * E).astype(np.float16), b_qkv=n(3 * E), w_out=n(E, E).astype(np.float16), b_out=n(E).astype(np.float16),
+                       ln1_gamma=(1 + n(E)).astype(np.float16), ln1_beta=n(E).astype(np.float16), w_ffn1=n(E, F).astype(np.float16),
+                       b_ffn1=n(F), w_ffn2=n(F, E).astype(np.float16), b_ffn2=n(E).astype(np.float16),
+                       ln2_gamma=(1 + n(E)).astype(np.float16), ln2_beta=n(E).astype(np.float16))
+    # oracle on the same rows in packed order (sequence b owns rows [b*S, (b+1)*S))
+    x_packed = np.ascontiguousarray(hidden.transpose(1, 0, 2)).reshape(B * S, E)
+    cu = np.arange(0, (B + 1) * S, S, dtype=np.int32)
+    ref, _ = O.encoder_layer_fp(x_packed.astype(np.float64), lp, B, S, N, cu, round_fp16=True)
+    ref = ref.reshape(B, S, E).transpose(1, 0, 2)
+
+    fc = lambda W, out, extra=(): H.Plugin(FC, "1", [("out_dims", out), ("type_id", 1), ("W", W.astype(np.float32).ravel())] + list(extra)).attach()
+    p_qkv = fc(lp.w_qkv, 3 * E, [("bias", lp.b_qkv)])
+    p_att = H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", E), ("num_heads", N), ("has_mask", 1)]).attach()
+    p_out = fc(lp.w_out, E)
+    p_ln1 = H.Plugin(SKIP, "5", [("type_id", 1), ("ld", E), ("beta", lp.ln1_beta.astype(np.float32)),
+                                 ("gamma", lp.ln1_gamma.astype(np.float32)), ("bias", lp.b_out.astype(np.float32))]).attach()
+    p_f1 = fc(lp.w_ffn1, F, [("bias", lp.b_ffn1), ("activation", 1)])
+    p_f2 = fc(lp.w_ffn2, E)
+    p_ln2 = H.Plugin(SKIP, "5", [("type_id", 1), ("ld", E), ("beta", lp.ln2_beta.astype(np.float32)),
+                                 ("gamma", lp.ln2_gamma.astype(np.float32)), ("bias", lp.b_ffn2.astype(np.float32))]).attach()
+    assert all(p.ok for p in (p_qkv, p_att, p_out, p_ln1, p_f1, p_f2, p_ln2))
+
+    d = lambda c: H.make_desc((S, B, c, 1, 1), H.HALF)
+    buf = lambda c: torch.empty((S, B, c), dtype=torch.float16, device=cuda)
+    x = _t(hidden, cuda)
+    qkv, ctx, ao, h1, f1, f2, out = buf(3 * E), buf(E), buf(E), buf(E), buf(F), buf(E), buf(E)
+    mask_idx = torch.full((B, 1), S, dtype=torch.int32, device=cuda)      # all-valid mask as the embedding plugin emits it
+    _enqueue(p_qkv, [x], [qkv], [d(E)], [d(3 * E)])
+    ws = torch.empty(256, dtype=torch.uint8, device=cuda)
+    _enqueue(p_att, [qkv, mask_idx], [ctx], [d(3 * E), H.make_desc((B, 1), H.INT32)], [d(E)], ws)
+    _enqueue(p_out, [ctx], [ao], [d(E)], [d(E)])
+    _enqueue(p_ln1, [ao, x], [h1], [d(E), d(E)], [d(E)])
+    _enqueue(p_f1, [h1], [f1], [d(E)], [d(F)])
+    _enqueue(p_f2, [f1], [f2], [d(F)], [d(E)])
+    _enqueue(p_ln2, [f2, h1], [out], [d(E), d(E)], [d(E)])
+    torch.cuda.synchronize()
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+    for p in (p_qkv, p_att, p_out, p_ln1, p_f1, p_f2, p_ln2):
+        p.close()
+
+
+def test_config2_front_end_and_two_layers(cuda):
+    """Config 2 shapes (BERT-base, B = 32, S = 128, lengths in [64, 128], segment split) on the first two layers:
+    EmbLayerNorm v6 semantics for the mask index, packed encoder for the layers."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(2)
+    B, S = 32, 128
+    p = O.make_bert_params(rng, 2, 768, 12, 3072, vocab=30522, max_pos=512)
+    lengths = rng.integers(64, 129, size=B).astype(np.int32)
+    ids_sb = rng.integers(0, 30522, size=(S, B)).astype(np.int32)
+    split = rng.integers(1, 128, size=B)
+    seg_sb = (np.arange(S)[:, None] >= split[None, :]).astype(np.int32)
+    mask_sb = (np.arange(S)[:, None] < lengths[None, :]).astype(np.int32)
+    # mask index output of the front end: bit-exact
+    assert np.array_equal(T.compute_mask_idx(_t(mask_sb, cuda)).cpu().numpy(), lengths)
+    # the valid tokens, packed, through the encoder
+    cu = O.cu_seqlens(lengths)
+    ids = np.concatenate([ids_sb[:lengths[b], b] for b in range(B)]).astype(np.int32)
+    seg = np.concatenate([seg_sb[:lengths[b], b] for b in range(B)]).astype(np.int32)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    out = enc.forward(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), S).cpu().numpy()
+    ref = O.encoder_fp(p, ids, seg, cu, S)
+    ok, worst, bad = O.close_abs_or_rel(out, ref, 1e-2, 1e-2)
+    assert bad <= out.size * 1e-3 and worst < 5e-2, (worst, bad)
+    # the fixed-layout embedding plugin kernel agrees with the packed one on the valid tokens (bit for bit)
+    emb_fixed = T.emb_layer_norm(_t(ids_sb, cuda), _t(seg_sb, cuda), enc.word_emb, enc.pos_emb, enc.tok_emb, enc.emb_gamma,
+                                 enc.emb_beta).cpu().numpy()
+    emb_packed = T.emb_layer_norm_var_seqlen(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), S, enc.word_emb, enc.pos_emb,
+                                             enc.tok_emb, enc.emb_gamma, enc.emb_beta).cpu().numpy()
+    gathered = np.concatenate([emb_fixed[:lengths[b], b] for b in range(B)])
+    assert np.array_equal(gathered, emb_packed)
+    enc.close()
+
+
+def test_config4_packed_var_len_sharded(cuda):
+    """Config 4: lengths uniform in [32, 384], seed 1, B = 256 (about 53k tokens), greedy token balancing over 8
+    shards; one BERT-large layer on the packed tokens of the heaviest shard, FP16 and INT8, and the property that a
+    sequence's output does not depend on which other sequences share its shard."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(1)
+    lengths_all = rng.integers(32, 385, size=256).astype(np.int32)
+    assert 50000 < int(lengths_all.sum()) < 56000
+    shards = T.shard_by_tokens(lengths_all, 8)
+    loads = [int(lengths_all[s].sum()) for s in shards]
+    assert max(loads) - min(loads) <= 384
+    mine = shards[int(np.argmax(loads))]
+    lengths = lengths_all[mine]
+    p = O.make_bert_params(rng, 1, 1024, 16, 4096, vocab=30522)
+    cu = O.cu_seqlens(lengths)
+    total = int(cu[-1])
+    ids = rng.integers(0, 30522, size=total).astype(np.int32)
+    seg = rng.integers(0, 2, size=total).astype(np.int32)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    out = enc.forward(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), 384).cpu().numpy()
+    # oracle on the first three sequences only (the layer is per-sequence independent)
+    k = 3
+    sub = O.encoder_fp(p, ids[:cu[k]], seg[:cu[k]], cu[:k + 1], 384)
+    ok, worst, bad = O.close_abs_or_rel(out[:cu[k]], sub, 1e-2, 1e-2)
+    assert bad <= sub.size * 1e-3 and worst < 5e-2, (worst, bad)
+    # same three sequences alone give bit-identical rows
+    alone = enc.forward(_t(ids[:cu[k]], cuda), _t(seg[:cu[k]], cuda), _t(cu[:k + 1], cuda), 384).cpu().numpy()
+    assert np.array_equal(alone, out[:cu[k]])
+    enc.close()
