@@ -148,6 +148,18 @@ __device__ __forceinline__ uint32_t packChar4(float a, float b, float c, float d
     return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
+// Same with the output scale folded into the rounding step: the values are clamped to [lo, hi] = [-128 / s, 127 / s]
+// first, then one FMA computes x * s + 1.5 * 2^23 (a single rounding, to nearest even).
+__device__ __forceinline__ uint32_t packChar4Scaled(float a, float b, float c, float d, float s, float lo, float hi)
+{
+    constexpr float kMagic = 12582912.f; // 1.5 * 2^23
+    uint32_t const ua = __float_as_uint(fmaf(fminf(fmaxf(a, lo), hi), s, kMagic));
+    uint32_t const ub = __float_as_uint(fmaf(fminf(fmaxf(b, lo), hi), s, kMagic));
+    uint32_t const uc = __float_as_uint(fmaf(fminf(fmaxf(c, lo), hi), s, kMagic));
+    uint32_t const ud = __float_as_uint(fmaf(fminf(fmaxf(d, lo), hi), s, kMagic));
+    return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
+}
+
 __device__ __forceinline__ int8_t quantChar(float a)
 {
     int32_t ia;

@@ -73,7 +73,9 @@ __device__ __forceinline__ void mbarArriveExpectTx(uint64_t* bar, uint32_t bytes
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smemAddr(bar)), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
+// `barAddr` is a shared::cta address (smemAddr); the loops of the single-thread producer / MMA roles keep such
+// addresses in registers so that a wait costs no address arithmetic.
+__device__ __forceinline__ bool mbarTryWaitAddr(uint32_t barAddr, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
@@ -83,9 +85,14 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(smemAddr(bar)), "r"(parity)
+        : "r"(barAddr), "r"(parity)
         : "memory");
     return ok != 0;
+}
+
+__device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
+{
+    return mbarTryWaitAddr(smemAddr(bar), parity);
 }
 
 // Every spin in these kernels is bounded: after kWaitLimitNs without progress the waiter records
@@ -93,27 +100,35 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
 // returns false. The kernel then drains, frees its TMEM and exits; the host sees the status word.
 constexpr uint64_t kWaitLimitNs = 2000000000ull; // 2 s
 
-__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
+__device__ __forceinline__ bool mbarWaitAddr(uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
 {
-    if (mbarTryWait(bar, parity))
-        return true;
-    uint64_t const t0 = globalTimerNs();
+    // The clock is only consulted every 256 failed polls (a read of %globaltimer costs far more than a poll, and most
+    // waits end within a few polls), so the common case is nothing but try_wait.
+    uint64_t t0 = 0;
     uint32_t polls = 0;
     while (true)
     {
-        if (mbarTryWait(bar, parity))
+        if (mbarTryWaitAddr(barAddr, parity))
             return true;
-        if ((++polls & 63u) == 0)
+        if ((++polls & 255u) == 0)
         {
             if (*abortFlag != 0)
                 return false;
-            if (globalTimerNs() - t0 > kWaitLimitNs)
+            uint64_t const now = globalTimerNs();
+            if (t0 == 0)
+                t0 = now;
+            else if (now - t0 > kWaitLimitNs)
             {
                 *abortFlag = code;
                 return false;
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
+{
+    return mbarWaitAddr(smemAddr(bar), parity, abortFlag, code);
 }
 
 // ---- TMA ------------------------------------------------------------------------------------
@@ -138,6 +153,36 @@ __device__ __forceinline__ void tmaLoad3d(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
         : "memory");
+}
+
+// Tiled store from this CTA's shared memory (bulk async-group completion). The writer makes its shared-memory
+// writes visible to the async proxy first (fenceProxyAsync by every writing thread, then a barrier); the issuing
+// thread must see its groups complete (bulkWaitGroup<0>) before the CTA exits. The innermost coordinate times the
+// element size is a multiple of 16 bytes at every call site; elements outside the tensor are not written.
+__device__ __forceinline__ void tmaStore2d(CUtensorMap const* map, void const* src, int32_t c0, int32_t c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void bulkCommitGroup()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// At most N of this thread's most recent bulk groups may still be reading their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulkWaitGroupRead()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+
+// At most N of this thread's most recent bulk groups may still be incomplete.
+template <int N>
+__device__ __forceinline__ void bulkWaitGroup()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---- tcgen05 / TMEM -------------------------------------------------------------------------
@@ -335,6 +380,61 @@ __device__ __forceinline__ void mmaI8Pair(uint32_t dTmem, uint64_t aDesc, uint64
         "}" ::"r"(dTmem),
         "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
+}
+
+// Lean forms for the inner loops of the single-thread roles. Those threads share a warp scheduler with busy epilogue
+// warps, so every instruction they need per k-block costs tensor-pipe time: shared-memory addresses and the descriptor
+// words are kept in registers, the 64-bit descriptors are assembled inside the asm block from a running low word
+// (start-address field in bits 0-13, + bytes >> 4 to advance) and the constant high word, and the accumulate flag is
+// a compile-time constant where it can be.
+template <bool kInt8, bool kAcc>
+__device__ __forceinline__ void mmaPairLoHi(uint32_t dTmem, uint32_t aLo, uint32_t bLo, uint32_t descHi, uint32_t iDesc)
+{
+    if constexpr (kInt8)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t"
+            "}" ::"r"(dTmem),
+            "r"(aLo), "r"(bLo), "r"(descHi), "r"(iDesc), "n"(kAcc ? 1 : 0)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %5, 0;\n\t"
+            "mov.b64 da, {%1, %3};\n\t"
+            "mov.b64 db, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t"
+            "}" ::"r"(dTmem),
+            "r"(aLo), "r"(bLo), "r"(descHi), "r"(iDesc), "n"(kAcc ? 1 : 0)
+            : "memory");
+}
+
+__device__ __forceinline__ void tcCommitPairAddr(uint32_t barAddr, uint16_t ctaMask)
+{
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(barAddr),
+        "h"(ctaMask)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmaLoad2dPairAddr(uint32_t dstAddr, CUtensorMap const* map, uint32_t barClusterAddr, int32_t c0, int32_t c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dstAddr), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void mbarArriveExpectTxAddr(uint32_t barAddr, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(barAddr), "r"(bytes) : "memory");
 }
 
 // ---- descriptors ----------------------------------------------------------------------------
