@@ -147,75 +147,66 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     constexpr uint32_t kIdescQk = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 0u, 128u, 128u);
     constexpr uint32_t kIdescPv = makeInstrDesc(kInt8 ? 2u : 1u, kInt8 ? 1u : 0u, 0u, 1u, 128u, 64u);
 
-    int const head = blockIdx.x;
-    int const b = blockIdx.y;
     int const warp = threadIdx.x >> 5;
     int const lane = threadIdx.x & 31;
 
-    // ---- sequence geometry (uniform over the CTA) ----
-    int32_t rowBase, rows, len;
-    if (args.fixedLayout)
+    // ---- work items: one (sequence, head) each, item = b * N + head, dealt round-robin to the persistent CTAs ----
+    struct Item
     {
-        rowBase = 0;
-        rows = args.S;
-        len = args.maskIdx ? min(max(__ldg(args.maskIdx + b), 0), args.S) : args.S;
-    }
-    else
-    {
-        rowBase = __ldg(args.cu + b);
-        len = min(max(__ldg(args.cu + b + 1) - rowBase, 0), args.S);
-        rows = len;
-    }
-    if (rows <= 0)
-        return;
-    int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
-    T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(head) * kHeadSize;
-    // linear layouts: the 64 values of (token, head) are contiguous. Interleaved: see outPtrIl below.
-    auto outRow = [&](int q) -> T* {
-        int64_t const r = args.fixedLayout ? static_cast<int64_t>(q) * args.B + b : static_cast<int64_t>(rowBase) + q;
-        return outBase + r * outRowStride;
+        int32_t b, head, rowBase, rows, len, nb, nq;
     };
-    // interleaved output [N][2][total][32]: 32-channel group `grp` of (token, head)
-    auto outPtrIl = [&](int q, int grp) -> T* {
-        return static_cast<T*>(args.out) + ((static_cast<int64_t>(head) * 2 + grp) * args.total + rowBase + q) * 32;
-    };
-    if (len == 0)
-    {
-        // no valid key: every probability is zero and so is the context row
-        constexpr int kChunks = L::kRowBytes / 16;
-        for (int i = threadIdx.x; i < rows * kChunks; i += kMhaThreads)
+    int const numItems = args.B * args.N;
+    // Geometry of item i (uniform over the CTA; every role derives the same values). Returns whether the item has
+    // work for the tensor pipeline (at least one query row and one valid key).
+    auto getItem = [&](int i, Item& it) -> bool {
+        it.b = i / args.N;
+        it.head = i - it.b * args.N;
+        if (args.fixedLayout)
         {
-            int const q = i / kChunks;
-            int const c = i % kChunks;
-            if (IL)
-                reinterpret_cast<uint4*>(outPtrIl(q, c / 2))[c % 2] = make_uint4(0, 0, 0, 0);
-            else
-                reinterpret_cast<uint4*>(outRow(q))[c] = make_uint4(0, 0, 0, 0);
+            it.rowBase = 0;
+            it.rows = args.S;
+            it.len = args.maskIdx ? min(max(__ldg(args.maskIdx + it.b), 0), args.S) : args.S;
         }
-        return;
-    }
-    int const nb = (len + kKeyBlock - 1) / kKeyBlock;   // key blocks
-    int const nq = (rows + kQTile - 1) / kQTile;        // query tiles
+        else
+        {
+            it.rowBase = __ldg(args.cu + it.b);
+            it.len = min(max(__ldg(args.cu + it.b + 1) - it.rowBase, 0), args.S);
+            it.rows = it.len;
+        }
+        it.nb = (it.len + kKeyBlock - 1) / kKeyBlock; // key blocks
+        it.nq = (it.rows + kQTile - 1) / kQTile;      // query tiles
+        return it.rows > 0 && it.len > 0;
+    };
+    // first item >= i of this CTA's sequence that has pipeline work; numItems or more if there is none
+    auto nextWork = [&](int i, Item& it) -> int {
+        while (i < numItems && !getItem(i, it))
+            i += gridDim.x;
+        return i;
+    };
+
+    // The layout of shared memory and TMEM follows the longest sequence the launch admits.
+    int const nbMax = (args.S + kKeyBlock - 1) / kKeyBlock;
     // S > 384: the context accumulator has to share TMEM columns with the scores of key block 0
-    bool const oAliasesScores = nb > 3;
+    bool const oAliasesScores = nbMax > 3;
     uint32_t const oCol = oAliasesScores ? 0u : kOColumn;
+    auto slotOf = [&](int j) { return nbMax <= 3 ? j : (j & 1); };
 
     extern __shared__ uint8_t smemRaw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
     uint8_t* sQ = smem;                          // kTileBytes
-    uint8_t* sK = smem + L::kOffset();           // nb x kTileBytes
-    uint8_t* sV = smem + L::vOffset(nb);         // nb x kTileBytes
-    uint8_t* sP = smem + L::pOffset(nb);         // pSlots(nb) x kPBytes
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::barrierOffset(nb));
-    uint64_t* kFull = bars;                      // [4] K_j landed
-    uint64_t* vFull = bars + kMaxBlocks;         // [4] V_j landed
-    uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete       (once per query tile)
-    uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written, 512 arrivals        (once per query tile)
-    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [4] PV product consumed P slot
-    uint64_t* qFull = pFree + kMaxBlocks;        // Q tile landed                        (once per query tile)
-    uint64_t* qFree = qFull + 1;                 // all score MMAs of the tile done: Q slot reusable
-    uint64_t* oFull = qFree + 1;                 // context accumulator complete         (once per query tile)
-    uint64_t* oFree = oFull + 1;                 // epilogue has read it, 512 arrivals   (once per query tile)
+    uint8_t* sK = smem + L::kOffset();           // nbMax x kTileBytes
+    uint8_t* sV = smem + L::vOffset(nbMax);      // nbMax x kTileBytes
+    uint8_t* sP = smem + L::pOffset(nbMax);      // pSlots(nbMax) x kPBytes
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::barrierOffset(nbMax));
+    uint64_t* kFull = bars;                      // [4] K_j landed                        (once per item using block j)
+    uint64_t* vFull = bars + kMaxBlocks;         // [4] V_j landed                        (once per item using block j)
+    uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete        (once per tile using block j)
+    uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written, 512 arrivals         (once per tile using block j)
+    uint64_t* pFree = bars + 4 * kMaxBlocks;     // [4] PV product consumed P slot        (once per fill of the slot)
+    uint64_t* qFull = pFree + kMaxBlocks;        // Q tile landed                         (once per tile)
+    uint64_t* qFree = qFull + 1;                 // all score MMAs of the tile done: Q slot (after an item's last tile: K) reusable
+    uint64_t* oFull = qFree + 1;                 // context accumulator complete          (once per tile; last tile: V reusable)
+    uint64_t* oFree = oFull + 1;                 // epilogue has read it, 512 arrivals    (once per tile)
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(oFree + 1);
     volatile uint32_t* abortFlag = tmemSlot + 1;
     float* rowRed = reinterpret_cast<float*>(tmemSlot + 4); // [2][4][128]: max then sum, per 32-column owner
@@ -246,36 +237,54 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     tcFenceAfter();
     uint32_t const tmemBase = *tmemSlot;
 
+    // Barriers that complete once per tile (qFull, qFree, oFull, oFree) are waited on with the parity of the CTA's
+    // running tile count; those that complete once per use of key block j keep one parity bit per block.
     if (warp == 0)
     {
         if (lane == 0)
         {
-            int32_t const rowK = args.fixedLayout ? 0 : rowBase;
-            // linear: (column of the token row, batch, row). interleaved: (0, row, 32-channel group of [3][N][2])
-            auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
-                if (IL)
-                    tmaLoad3d(dst, &mapQkv, bar, 0, row, (which * args.N + head) * 2);
-                else
-                    tmaLoad3d(dst, &mapQkv, bar, (head * 3 + which) * kHeadSize, args.fixedLayout ? b : 0, row);
-            };
-            mbarArriveExpectTx(qFull, L::kTileBytes);
-            load(sQ, qFull, 0, rowK);
-            for (int j = 0; j < nb; ++j)
+            Item it;
+            uint32_t tiles = 0; // Q tiles requested so far
+            bool ok = true;
+            for (int item = nextWork(blockIdx.x, it); item < numItems && ok; item = nextWork(item + gridDim.x, it))
             {
-                mbarArriveExpectTx(&kFull[j], L::kTileBytes);
-                load(sK + j * L::kTileBytes, &kFull[j], 1, rowK + j * kKeyBlock);
-            }
-            for (int j = 0; j < nb; ++j)
-            {
-                mbarArriveExpectTx(&vFull[j], L::kTileBytes);
-                load(sV + j * L::kTileBytes, &vFull[j], 2, rowK + j * kKeyBlock);
-            }
-            for (int t = 1; t < nq; ++t)
-            {
-                if (!mbarWait(qFree, (t - 1) & 1, abortFlag, kWaitStageFree))
-                    break;
-                mbarArriveExpectTx(qFull, L::kTileBytes);
-                load(sQ, qFull, 0, rowK + t * kQTile);
+                int32_t const rowK = args.fixedLayout ? 0 : it.rowBase;
+                // linear: (column of the token row, batch, row). interleaved: (0, row, 32-channel group of [3][N][2])
+                auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
+                    if (IL)
+                        tmaLoad3d(dst, &mapQkv, bar, 0, row, (which * args.N + it.head) * 2);
+                    else
+                        tmaLoad3d(dst, &mapQkv, bar, (it.head * 3 + which) * kHeadSize, args.fixedLayout ? it.b : 0, row);
+                };
+                for (int t = 0; t < it.nq && ok; ++t)
+                {
+                    // the score MMAs of the previous tile have read Q (and, across items, K)
+                    if (tiles > 0)
+                        ok = mbarWait(qFree, (tiles - 1) & 1, abortFlag, kWaitStageFree);
+                    if (!ok)
+                        break;
+                    mbarArriveExpectTx(qFull, L::kTileBytes);
+                    load(sQ, qFull, 0, rowK + t * kQTile);
+                    if (t == 0)
+                    {
+                        for (int j = 0; j < it.nb; ++j)
+                        {
+                            mbarArriveExpectTx(&kFull[j], L::kTileBytes);
+                            load(sK + j * L::kTileBytes, &kFull[j], 1, rowK + j * kKeyBlock);
+                        }
+                        // the PV products of the previous item's last tile have read V
+                        if (tiles > 0)
+                            ok = mbarWait(oFull, (tiles - 1) & 1, abortFlag, kWaitStageFree);
+                        if (!ok)
+                            break;
+                        for (int j = 0; j < it.nb; ++j)
+                        {
+                            mbarArriveExpectTx(&vFull[j], L::kTileBytes);
+                            load(sV + j * L::kTileBytes, &vFull[j], 2, rowK + j * kKeyBlock);
+                        }
+                    }
+                    ++tiles;
+                }
             }
         }
     }
@@ -294,7 +303,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             {
                 uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
                 uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
-                uint32_t const pAddr = smemAddr(sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes);
+                uint32_t const pAddr = smemAddr(sP + slotOf(j) * L::kPBytes);
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k) // next 32 bytes of the head dimension
                     kDesc[j][k] = makeSmemDesc(kAddr + (IL ? k * kSubTile : k * 32), 16, kAtomBytes, kSwz);
@@ -310,8 +319,11 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                                      : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
                 }
             }
-            // scores of key block j for the query tile whose Q is in shared memory
-            auto issueScores = [&](int j) {
+            uint32_t qkTiles = 0;  // tiles whose scores have been issued
+            uint32_t pvTiles = 0;  // tiles whose context has been issued
+            uint32_t kBits = 0, vBits = 0, pBits = 0; // parity per key block: K landed, V landed, P written
+            // scores of key block j for the query tile whose Q is in shared memory; nbOf = key blocks of that tile's item
+            auto issueScores = [&](int j, int nbOf) {
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k)
                 {
@@ -321,77 +333,130 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         mmaF16(tmemBase + j * kKeyBlock, qDesc[k], kDesc[j][k], kIdescQk, k != 0);
                 }
                 tcCommit(&sFull[j]);
-                if (j == nb - 1)
+                if (j == nbOf - 1)
                     tcCommit(qFree);
             };
-            ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
-#pragma unroll
-            for (int j = 0; j < kMaxBlocks; ++j)
+            // first use of K_j by an item: wait for it to land
+            auto waitK = [&](int j) -> bool {
+                bool const got = mbarWait(&kFull[j], (kBits >> j) & 1u, abortFlag, kWaitTmaFull);
+                kBits ^= 1u << j;
+                return got;
+            };
+            Item cur, nxt;
+            int item = nextWork(blockIdx.x, cur);
+            if (item < numItems)
             {
-                if (j < nb && ok)
-                {
-                    ok = mbarWait(&kFull[j], 0, abortFlag, kWaitTmaFull);
-                    if (ok)
-                    {
-                        tcFenceAfter();
-                        issueScores(j);
-                    }
-                }
-            }
-            for (int t = 0; t < nq && ok; ++t)
-            {
-                bool const more = t + 1 < nq;
+                ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
 #pragma unroll
                 for (int j = 0; j < kMaxBlocks; ++j)
                 {
-                    if (j < nb && ok)
+                    if (j < cur.nb && ok)
                     {
-                        if (t == 0)
-                            ok = mbarWait(&vFull[j], 0, abortFlag, kWaitTmaFull);
-                        if (ok && j == 0 && t > 0) // the previous tile's context must have been read out
-                            ok = mbarWait(oFree, (t - 1) & 1, abortFlag, kWaitAccFree);
-                        ok = ok && mbarWait(&pReady[j], t & 1, abortFlag, kWaitSoftmax);
+                        ok = waitK(j);
                         if (ok)
                         {
                             tcFenceAfter();
+                            issueScores(j, cur.nb);
+                        }
+                    }
+                }
+                qkTiles = 1;
+            }
+            while (item < numItems && ok)
+            {
+                int const nextItem = nextWork(item + gridDim.x, nxt);
+                for (int t = 0; t < cur.nq && ok; ++t)
+                {
+                    bool const lastT = t + 1 == cur.nq;
+                    // the scores issued while this tile's context is formed: the item's next tile, or the first tile
+                    // of the CTA's next item (whose K then has to have landed), or none
+                    int const nbFollow = !lastT ? cur.nb : (nextItem < numItems ? nxt.nb : 0);
 #pragma unroll
-                            for (int k = 0; k < kPvMmas; ++k)
+                    for (int j = 0; j < kMaxBlocks; ++j)
+                    {
+                        if (j < cur.nb && ok)
+                        {
+                            if (t == 0)
                             {
-                                if (kInt8)
-                                    mmaI8(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
-                                else
-                                    mmaF16(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                                ok = mbarWait(&vFull[j], (vBits >> j) & 1u, abortFlag, kWaitTmaFull);
+                                vBits ^= 1u << j;
                             }
-                            tcCommit(&pFree[nb <= 3 ? j : (j & 1)]);
-                            if (j == nb - 1)
-                                tcCommit(oFull);
-                            // scores of the next tile for this key block: its columns were released by pReady[j]
-                            if (more && !oAliasesScores)
+                            if (ok && j == 0 && pvTiles > 0) // the previous tile's context must have been read out
+                                ok = mbarWait(oFree, (pvTiles - 1) & 1, abortFlag, kWaitAccFree);
+                            ok = ok && mbarWait(&pReady[j], (pBits >> j) & 1u, abortFlag, kWaitSoftmax);
+                            pBits ^= 1u << j;
+                            if (ok)
                             {
-                                if (j == 0)
-                                    ok = mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
-                                if (ok)
+                                tcFenceAfter();
+#pragma unroll
+                                for (int k = 0; k < kPvMmas; ++k)
                                 {
-                                    tcFenceAfter();
-                                    issueScores(j);
+                                    if (kInt8)
+                                        mmaI8(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                                    else
+                                        mmaF16(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                                }
+                                tcCommit(&pFree[slotOf(j)]);
+                                if (j == cur.nb - 1)
+                                    tcCommit(oFull);
+                                // scores of the following tile for this key block: its columns were released by pReady[j]
+                                if (j < nbFollow && !oAliasesScores)
+                                {
+                                    if (j == 0)
+                                        ok = mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
+                                    if (ok && lastT)
+                                        ok = waitK(j);
+                                    if (ok)
+                                    {
+                                        tcFenceAfter();
+                                        issueScores(j, nbFollow);
+                                    }
                                 }
                             }
                         }
                     }
-                }
-                if (ok && more && oAliasesScores)
-                {
-                    // the context accumulator occupies score columns: wait until the epilogue has read it
-                    ok = mbarWait(oFree, t & 1, abortFlag, kWaitAccFree) && mbarWait(qFull, (t + 1) & 1, abortFlag, kWaitTmaFull);
-                    if (ok)
+                    if (ok && !oAliasesScores)
                     {
-                        tcFenceAfter();
+                        // key blocks the next item has beyond this one's: their score columns are idle
+#pragma unroll
+                        for (int j = 1; j < kMaxBlocks; ++j)
+                        {
+                            if (j >= cur.nb && j < nbFollow && ok)
+                            {
+                                ok = waitK(j);
+                                if (ok)
+                                {
+                                    tcFenceAfter();
+                                    issueScores(j, nbFollow);
+                                }
+                            }
+                        }
+                    }
+                    if (ok && nbFollow > 0 && oAliasesScores)
+                    {
+                        // the context accumulator occupies score columns: wait until the epilogue has read it
+                        ok = mbarWait(oFree, pvTiles & 1, abortFlag, kWaitAccFree) && mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
 #pragma unroll
                         for (int j = 0; j < kMaxBlocks; ++j)
-                            if (j < nb)
-                                issueScores(j);
+                        {
+                            if (j < nbFollow && ok)
+                            {
+                                if (lastT)
+                                    ok = waitK(j);
+                                if (ok)
+                                {
+                                    tcFenceAfter();
+                                    issueScores(j, nbFollow);
+                                }
+                            }
+                        }
                     }
+                    if (nbFollow > 0)
+                        ++qkTiles;
+                    ++pvTiles;
                 }
+                cur = nxt;
+                item = nextItem;
             }
         }
     }
@@ -406,15 +471,27 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         constexpr uint32_t kMagicBits = 0x4B400000u;
         bool ok = true;
         auto colOf = [&](int j) { return j * kKeyBlock + sub * 32; };
+        uint32_t tiles = 0;       // tiles this CTA has started
+        uint32_t sBits = 0;       // parity per key block of sFull (and of this thread's arrivals on pReady)
+        uint32_t slotFilled = 0;  // per P slot: has it been filled before ...
+        uint32_t slotParity = 0;  // ... and the parity of the pFree phase that ends its latest fill
         // Before a P slot is refilled, the PV product that read its previous contents must have completed.
-        auto acquireP = [&](int t, int j) -> bool {
-            int const fill = nb <= 3 ? t : 2 * t + (j >> 1); // how often this slot has been filled before
-            return fill == 0 || mbarWait(&pFree[nb <= 3 ? j : (j & 1)], (fill - 1) & 1, abortFlag, kWaitSoftmax);
+        auto acquireP = [&](int j) -> bool {
+            int const slot = slotOf(j);
+            bool got = true;
+            if ((slotFilled >> slot) & 1u)
+            {
+                got = mbarWait(&pFree[slot], (slotParity >> slot) & 1u, abortFlag, kWaitSoftmax);
+                slotParity ^= 1u << slot;
+            }
+            slotFilled |= 1u << slot;
+            return got;
         };
-        // Reads 16 of the 64 context values of this row, normalises / requantises and stores them.
-        auto epilogue = [&](int t, float inv) {
+        // Reads 16 of the 64 context values of this row (tile number `tileNo` of the CTA), normalises / requantises
+        // and stores them to `dst` (null: row beyond the sequence).
+        auto epilogue = [&](uint32_t tileNo, T* dst, float inv) {
             if (ok)
-                ok = mbarWait(oFull, t & 1, abortFlag, kWaitAccFull);
+                ok = mbarWait(oFull, tileNo & 1, abortFlag, kWaitAccFull);
             if (!ok)
                 return;
             tcFenceAfter();
@@ -423,10 +500,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             tmemLoadWait16(x);
             tcFenceBefore();
             mbarArrive(oFree);
-            int const q = t * kQTile + r;
-            if (q >= rows)
+            if (dst == nullptr)
                 return;
-            T* dst = IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16;
             if (kInt8)
             {
                 float const s2 = args.scaleBmm2;
@@ -454,46 +529,67 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             }
         };
 
-        // The epilogue of tile t runs after pass A of tile t+1: the last PV product of tile t then completes under
-        // useful work instead of a stall. Not possible when the context accumulator shares columns with the scores.
+        // The epilogue of a tile runs after pass A of the CTA's next tile (of the same or the next item): the last PV
+        // product then completes under useful work instead of a stall. Not possible when the context accumulator
+        // shares columns with the scores.
         bool const deferEpilogue = !oAliasesScores;
-        float invPrev = 0.f;
+        bool pending = false;
+        T* pendDst = nullptr;
+        float pendInv = 0.f;
 
-        for (int t = 0; t < nq; ++t)
+        Item it;
+        for (int item = blockIdx.x; item < numItems; item += gridDim.x)
         {
-            uint32_t const tilePhase = t & 1;
-            uint32_t x[32];
-
-            // ---- pass A: row maximum (INT8: integer maximum, no conversions) ----
-            float mx = -INFINITY;
-            int32_t mxi = INT32_MIN;
-#pragma unroll
-            for (int j = 0; j < kMaxBlocks; ++j)
+            bool const work = getItem(item, it);
+            int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
+            T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(it.head) * kHeadSize;
+            // linear layouts: the 64 values of (token, head) are contiguous
+            auto outRow = [&](int q) -> T* {
+                int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + it.b : static_cast<int64_t>(it.rowBase) + q;
+                return outBase + rr * outRowStride;
+            };
+            // interleaved output [N][2][total][32]: 32-channel group `grp` of (token, head)
+            auto outPtrIl = [&](int q, int grp) -> T* {
+                return static_cast<T*>(args.out) + ((static_cast<int64_t>(it.head) * 2 + grp) * args.total + it.rowBase + q) * 32;
+            };
+            if (!work)
             {
-                if (j < nb)
+                // no valid key: every probability is zero and so is the context row
+                constexpr int kChunks = L::kRowBytes / 16;
+                for (int i = threadIdx.x - 64; i < it.rows * kChunks; i += kSoftmaxThreads)
                 {
-                    ok = ok && mbarWait(&sFull[j], tilePhase, abortFlag, kWaitSoftmax);
-                    tcFenceAfter();
-                    tmemLoad32(tRow + colOf(j), x);
-                    tmemLoadWait32(x);
-                    int const limit = len - colOf(j);
-                    if (limit >= 32)
-                    {
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                        {
-                            if (kInt8)
-                                mxi = max(mxi, static_cast<int32_t>(x[i]));
-                            else
-                                mx = fmaxf(mx, __uint_as_float(x[i]));
-                        }
-                    }
+                    int const q = i / kChunks;
+                    int const c = i % kChunks;
+                    if (IL)
+                        reinterpret_cast<uint4*>(outPtrIl(q, c / 2))[c % 2] = make_uint4(0, 0, 0, 0);
                     else
-                    {
+                        reinterpret_cast<uint4*>(outRow(q))[c] = make_uint4(0, 0, 0, 0);
+                }
+                continue;
+            }
+            int const nb = it.nb;
+            int const len = it.len;
+            for (int t = 0; t < it.nq; ++t)
+            {
+                uint32_t x[32];
+
+                // ---- pass A: row maximum (INT8: integer maximum, no conversions) ----
+                float mx = -INFINITY;
+                int32_t mxi = INT32_MIN;
 #pragma unroll
-                        for (int i = 0; i < 32; ++i)
+                for (int j = 0; j < kMaxBlocks; ++j)
+                {
+                    if (j < nb)
+                    {
+                        ok = ok && mbarWait(&sFull[j], (sBits >> j) & 1u, abortFlag, kWaitSoftmax);
+                        tcFenceAfter();
+                        tmemLoad32(tRow + colOf(j), x);
+                        tmemLoadWait32(x);
+                        int const limit = len - colOf(j);
+                        if (limit >= 32)
                         {
-                            if (i < limit)
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
                             {
                                 if (kInt8)
                                     mxi = max(mxi, static_cast<int32_t>(x[i]));
@@ -501,77 +597,37 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                                     mx = fmaxf(mx, __uint_as_float(x[i]));
                             }
                         }
-                    }
-                }
-            }
-            if (kInt8)
-                mx = mxi == INT32_MIN ? -INFINITY : static_cast<float>(mxi);
-            if (deferEpilogue && t > 0)
-                epilogue(t - 1, invPrev);
-            rowRed[sub * kQTile + r] = mx;
-            softmaxBarrier();
-            mx = fmaxf(fmaxf(rowRed[r], rowRed[kQTile + r]), fmaxf(rowRed[2 * kQTile + r], rowRed[3 * kQTile + r]));
-            float const mOff = mx * sl2;
-            float const mxMagic = kMagic + mx; // exact: both are integers below 2^24
-
-            // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < kMaxBlocks; ++j)
-            {
-                if (j < nb)
-                {
-                    tmemLoad32(tRow + colOf(j), x);
-                    tmemLoadWait32(x);
-                    int const limit = len - colOf(j);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                    {
-                        // INT8: (acc - max) is formed exactly (integers through the 2^23 trick, no conversion unit),
-                        // so the exponent carries a single rounding; FP16: one fused multiply-add.
-                        float e = kInt8 ? ex2Approx((__uint_as_float(x[i] + kMagicBits) - mxMagic) * sl2)
-                                        : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
-                        if (limit < 32 && i >= limit)
-                            e = 0.f;
-                        sum += e;
-                        x[i] = __float_as_uint(e);
-                    }
-                    if (kInt8)
-                    {
-                        tmemStore32(tRow + colOf(j), x);
-                    }
-                    else
-                    {
-                        ok = ok && acquireP(t, j);
-                        // FP16 P block = two [128 rows][64 keys] tiles of 128-byte rows; this thread owns 4 chunks of a row
-                        uint8_t* pRow = sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes + (sub >> 1) * (kQTile * 128) + r * 128;
-#pragma unroll
-                        for (int g = 0; g < 4; ++g)
+                        else
                         {
-                            float f[8];
 #pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                f[i] = __uint_as_float(x[g * 8 + i]);
-                            int const chunk = (sub & 1) * 4 + g;
-                            *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
+                            for (int i = 0; i < 32; ++i)
+                            {
+                                if (i < limit)
+                                {
+                                    if (kInt8)
+                                        mxi = max(mxi, static_cast<int32_t>(x[i]));
+                                    else
+                                        mx = fmaxf(mx, __uint_as_float(x[i]));
+                                }
+                            }
                         }
-                        fenceProxyAsync();
-                        tcFenceBefore();
-                        mbarArrive(&pReady[j]);
                     }
                 }
-            }
-            if (kInt8)
-                tmemStoreWait();
-            rowRed[4 * kQTile + sub * kQTile + r] = sum;
-            softmaxBarrier();
-            sum = (rowRed[4 * kQTile + r] + rowRed[5 * kQTile + r]) + (rowRed[6 * kQTile + r] + rowRed[7 * kQTile + r]);
-            float const inv = 1.f / sum;
+                if (kInt8)
+                    mx = mxi == INT32_MIN ? -INFINITY : static_cast<float>(mxi);
+                if (pending)
+                {
+                    epilogue(tiles - 1, pendDst, pendInv);
+                    pending = false;
+                }
+                rowRed[sub * kQTile + r] = mx;
+                softmaxBarrier();
+                mx = fmaxf(fmaxf(rowRed[r], rowRed[kQTile + r]), fmaxf(rowRed[2 * kQTile + r], rowRed[3 * kQTile + r]));
+                float const mOff = mx * sl2;
+                float const mxMagic = kMagic + mx; // exact: both are integers below 2^24
 
-            if (kInt8)
-            {
-                // ---- pass C (INT8): P_q = rni(p / sum * scale_softmax) ----
-                float const pq = inv * args.scaleSoftmax;
+                // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
+                float sum = 0.f;
 #pragma unroll
                 for (int j = 0; j < kMaxBlocks; ++j)
                 {
@@ -579,33 +635,98 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     {
                         tmemLoad32(tRow + colOf(j), x);
                         tmemLoadWait32(x);
-                        ok = ok && acquireP(t, j);
-                        uint8_t* pRow = sP + (nb <= 3 ? j : (j & 1)) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
+                        int const limit = len - colOf(j);
 #pragma unroll
-                        for (int g = 0; g < 2; ++g)
+                        for (int i = 0; i < 32; ++i)
                         {
-                            uint4 o;
-                            uint32_t* w = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                w[i] = packProb4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
-                                    __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
-                            int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
-                            *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
+                            // INT8: (acc - max) is formed exactly (integers through the 2^23 trick, no conversion unit),
+                            // so the exponent carries a single rounding; FP16: one fused multiply-add.
+                            float e = kInt8 ? ex2Approx((__uint_as_float(x[i] + kMagicBits) - mxMagic) * sl2)
+                                            : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
+                            if (limit < 32 && i >= limit)
+                                e = 0.f;
+                            sum += e;
+                            x[i] = __float_as_uint(e);
                         }
-                        fenceProxyAsync();
-                        tcFenceBefore();
-                        mbarArrive(&pReady[j]);
+                        if (kInt8)
+                        {
+                            tmemStore32(tRow + colOf(j), x);
+                        }
+                        else
+                        {
+                            ok = acquireP(j) && ok;
+                            // FP16 P block = two [128 rows][64 keys] tiles of 128-byte rows; this thread owns 4 chunks of a row
+                            uint8_t* pRow = sP + slotOf(j) * L::kPBytes + (sub >> 1) * (kQTile * 128) + r * 128;
+#pragma unroll
+                            for (int g = 0; g < 4; ++g)
+                            {
+                                float f[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    f[i] = __uint_as_float(x[g * 8 + i]);
+                                int const chunk = (sub & 1) * 4 + g;
+                                *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = packHalf8(f);
+                            }
+                            fenceProxyAsync();
+                            tcFenceBefore();
+                            mbarArrive(&pReady[j]);
+                        }
                     }
                 }
+                if (kInt8)
+                    tmemStoreWait();
+                rowRed[4 * kQTile + sub * kQTile + r] = sum;
+                softmaxBarrier();
+                sum = (rowRed[4 * kQTile + r] + rowRed[5 * kQTile + r]) + (rowRed[6 * kQTile + r] + rowRed[7 * kQTile + r]);
+                float const inv = 1.f / sum;
+
+                if (kInt8)
+                {
+                    // ---- pass C (INT8): P_q = rni(p / sum * scale_softmax) ----
+                    float const pq = inv * args.scaleSoftmax;
+#pragma unroll
+                    for (int j = 0; j < kMaxBlocks; ++j)
+                    {
+                        if (j < nb)
+                        {
+                            tmemLoad32(tRow + colOf(j), x);
+                            tmemLoadWait32(x);
+                            ok = acquireP(j) && ok;
+                            uint8_t* pRow = sP + slotOf(j) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
+#pragma unroll
+                            for (int g = 0; g < 2; ++g)
+                            {
+                                uint4 o;
+                                uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    w[i] = packProb4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
+                                        __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                                int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
+                                *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
+                            }
+                            fenceProxyAsync();
+                            tcFenceBefore();
+                            mbarArrive(&pReady[j]);
+                        }
+                    }
+                }
+                sBits ^= (1u << nb) - 1u; // every block of this tile used its sFull / pReady phase
+                int const q = t * kQTile + r;
+                T* const dst = q >= it.rows ? nullptr : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16);
+                ++tiles;
+                if (deferEpilogue)
+                {
+                    pending = true;
+                    pendDst = dst;
+                    pendInv = inv;
+                }
+                else
+                    epilogue(tiles - 1, dst, inv);
             }
-            if (deferEpilogue)
-                invPrev = inv;
-            else
-                epilogue(t, inv);
         }
-        if (deferEpilogue)
-            epilogue(nq - 1, invPrev);
+        if (pending)
+            epilogue(tiles - 1, pendDst, pendInv);
         tcFenceBefore();
     }
 
@@ -667,7 +788,9 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     MhaArgs args{p.B, p.S, p.num_heads, p.total, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
         p.scale_softmax, p.scale_bmm2, p.status_word};
-    dim3 const grid(p.num_heads, p.B);
+    // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
+    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
+    int const grid = static_cast<int>(items < smCount() ? items : smCount());
     kernel<<<grid, kMhaThreads, smem, stream>>>(map, args);
     return checkLaunch("mhaTcgen05Kernel");
 }
