@@ -80,8 +80,8 @@ struct MhaSmem
     {
         return pOffset(nb) + pSlots(nb) * kPBytes;
     }
-    // kFull[4] vFull[4] sFull[4] pReady[4] pFree[4] qFull qFree oFull oFree, tmem slot + abort flag, max / sum scratch
-    static constexpr int kBarrierBytes = (5 * kMaxBlocks + 4) * 8 + 16 + 8 * kQTile * 4;
+    // kFull[4] vFull[4] sFull[4] pReady[4] pFree[4] sFree[4] qFull qFree oFull oFree vFree, tmem slot + abort flag, max / sum scratch
+    static constexpr int kBarrierBytes = (6 * kMaxBlocks + 5) * 8 + 16 + 8 * kQTile * 4;
     static __host__ __device__ constexpr int dynamicBytes(int nb)
     {
         return barrierOffset(nb) + kBarrierBytes + 1024;
@@ -203,11 +203,13 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     uint64_t* sFull = bars + 2 * kMaxBlocks;     // [4] scores of block j complete        (once per tile using block j)
     uint64_t* pReady = bars + 3 * kMaxBlocks;    // [4] P_j written, 512 arrivals         (once per tile using block j)
     uint64_t* pFree = bars + 4 * kMaxBlocks;     // [4] PV product consumed P slot        (once per fill of the slot)
-    uint64_t* qFull = pFree + kMaxBlocks;        // Q tile landed                         (once per tile)
+    uint64_t* sFree = bars + 5 * kMaxBlocks;     // [4] softmax holds S_j in registers, 512 arrivals (once per tile using block j)
+    uint64_t* qFull = sFree + kMaxBlocks;        // Q tile landed                         (once per tile)
     uint64_t* qFree = qFull + 1;                 // all score MMAs of the tile done: Q slot (after an item's last tile: K) reusable
-    uint64_t* oFull = qFree + 1;                 // context accumulator complete          (once per tile; last tile: V reusable)
+    uint64_t* oFull = qFree + 1;                 // context accumulator complete          (once per tile)
     uint64_t* oFree = oFull + 1;                 // epilogue has read it, 512 arrivals    (once per tile)
-    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(oFree + 1);
+    uint64_t* vFree = oFree + 1;                 // all PV products of an item done: V reusable (once per item)
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(vFree + 1);
     volatile uint32_t* abortFlag = tmemSlot + 1;
     float* rowRed = reinterpret_cast<float*>(tmemSlot + 4); // [2][4][128]: max then sum, per 32-column owner
 
@@ -221,11 +223,15 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             mbarInit(&pReady[i], kSoftmaxThreads);
         }
         for (int i = 0; i < kMaxBlocks; ++i)
+        {
             mbarInit(&pFree[i], 1);
+            mbarInit(&sFree[i], kSoftmaxThreads);
+        }
         mbarInit(qFull, 1);
         mbarInit(qFree, 1);
         mbarInit(oFull, 1);
         mbarInit(oFree, kSoftmaxThreads);
+        mbarInit(vFree, 1);
         *abortFlag = 0;
         fenceBarrierInit();
         prefetchTensorMap(&mapQkv);
@@ -244,7 +250,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         if (lane == 0)
         {
             Item it;
-            uint32_t tiles = 0; // Q tiles requested so far
+            uint32_t tiles = 0;       // Q tiles requested so far
+            uint32_t itemsLoaded = 0; // items whose K / V have been requested
             bool ok = true;
             for (int item = nextWork(blockIdx.x, it); item < numItems && ok; item = nextWork(item + gridDim.x, it))
             {
@@ -272,9 +279,11 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                             mbarArriveExpectTx(&kFull[j], L::kTileBytes);
                             load(sK + j * L::kTileBytes, &kFull[j], 1, rowK + j * kKeyBlock);
                         }
-                        // the PV products of the previous item's last tile have read V
-                        if (tiles > 0)
-                            ok = mbarWait(oFull, (tiles - 1) & 1, abortFlag, kWaitStageFree);
+                        // The PV products of the previous item have read V. (Not oFull: this thread may run ahead of
+                        // or behind the per-tile barriers by more than one phase, and a parity wait is only meaningful
+                        // for the very next phase; vFree completes once per item, in step with this loop.)
+                        if (itemsLoaded > 0)
+                            ok = mbarWait(vFree, (itemsLoaded - 1) & 1, abortFlag, kWaitStageFree);
                         if (!ok)
                             break;
                         for (int j = 0; j < it.nb; ++j)
@@ -285,6 +294,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     }
                     ++tiles;
                 }
+                ++itemsLoaded;
             }
         }
     }
@@ -321,7 +331,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             }
             uint32_t qkTiles = 0;  // tiles whose scores have been issued
             uint32_t pvTiles = 0;  // tiles whose context has been issued
-            uint32_t kBits = 0, vBits = 0, pBits = 0; // parity per key block: K landed, V landed, P written
+            uint32_t kBits = 0, vBits = 0, pBits = 0, fBits = 0; // parity per key block: K landed, V landed, P written, S read
             // scores of key block j for the query tile whose Q is in shared memory; nbOf = key blocks of that tile's item
             auto issueScores = [&](int j, int nbOf) {
 #pragma unroll
@@ -376,7 +386,24 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     {
                         if (j < cur.nb && ok)
                         {
-                            if (t == 0)
+                            // Scores of the following tile for this key block first: they only need the softmax warps
+                            // to hold this tile's S_j in registers (sFree), not the finished P_j, and the next pass A
+                            // waits for them, while this tile's context is not read before the pass after.
+                            if (j < nbFollow && !oAliasesScores)
+                            {
+                                if (j == 0)
+                                    ok = mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
+                                if (ok && lastT)
+                                    ok = waitK(j);
+                                ok = ok && mbarWait(&sFree[j], (fBits >> j) & 1u, abortFlag, kWaitSoftmax);
+                                if (ok)
+                                {
+                                    tcFenceAfter();
+                                    issueScores(j, nbFollow);
+                                }
+                            }
+                            fBits ^= 1u << j; // the softmax warps complete this phase in every tile that uses block j
+                            if (ok && t == 0)
                             {
                                 ok = mbarWait(&vFull[j], (vBits >> j) & 1u, abortFlag, kWaitTmaFull);
                                 vBits ^= 1u << j;
@@ -398,19 +425,10 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                                 }
                                 tcCommit(&pFree[slotOf(j)]);
                                 if (j == cur.nb - 1)
-                                    tcCommit(oFull);
-                                // scores of the following tile for this key block: its columns were released by pReady[j]
-                                if (j < nbFollow && !oAliasesScores)
                                 {
-                                    if (j == 0)
-                                        ok = mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
-                                    if (ok && lastT)
-                                        ok = waitK(j);
-                                    if (ok)
-                                    {
-                                        tcFenceAfter();
-                                        issueScores(j, nbFollow);
-                                    }
+                                    tcCommit(oFull);
+                                    if (lastT)
+                                        tcCommit(vFree);
                                 }
                             }
                         }
@@ -635,6 +653,12 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     {
                         tmemLoad32(tRow + colOf(j), x);
                         tmemLoadWait32(x);
+                        if (!kInt8)
+                        {
+                            // the scores are in registers: their TMEM columns may take the next tile's scores
+                            tcFenceBefore();
+                            mbarArrive(&sFree[j]);
+                        }
                         int const limit = len - colOf(j);
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
@@ -691,6 +715,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         {
                             tmemLoad32(tRow + colOf(j), x);
                             tmemLoadWait32(x);
+                            tcFenceBefore();
+                            mbarArrive(&sFree[j]); // the parked exponentials are in registers: columns free for new scores
                             ok = acquireP(j) && ok;
                             uint8_t* pRow = sP + slotOf(j) * L::kPBytes + r * 128; // INT8 P block: [128 rows][128 keys]
 #pragma unroll
