@@ -217,6 +217,7 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
     int const wInRow = warp % WPR;
     int const chunksPerRow = ld / E;
     float const rld = 1.f / static_cast<float>(ld);
+    float const qLo = -128.f / qScale, qHi = 127.f / qScale; // qScale > 0 (checked by the caller)
 
     int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
@@ -240,6 +241,26 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
             int const c = (i * WPR + wInRow) * 32 + lane;
             uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
             uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
+            // the bias rides in the second FMA of the dequantising sum
+            float fbias[E];
+            if (HAS_BIAS && c < chunksPerRow)
+            {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    float f8[8];
+                    unpackHalf8(ldgKeep(bias + c * E + 8 * h), f8);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        fbias[8 * h + j] = f8[j];
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < E; ++j)
+                    fbias[j] = 0.f;
+            }
 #pragma unroll
             for (int w = 0; w < 4; ++w)
             {
@@ -248,19 +269,7 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
                 unpackChar4(bw[w], fb);
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
-                    x[i][4 * w + j] = dqIn * fa[j] + dqSkip * fb[j];
-            }
-            if (HAS_BIAS && c < chunksPerRow)
-            {
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                {
-                    float fb[8];
-                    unpackHalf8(ldgKeep(bias + c * E + 8 * h), fb);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        x[i][8 * h + j] += fb[j];
-                }
+                    x[i][4 * w + j] = fmaf(dqIn, fa[j], fmaf(dqSkip, fb[j], fbias[4 * w + j]));
             }
 #pragma unroll
             for (int j = 0; j < E; ++j)
@@ -299,9 +308,10 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
                     unpackHalf8(ldgKeep(beta + c * E + 8 * h), bt);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        y[j] = (g[j] * (x[i][8 * h + j] - mu) * rsigma + bt[j]) * qScale;
-                    ow[2 * h] = packChar4(y[0], y[1], y[2], y[3]);
-                    ow[2 * h + 1] = packChar4(y[4], y[5], y[6], y[7]);
+                        y[j] = fmaf(g[j] * rsigma, x[i][8 * h + j] - mu, bt[j]);
+                    // the output scale is folded into the rounding FMA of the pack
+                    ow[2 * h] = packChar4Scaled(y[0], y[1], y[2], y[3], qScale, qLo, qHi);
+                    ow[2 * h + 1] = packChar4Scaled(y[4], y[5], y[6], y[7], qScale, qLo, qHi);
                 }
                 stgStream(out + row * ld + c * E, o);
             }
@@ -586,6 +596,7 @@ extern "C" int32_t bert_b200_skip_layer_norm_dqq(void* stream, int32_t ld, int64
         return BERT_B200_OK;
     B200_REQUIRE(input && skip && beta && gamma && output, "skip_layer_norm_dqq: null pointer");
     B200_REQUIRE(ld % 16 == 0 && ld <= 16 * 32 * 4 * 8, "skip_layer_norm_dqq: ld=%d must be a multiple of 16, <= 16384", ld);
+    B200_REQUIRE(q_scale > 0.f, "skip_layer_norm_dqq: q_scale must be positive");
     B200_REQUIRE(aligned16(input) && aligned16(skip) && aligned16(output) && aligned16(beta) && aligned16(gamma)
             && (!bias || aligned16(bias)),
         "skip_layer_norm_dqq: pointers must be 16-byte aligned");
