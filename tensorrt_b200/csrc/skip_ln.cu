@@ -17,21 +17,25 @@ namespace
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 
-// Sums `v` over the WPR warps that share one row. `slot` is this row's scratch line in shared memory.
+// Sums `v` over the WPR warps that share one row. `slots` is this row's scratch in shared memory, two lines used
+// alternately (`turn` flips per call): a warp can only reach its next-but-one reduction after every warp of the row
+// has passed the barrier in between, so one barrier per reduction is enough. The barrier is a named one over just
+// the row's WPR warps (id 1 + row in CTA), not the whole CTA.
 template <int WPR>
-__device__ __forceinline__ float rowSum(float v, float* slot, int wInRow, int lane)
+__device__ __forceinline__ float rowSum(float v, float (*slots)[WPR > 1 ? WPR : 1], int rowInCta, int wInRow, int lane, int& turn)
 {
     v = warpSum(v);
     if (WPR == 1)
         return v;
+    float* const slot = slots[turn];
+    turn ^= 1;
     if (lane == 0)
         slot[wInRow] = v;
-    __syncthreads();
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + rowInCta), "n"(WPR * 32) : "memory");
     float t = 0.f;
 #pragma unroll
     for (int w = 0; w < WPR; ++w)
         t += slot[w];
-    __syncthreads();
     return t;
 }
 
@@ -77,7 +81,8 @@ __global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64
 {
     constexpr int E = Vec<T>::kElems;
     constexpr int kRowsPerCta = kWarpsPerCta / WPR;
-    __shared__ float red[kRowsPerCta][WPR > 1 ? WPR : 1];
+    __shared__ float red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
+    int turn = 0;
 
     int const lane = threadIdx.x & 31;
     int const warp = threadIdx.x >> 5;
@@ -128,7 +133,7 @@ __global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64
             for (int j = 0; j < E; ++j)
                 s += x[i][j];
         }
-        float const mu = rowSum<WPR>(s, red[rowInCta], wInRow, lane) * rld;
+        float const mu = rowSum<WPR>(s, red[rowInCta], rowInCta, wInRow, lane, turn) * rld;
         float q = 0.f;
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
@@ -144,7 +149,7 @@ __global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64
                 }
             }
         }
-        float const var = rowSum<WPR>(q, red[rowInCta], wInRow, lane) * rld;
+        float const var = rowSum<WPR>(q, red[rowInCta], rowInCta, wInRow, lane, turn) * rld;
         float const rsigma = rsqrtf(var + eps);
 
 #pragma unroll
@@ -209,7 +214,8 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
 {
     constexpr int E = 16;
     constexpr int kRowsPerCta = kWarpsPerCta / WPR;
-    __shared__ float red[kRowsPerCta][WPR > 1 ? WPR : 1];
+    __shared__ float red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
+    int turn = 0;
 
     int const lane = threadIdx.x & 31;
     int const warp = threadIdx.x >> 5;
@@ -275,7 +281,7 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
             for (int j = 0; j < E; ++j)
                 s += x[i][j];
         }
-        float const mu = rowSum<WPR>(s, red[rowInCta], wInRow, lane) * rld;
+        float const mu = rowSum<WPR>(s, red[rowInCta], rowInCta, wInRow, lane, turn) * rld;
         float q = 0.f;
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
@@ -291,7 +297,7 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
                 }
             }
         }
-        float const rsigma = rsqrtf(rowSum<WPR>(q, red[rowInCta], wInRow, lane) * rld + eps);
+        float const rsigma = rsqrtf(rowSum<WPR>(q, red[rowInCta], rowInCta, wInRow, lane, turn) * rld + eps);
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
@@ -499,6 +505,10 @@ int32_t dispatchSkipLn(cudaStream_t stream, int32_t ld, int64_t rows, T const* i
     int wpr = 1;
     while (chunks > 32 * 4 * wpr)
         wpr *= 2;
+    // Four chunks per lane and a single warp per row (128 chunks: 1024 halves) keeps too few rows in flight; two
+    // warps with two chunks each measured 20-28 % faster.
+    if (wpr == 1 && chunks > 32 * 3)
+        wpr = 2;
     int const cpl = (chunks + 32 * wpr - 1) / (32 * wpr);
 #define B200_SKIPLN_CASE(C, W)                                                                                         \
     if (cpl == C && wpr == W)                                                                                          \
@@ -507,6 +517,7 @@ int32_t dispatchSkipLn(cudaStream_t stream, int32_t ld, int64_t rows, T const* i
     B200_SKIPLN_CASE(2, 1)
     B200_SKIPLN_CASE(3, 1)
     B200_SKIPLN_CASE(4, 1)
+    B200_SKIPLN_CASE(2, 2)
     B200_SKIPLN_CASE(3, 2)
     B200_SKIPLN_CASE(4, 2)
     B200_SKIPLN_CASE(3, 4)
