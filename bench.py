@@ -70,12 +70,17 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+FC_DRAM_BYTES_PER_LAUNCH_INT8 = 69.4e6  # dram__bytes_read.sum + dram__bytes_write.sum, mean of QKV / out / FFN1 / FFN2
+
+
 def cpu_forward_rate(batch_hint=None, budget_s=15.0, steps=1, warmup=0):
     """Sequences/s of the FP32 torch-CPU port on a bounded sample (full 24 layers, S=384)."""
     import torch
 
     from oracle import cpu_encoder as ce
 
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its ranks; only rank 0 runs this)
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     p = ce.random_params(LAYERS, HIDDEN, HEADS, FFN, seed=0)
     g = torch.Generator().manual_seed(1)
 
@@ -189,6 +194,8 @@ def run_b200(args):
     if world > 1:
         import torch.distributed as dist
 
+        # stdout carries the one JSON line only: NCCL's banner / debug text (NCCL_DEBUG=VERSION or INFO) goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     import tensorrt_b200 as T
@@ -242,9 +249,12 @@ def run_b200(args):
             peak, src = 2 * peaks["tc_sustained"], f"2 x {peaks['source']} bf16 sustained (no measured INT8 figure)"
         else:
             peak, src = peaks["tc_sustained"], f"{peaks['source']} bf16 sustained"
-        return {"bound": "tensor", "kernel": "fcTcgen05Kernel (4 FC shapes per layer)", "achieved": achieved, "peak": peak,
+        # DRAM bytes per FC launch from one `ncu --set full` capture of the four launches of a layer at this batch
+        # (profiles/fc_pair_int8_bert_large_layer_fullset.md); no capture exists for FP16 or other batch sizes
+        traffic = FC_DRAM_BYTES_PER_LAUNCH_INT8 if (name == "int8" and BATCH == 64) else None
+        return {"bound": "tensor", "kernel": "fcTcgen05PairKernel (4 FC shapes per layer)", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s" if name == "fp16" else "TOP/s", "frac": achieved / peak if achieved else None,
-                "traffic": None, "peak_source": src, "launches_per_step": fc_n,
+                "traffic": traffic, "peak_source": src, "launches_per_step": fc_n,
                 "flops_per_launch_avg": flops_per_forward / max(fc_n, 1), "ms_per_launch_avg": fc_ms / max(fc_n, 1)}
 
     def breakdown(name):
