@@ -157,26 +157,34 @@ def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, profile_ste
 
 
 def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
-    """Same step through the host-buffer entry point: H2D of ids / segment ids / cu_seqlens from pinned memory,
-    forward, D2H of the FP16 hidden states into pinned memory, stream synchronise - all inside the timed region."""
+    """Same step through the host-buffer entry point of the C ABI (the pipelined form a serving loop uses): every step
+    copies ids / segment ids / cu_seqlens from pinned host memory, runs the encoder and copies the FP16 hidden states
+    into pinned host memory. The output copy of step i runs on a second stream and overlaps step i + 1 (two
+    alternating output buffers); the timed region ends when the last copy has landed."""
     import torch
 
     ids_h, seg_h, cu_h = ids.cpu().pin_memory(), seg.cpu().pin_memory(), cu.cpu().pin_memory()
-    out_h = torch.empty(out_dev.shape, dtype=torch.float16).pin_memory()
-    for _ in range(warmup):
-        enc.forward_host(ids_h, seg_h, cu_h, SEQ, out_dev, out_h)
+    outs_dev = [out_dev, torch.empty_like(out_dev)]
+    outs_h = [torch.empty(out_dev.shape, dtype=torch.float16).pin_memory() for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    cur = torch.cuda.current_stream()
+    for i in range(warmup):
+        enc.forward_host_async(ids_h, seg_h, cu_h, SEQ, outs_dev[i & 1], outs_h[i & 1], copy_stream, i & 1)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(steps):
-        enc.forward_host(ids_h, seg_h, cu_h, SEQ, out_dev, out_h)
+    for i in range(steps):
+        enc.forward_host_async(ids_h, seg_h, cu_h, SEQ, outs_dev[i & 1], outs_h[i & 1], copy_stream, i & 1)
+    cur.wait_stream(copy_stream)  # the timed region includes the last device-to-host copy
     e1.record()
+    enc.wait_host(0)
+    enc.wait_host(1)
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     h2d = ids_h.numel() * 4 + seg_h.numel() * 4 + cu_h.numel() * 4
-    d2h = out_h.numel() * 2
+    d2h = outs_h[0].numel() * 2
     return ms, h2d, d2h
 
 

@@ -9,8 +9,9 @@
  *  - Plain pointers and sizes only. `stream` is a cudaStream_t passed as void*.
  *  - All data pointers are DEVICE pointers unless the name ends in `_host`.
  *  - Functions enqueue work on `stream` and return immediately: they never allocate device
- *    memory, never synchronise and never touch another device (bert_b200_encoder_forward_host
- *    is the documented exception: it copies host buffers and synchronises the stream).
+ *    memory, never synchronise and never touch another device (the bert_b200_encoder_*_host
+ *    functions are the documented exception: they copy host buffers; _forward_host and
+ *    _wait_host block the calling thread).
  *  - Return value: BERT_B200_OK (0) on success, otherwise a bert_b200_status; the reason is
  *    available from bert_b200_last_error() (thread local). Nothing throws, traps, resets the
  *    device or exits the process.
@@ -395,6 +396,22 @@ BERT_B200_API int32_t bert_b200_encoder_forward_host(bert_b200_encoder* enc, voi
     int32_t max_seqlen, int32_t const* input_ids_host, int32_t const* segment_ids_host,
     int32_t const* cu_seqlens_host, void* workspace, int64_t workspace_bytes, void* output_dev,
     void* output_host);
+
+/*
+ * Pipelined form of the host interface for a serving loop: nothing is synchronised. The encoder runs on
+ * `stream`; the copy of the FP16 output into output_host runs on `copy_stream` (a different stream) as soon as
+ * the encoder has finished, so it overlaps the next call's kernels. `slot` (0 or 1) names one of two
+ * (output_dev, output_host) buffer pairs the caller alternates between: a call first makes `stream` wait for
+ * the previous copy out of the same slot. bert_b200_encoder_wait_host(enc, slot) blocks the calling thread
+ * until that slot's output_host is complete. The host id buffers must stay valid until then; the two events
+ * per slot are created by the first call that uses the slot (make it outside stream capture).
+ * ref: none - the reference leaves host transfers to the application (samples/common/buffers.h).
+ */
+BERT_B200_API int32_t bert_b200_encoder_forward_host_async(bert_b200_encoder* enc, void* stream, void* copy_stream,
+    int32_t slot, int32_t B, int32_t total, int32_t max_seqlen, int32_t const* input_ids_host,
+    int32_t const* segment_ids_host, int32_t const* cu_seqlens_host, void* workspace, int64_t workspace_bytes,
+    void* output_dev, void* output_host);
+BERT_B200_API int32_t bert_b200_encoder_wait_host(bert_b200_encoder* enc, int32_t slot);
 
 #ifdef __cplusplus
 }

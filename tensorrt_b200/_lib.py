@@ -78,6 +78,8 @@ SIGNATURES = {
     "bert_b200_encoder_static_workspace_limit": (i64, []),
     "bert_b200_encoder_forward_static": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp]),
     "bert_b200_encoder_forward_host": (i32, [vp, vp, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp]),
+    "bert_b200_encoder_forward_host_async": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, i64, vp, vp]),
+    "bert_b200_encoder_wait_host": (i32, [vp, i32]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():

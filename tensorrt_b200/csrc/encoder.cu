@@ -26,11 +26,22 @@ struct bert_b200_encoder
     int32_t timedLaunches = 0;
     // optional calibration: device array [num_layers][8] receiving |x| maxima
     float* amaxDev = nullptr;
+    // pipelined host interface: per slot "encoder output complete" and "output copied to the host" (created on first use)
+    cudaEvent_t computeDone[2] = {nullptr, nullptr};
+    cudaEvent_t copyDone[2] = {nullptr, nullptr};
+    bool slotUsed[2] = {false, false};
 
     ~bert_b200_encoder()
     {
         for (cudaEvent_t e : events)
             cudaEventDestroy(e);
+        for (int i = 0; i < 2; ++i)
+        {
+            if (computeDone[i])
+                cudaEventDestroy(computeDone[i]);
+            if (copyDone[i])
+                cudaEventDestroy(copyDone[i]);
+        }
     }
 };
 
@@ -450,6 +461,70 @@ extern "C" int32_t bert_b200_encoder_forward_host(bert_b200_encoder* enc, void* 
         e = cudaStreamSynchronize(s);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host: D2H copy: %s", cudaGetErrorString(e));
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_forward_host_async(bert_b200_encoder* enc, void* stream, void* copy_stream,
+    int32_t slot, int32_t B, int32_t total, int32_t max_seqlen, int32_t const* input_ids_host,
+    int32_t const* segment_ids_host, int32_t const* cu_seqlens_host, void* workspace, int64_t workspace_bytes,
+    void* output_dev, void* output_host)
+{
+    Workspace w{};
+    int32_t st = checkForward(enc, B, total, max_seqlen, input_ids_host, segment_ids_host, cu_seqlens_host, workspace,
+        workspace_bytes, output_dev, &w);
+    if (st != BERT_B200_OK)
+        return st;
+    B200_REQUIRE(output_host != nullptr, "encoder_forward_host_async: null output_host");
+    B200_REQUIRE(slot == 0 || slot == 1, "encoder_forward_host_async: slot %d (0 or 1)", slot);
+    B200_REQUIRE(stream != copy_stream, "encoder_forward_host_async: the copy stream must differ from the compute stream");
+    auto s = static_cast<cudaStream_t>(stream);
+    auto cs = static_cast<cudaStream_t>(copy_stream);
+    cudaError_t e = cudaSuccess;
+    if (!enc->computeDone[slot])
+    {
+        e = cudaEventCreateWithFlags(&enc->computeDone[slot], cudaEventDisableTiming);
+        if (e == cudaSuccess)
+            e = cudaEventCreateWithFlags(&enc->copyDone[slot], cudaEventDisableTiming);
+        if (e != cudaSuccess)
+            B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host_async: event: %s", cudaGetErrorString(e));
+    }
+    // the previous copy out of this slot's device buffer must have finished before the encoder overwrites it
+    if (enc->slotUsed[slot])
+        e = cudaStreamWaitEvent(s, enc->copyDone[slot], 0);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w.ids, input_ids_host, sizeof(int32_t) * total, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w.seg, segment_ids_host, sizeof(int32_t) * total, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(w.cu, cu_seqlens_host, sizeof(int32_t) * (B + 1), cudaMemcpyHostToDevice, s);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host_async: H2D copy: %s", cudaGetErrorString(e));
+    st = forwardImpl(enc, s, B, total, max_seqlen, w.ids, w.seg, w.cu, w, output_dev);
+    if (st != BERT_B200_OK)
+        return st;
+    e = cudaEventRecord(enc->computeDone[slot], s);
+    if (e == cudaSuccess)
+        e = cudaStreamWaitEvent(cs, enc->computeDone[slot], 0);
+    if (e == cudaSuccess)
+        e = cudaMemcpyAsync(output_host, output_dev, sizeof(__half) * static_cast<size_t>(total) * enc->cfg.hidden_size,
+            cudaMemcpyDeviceToHost, cs);
+    if (e == cudaSuccess)
+        e = cudaEventRecord(enc->copyDone[slot], cs);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_host_async: D2H copy: %s", cudaGetErrorString(e));
+    enc->slotUsed[slot] = true;
+    return BERT_B200_OK;
+}
+
+extern "C" int32_t bert_b200_encoder_wait_host(bert_b200_encoder* enc, int32_t slot)
+{
+    B200_REQUIRE(enc != nullptr, "encoder_wait_host: null encoder");
+    B200_REQUIRE(slot == 0 || slot == 1, "encoder_wait_host: slot %d (0 or 1)", slot);
+    if (!enc->slotUsed[slot])
+        return BERT_B200_OK;
+    cudaError_t const e = cudaEventSynchronize(enc->copyDone[slot]);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_wait_host: %s", cudaGetErrorString(e));
     return BERT_B200_OK;
 }
 

@@ -132,6 +132,26 @@ class BertEncoder:
               "encoder_forward_host")
         return out_h
 
+    def forward_host_async(self, ids_h, seg_h, cu_h, max_seqlen, out_dev, out_h, copy_stream, slot):
+        """Pipelined form of forward_host: nothing is synchronised. The encoder runs on the current stream, the copy
+        of the result into the pinned host tensor out_h on `copy_stream` (a torch.cuda.Stream), overlapping the next
+        call. `slot` (0 / 1) names one of two (out_dev, out_h) pairs used alternately; wait_host(slot) blocks until
+        that slot's out_h is complete."""
+        total, B = ids_h.shape[0], cu_h.shape[0] - 1
+        ws = self._workspace(total, B)
+        self._last = (total, B)
+        s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        check(lib.bert_b200_encoder_forward_host_async(self._h, s, C.c_void_p(copy_stream.cuda_stream), slot, B, total,
+                                                       max_seqlen, C.c_void_p(ids_h.data_ptr()),
+                                                       C.c_void_p(seg_h.data_ptr()), C.c_void_p(cu_h.data_ptr()),
+                                                       C.c_void_p(ws.data_ptr()), self._ws_bytes,
+                                                       C.c_void_p(out_dev.data_ptr()), C.c_void_p(out_h.data_ptr())),
+              "encoder_forward_host_async")
+        return out_h
+
+    def wait_host(self, slot):
+        check(lib.bert_b200_encoder_wait_host(self._h, slot), "encoder_wait_host")
+
     def enable_timing(self, on=True):
         """Bracket every kernel of forward() with CUDA events (see read_timing)."""
         check(lib.bert_b200_encoder_enable_timing(self._h, 1 if on else 0), "encoder_enable_timing")

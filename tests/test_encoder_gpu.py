@@ -76,3 +76,41 @@ def test_encoder_int8(cuda, lengths):
     cos_fp = float((out * ref_fp).sum() / np.sqrt((out * out).sum() * (ref_fp * ref_fp).sum()))
     assert cos_fp > 0.99, cos_fp
     enc.close()
+
+
+def test_forward_host_async_matches_forward_host(cuda):
+    """The pipelined host interface (two alternating output slots, copy on a second stream) returns what the
+    synchronous one returns, for several steps in flight and different inputs per step."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(11)
+    p = O.make_bert_params(rng, 2, 256, 4, 1024, vocab=1000)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    B, S = 6, 96
+    lengths = rng.integers(10, S + 1, size=B).astype(np.int32)
+    cu = O.cu_seqlens(lengths)
+    total = int(cu[-1])
+    steps = 5
+    ids = [torch.from_numpy(rng.integers(0, 1000, size=total).astype(np.int32)).pin_memory() for _ in range(steps)]
+    seg = torch.from_numpy(rng.integers(0, 2, size=total).astype(np.int32)).pin_memory()
+    cu_h = torch.from_numpy(cu).pin_memory()
+    out_dev = [torch.empty((total, 256), dtype=torch.float16, device=cuda) for _ in range(2)]
+    want = []
+    for i in range(steps):
+        out_h = torch.empty((total, 256), dtype=torch.float16).pin_memory()
+        enc.forward_host(ids[i], seg, cu_h, S, out_dev[0], out_h)
+        want.append(out_h.clone())
+    copy_stream = torch.cuda.Stream()
+    outs_h = [torch.empty((total, 256), dtype=torch.float16).pin_memory() for _ in range(2)]
+    got = []
+    for i in range(steps):
+        if i >= 2:  # the slot is about to be reused: collect its previous result first
+            enc.wait_host(i & 1)
+            got.append(outs_h[i & 1].clone())
+        enc.forward_host_async(ids[i], seg, cu_h, S, out_dev[i & 1], outs_h[i & 1], copy_stream, i & 1)
+    for i in range(steps - 2, steps):
+        enc.wait_host(i & 1)
+        got.append(outs_h[i & 1].clone())
+    for i in range(steps):
+        assert torch.equal(got[i], want[i]), i
+    enc.close()
