@@ -3,8 +3,8 @@ lie in the TensorRT-OSS tree (never copied), plus oracle/ref_shim.cu. Test infra
 
     python oracle/build_ref.py [--force]
 
-Needs the reference tree (REFERENCE_ROOT, default /root/reference) and nvcc; without the tree an existing library is
-kept and nothing is built. The reference's build system is not run: each source is compiled directly.
+Needs a checkout of the reference tree (environment variable REFERENCE_ROOT, else the build machine's default
+location below) and nvcc; without the tree an existing library is kept and nothing is built. The reference's build system is not run: each source is compiled directly.
 """
 from __future__ import annotations
 
