@@ -1516,6 +1516,8 @@ PLUGIN_API nvinfer1::IPluginCreatorInterface* const* getCreators(int32_t& nbCrea
     std::call_once(once, [] {
         for (CreatorBase* c : allCreators())
             list.push_back(c);
+        for (nvinfer1::IPluginCreatorInterface* c : allLegacyCreators())
+            list.push_back(c);
     });
     nbCreators = static_cast<int32_t>(list.size());
     return list.data();
@@ -1539,6 +1541,12 @@ PLUGIN_API bool initLibNvInferPlugins(void* logger, char const* libNamespace)
     for (CreatorBase* c : allCreators())
     {
         c->setPluginNamespace(libNamespace ? libNamespace : "");
+        if (fn && fn())
+            ok = fn()->registerCreator(*c, libNamespace ? libNamespace : "") && ok;
+    }
+    for (nvinfer1::IPluginCreatorInterface* c : allLegacyCreators())
+    {
+        static_cast<nvinfer1::IPluginCreator*>(c)->setPluginNamespace(libNamespace ? libNamespace : "");
         if (fn && fn())
             ok = fn()->registerCreator(*c, libNamespace ? libNamespace : "") && ok;
     }

@@ -99,6 +99,29 @@ T* capability(nvinfer1::IPluginV3* p, nvinfer1::PluginCapabilityType type)
 
 HARNESS_API nvinfer1::IPluginCreatorInterface* const* getCreators(int32_t& nbCreators);
 
+namespace
+{
+bool isLegacy(nvinfer1::IPluginCreatorInterface* c)
+{
+    return std::strcmp(c->getInterfaceInfo().kind, "PLUGIN CREATOR_V1") == 0;
+}
+
+nvinfer1::IPluginCreator* legacyCreator(char const* name, char const* version)
+{
+    int32_t n = 0;
+    auto* const* list = getCreators(n);
+    for (int32_t i = 0; i < n; ++i)
+    {
+        if (!isLegacy(list[i]))
+            continue;
+        auto* c = static_cast<nvinfer1::IPluginCreator*>(list[i]);
+        if (std::strcmp(c->getPluginName(), name) == 0 && std::strcmp(c->getPluginVersion(), version) == 0)
+            return c;
+    }
+    return nullptr;
+}
+} // namespace
+
 HARNESS_API int32_t bert_b200_harness_num_creators()
 {
     int32_t n = 0;
@@ -113,6 +136,15 @@ HARNESS_API int32_t bert_b200_harness_creator_info(int32_t i, char const** name,
     auto* const* list = getCreators(n);
     if (i < 0 || i >= n)
         return 1;
+    if (isLegacy(list[i]))
+    {
+        auto* c = static_cast<nvinfer1::IPluginCreator*>(list[i]);
+        *name = c->getPluginName();
+        *version = c->getPluginVersion();
+        *ns = c->getPluginNamespace();
+        *nbFields = c->getFieldNames()->nbFields;
+        return 0;
+    }
     auto* c = static_cast<nvinfer1::IPluginCreatorV3One*>(list[i]);
     *name = c->getPluginName();
     *version = c->getPluginVersion();
@@ -121,13 +153,22 @@ HARNESS_API int32_t bert_b200_harness_creator_info(int32_t i, char const** name,
     return 0;
 }
 
+// 1 if creator i is an IPluginCreator (legacy IPluginV2DynamicExt plugins), 0 if IPluginCreatorV3One
+HARNESS_API int32_t bert_b200_harness_creator_is_legacy(int32_t i)
+{
+    int32_t n = 0;
+    auto* const* list = getCreators(n);
+    return i >= 0 && i < n ? (isLegacy(list[i]) ? 1 : 0) : -1;
+}
+
 HARNESS_API char const* bert_b200_harness_creator_field_name(int32_t i, int32_t f)
 {
     int32_t n = 0;
     auto* const* list = getCreators(n);
     if (i < 0 || i >= n)
         return nullptr;
-    auto const* fc = static_cast<nvinfer1::IPluginCreatorV3One*>(list[i])->getFieldNames();
+    auto const* fc = isLegacy(list[i]) ? static_cast<nvinfer1::IPluginCreator*>(list[i])->getFieldNames()
+                                       : static_cast<nvinfer1::IPluginCreatorV3One*>(list[i])->getFieldNames();
     return f >= 0 && f < fc->nbFields ? fc->fields[f].name : nullptr;
 }
 
@@ -138,6 +179,8 @@ HARNESS_API nvinfer1::IPluginV3* bert_b200_harness_create(
     auto* const* list = getCreators(n);
     for (int32_t i = 0; i < n; ++i)
     {
+        if (isLegacy(list[i]))
+            continue;
         auto* c = static_cast<nvinfer1::IPluginCreatorV3One*>(list[i]);
         if (std::strcmp(c->getPluginName(), name) == 0 && std::strcmp(c->getPluginVersion(), version) == 0)
             return c->createPlugin("harness_layer", fc, static_cast<nvinfer1::TensorRTPhase>(phase));
@@ -253,4 +296,113 @@ HARNESS_API nvinfer1::PluginFieldCollection const* bert_b200_harness_serialize(n
 {
     auto* rt = capability<nvinfer1::IPluginV3OneRuntime>(p, nvinfer1::PluginCapabilityType::kRUNTIME);
     return rt ? rt->getFieldsToSerialize() : nullptr;
+}
+
+// ---- legacy IPluginV2DynamicExt objects: the calls the builder and the runtime make on them ----------------------
+
+using LegacyPlugin = nvinfer1::IPluginV2DynamicExt;
+
+HARNESS_API LegacyPlugin* bert_b200_harness_legacy_create(char const* name, char const* version, nvinfer1::PluginFieldCollection const* fc)
+{
+    auto* c = legacyCreator(name, version);
+    return c ? static_cast<LegacyPlugin*>(c->createPlugin("harness_layer", fc)) : nullptr;
+}
+
+HARNESS_API LegacyPlugin* bert_b200_harness_legacy_deserialize(char const* name, char const* version, void const* data, int64_t length)
+{
+    auto* c = legacyCreator(name, version);
+    return c ? static_cast<LegacyPlugin*>(c->deserializePlugin("harness_layer", data, static_cast<size_t>(length))) : nullptr;
+}
+
+HARNESS_API void bert_b200_harness_legacy_destroy(LegacyPlugin* p)
+{
+    if (p)
+        p->destroy();
+}
+
+HARNESS_API LegacyPlugin* bert_b200_harness_legacy_clone(LegacyPlugin* p)
+{
+    return p ? p->clone() : nullptr;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_info(LegacyPlugin* p, char const** type, char const** version, char const** ns)
+{
+    if (!p)
+        return 1;
+    *type = p->getPluginType();
+    *version = p->getPluginVersion();
+    *ns = p->getPluginNamespace();
+    return 0;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_nb_outputs(LegacyPlugin* p)
+{
+    return p ? p->getNbOutputs() : -1;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_supports_format(
+    LegacyPlugin* p, int32_t pos, nvinfer1::PluginTensorDesc const* inOut, int32_t nbInputs, int32_t nbOutputs)
+{
+    return p ? (p->supportsFormatCombination(pos, inOut, nbInputs, nbOutputs) ? 1 : 0) : -1;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_output_dims(
+    LegacyPlugin* p, int32_t outputIndex, nvinfer1::Dims const* inputs, int32_t nbInputs, nvinfer1::Dims* output)
+{
+    if (!p || nbInputs > 8)
+        return 1;
+    ExprBuilder eb;
+    nvinfer1::DimsExprs in[8];
+    for (int32_t i = 0; i < nbInputs; ++i)
+    {
+        in[i].nbDims = inputs[i].nbDims;
+        for (int32_t k = 0; k < inputs[i].nbDims; ++k)
+            in[i].d[k] = eb.constant(inputs[i].d[k]);
+    }
+    nvinfer1::DimsExprs const out = p->getOutputDimensions(outputIndex, in, nbInputs, eb);
+    if (out.nbDims < 0)
+        return 2;
+    output->nbDims = out.nbDims;
+    for (int32_t k = 0; k < out.nbDims; ++k)
+        output->d[k] = out.d[k]->getConstantValue();
+    return 0;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_output_type(LegacyPlugin* p, int32_t index, int32_t const* inTypes, int32_t nbInputs)
+{
+    return p ? static_cast<int32_t>(p->getOutputDataType(index, reinterpret_cast<nvinfer1::DataType const*>(inTypes), nbInputs)) : -1;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_configure(LegacyPlugin* p, nvinfer1::DynamicPluginTensorDesc const* in, int32_t nbInputs,
+    nvinfer1::DynamicPluginTensorDesc const* out, int32_t nbOutputs)
+{
+    if (!p)
+        return 1;
+    p->configurePlugin(in, nbInputs, out, nbOutputs);
+    return 0;
+}
+
+HARNESS_API int64_t bert_b200_harness_legacy_workspace_size(LegacyPlugin* p, nvinfer1::PluginTensorDesc const* in, int32_t nbInputs,
+    nvinfer1::PluginTensorDesc const* out, int32_t nbOutputs)
+{
+    return p ? static_cast<int64_t>(p->getWorkspaceSize(in, nbInputs, out, nbOutputs)) : -1;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_enqueue(LegacyPlugin* p, nvinfer1::PluginTensorDesc const* inDesc,
+    nvinfer1::PluginTensorDesc const* outDesc, void const* const* inputs, void* const* outputs, void* workspace, void* stream)
+{
+    return p ? p->enqueue(inDesc, outDesc, inputs, outputs, workspace, static_cast<cudaStream_t>(stream)) : 1;
+}
+
+HARNESS_API int64_t bert_b200_harness_legacy_serialization_size(LegacyPlugin* p)
+{
+    return p ? static_cast<int64_t>(p->getSerializationSize()) : -1;
+}
+
+HARNESS_API int32_t bert_b200_harness_legacy_serialize(LegacyPlugin* p, void* buffer)
+{
+    if (!p || !buffer)
+        return 1;
+    p->serialize(buffer);
+    return 0;
 }

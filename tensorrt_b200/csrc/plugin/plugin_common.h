@@ -284,4 +284,7 @@ protected:
 // Every creator of this library, in registration order.
 std::vector<CreatorBase*> const& allCreators();
 
+// The creators of the legacy IPluginV2DynamicExt versions (legacy_plugins.cpp), each an nvinfer1::IPluginCreator.
+std::vector<nvinfer1::IPluginCreatorInterface*> const& allLegacyCreators();
+
 } // namespace bert_b200_plugin

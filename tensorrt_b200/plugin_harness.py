@@ -198,3 +198,98 @@ class Plugin:
 
     def serialize(self) -> dict:
         return read_fields(plib.bert_b200_harness_serialize(C.c_void_p(self.h)))
+
+
+# ---- legacy IPluginV2DynamicExt objects -------------------------------------------------------------------------
+for _n in ("legacy_create", "legacy_deserialize", "legacy_clone"):
+    getattr(plib, "bert_b200_harness_" + _n).restype = C.c_void_p
+plib.bert_b200_harness_legacy_create.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(PluginFieldCollection)]
+plib.bert_b200_harness_legacy_deserialize.argtypes = [C.c_char_p, C.c_char_p, C.c_void_p, C.c_int64]
+plib.bert_b200_harness_legacy_clone.argtypes = [C.c_void_p]
+plib.bert_b200_harness_legacy_destroy.argtypes = [C.c_void_p]
+plib.bert_b200_harness_legacy_workspace_size.restype = C.c_int64
+plib.bert_b200_harness_legacy_serialization_size.restype = C.c_int64
+plib.bert_b200_harness_legacy_serialization_size.argtypes = [C.c_void_p]
+
+
+def legacy_creators():
+    """[(name, version)] of the IPluginCreator (legacy plugin) entries getCreators() returns."""
+    res = []
+    for i, (name, ver, _, _) in enumerate(creators()):
+        if plib.bert_b200_harness_creator_is_legacy(i) == 1:
+            res.append((name, ver))
+    return res
+
+
+class LegacyPlugin:
+    """An IPluginV2DynamicExt object of a legacy plugin version, created from fields or from a serialised buffer."""
+
+    def __init__(self, name, version, items=None, serialized: bytes | None = None, handle=None):
+        self.name, self.version = name, version
+        if handle is None:
+            if serialized is not None:
+                self._buf = C.create_string_buffer(serialized, len(serialized))
+                handle = plib.bert_b200_harness_legacy_deserialize(name.encode(), version.encode(), self._buf, len(serialized))
+            else:
+                self._fc = FieldCollection(items)
+                handle = plib.bert_b200_harness_legacy_create(name.encode(), version.encode(), C.byref(self._fc.fc))
+        self.h = handle
+
+    @property
+    def ok(self):
+        return bool(self.h)
+
+    def close(self):
+        if self.h:
+            plib.bert_b200_harness_legacy_destroy(C.c_void_p(self.h))
+            self.h = None
+
+    def clone(self):
+        return LegacyPlugin(self.name, self.version, handle=plib.bert_b200_harness_legacy_clone(C.c_void_p(self.h)))
+
+    def info(self):
+        t, ver, ns = C.c_char_p(), C.c_char_p(), C.c_char_p()
+        plib.bert_b200_harness_legacy_info(C.c_void_p(self.h), C.byref(t), C.byref(ver), C.byref(ns))
+        return t.value.decode(), ver.value.decode(), ns.value.decode()
+
+    def nb_outputs(self):
+        return plib.bert_b200_harness_legacy_nb_outputs(C.c_void_p(self.h))
+
+    def supports(self, pos, descs, nb_in, nb_out):
+        arr = (PluginTensorDesc * len(descs))(*descs)
+        return plib.bert_b200_harness_legacy_supports_format(C.c_void_p(self.h), pos, arr, nb_in, nb_out) == 1
+
+    def output_dims(self, index, in_shapes):
+        ins = (Dims * len(in_shapes))(*[make_dims(s) for s in in_shapes])
+        out = Dims()
+        st = plib.bert_b200_harness_legacy_output_dims(C.c_void_p(self.h), index, ins, len(in_shapes), C.byref(out))
+        return None if st != 0 else tuple(out.d[i] for i in range(out.nbDims))
+
+    def output_type(self, index, in_types):
+        it = (C.c_int32 * len(in_types))(*in_types)
+        return plib.bert_b200_harness_legacy_output_type(C.c_void_p(self.h), index, it, len(in_types))
+
+    def configure(self, ins, outs):
+        a = (DynamicPluginTensorDesc * len(ins))(*ins)
+        b = (DynamicPluginTensorDesc * len(outs))(*outs)
+        return plib.bert_b200_harness_legacy_configure(C.c_void_p(self.h), a, len(ins), b, len(outs))
+
+    def workspace_size(self, ins, outs):
+        a = (PluginTensorDesc * len(ins))(*ins)
+        b = (PluginTensorDesc * len(outs))(*outs)
+        return plib.bert_b200_harness_legacy_workspace_size(C.c_void_p(self.h), a, len(ins), b, len(outs))
+
+    def enqueue(self, in_descs, out_descs, in_ptrs, out_ptrs, workspace=None, stream=None):
+        a = (PluginTensorDesc * len(in_descs))(*in_descs)
+        b = (PluginTensorDesc * len(out_descs))(*out_descs)
+        ip = (C.c_void_p * len(in_ptrs))(*in_ptrs)
+        op = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        return plib.bert_b200_harness_legacy_enqueue(C.c_void_p(self.h), a, b, ip, op, C.c_void_p(workspace or 0),
+                                                     C.c_void_p(stream or 0))
+
+    def serialize(self) -> bytes:
+        n = plib.bert_b200_harness_legacy_serialization_size(C.c_void_p(self.h))
+        buf = C.create_string_buffer(int(n))
+        st = plib.bert_b200_harness_legacy_serialize(C.c_void_p(self.h), buf)
+        assert st == 0
+        return bytes(buf.raw)

@@ -25,7 +25,10 @@ def test_creator_inventory():
     got = {(n, v) for n, v, ns, _ in H.creators()}
     want = {(EMB, "4"), (EMB, "5"), (EMB, "6"), (QKV, "4"), (QKV, "5"), (QKV, "6"), (SKIP, "5"), (SKIP, "6"),
             (SKIP, "7"), (SKIP, "8"), (FC, "1")}
-    assert got == want
+    legacy = {(QKV, "1"), (QKV, "2"), (QKV, "3"), (EMB, "1"), (EMB, "2"), (EMB, "3"), (SKIP, "1"), (SKIP, "2"),
+              (SKIP, "3"), (SKIP, "4")}
+    assert got == want | legacy
+    assert set(H.legacy_creators()) == legacy
     assert all(ns == "" for _, _, ns, _ in H.creators())
     fields = {(n, v): f for n, v, _, f in H.creators()}
     assert set(fields[(QKV, "4")]) == {"type_id", "hidden_size", "num_heads", "has_mask", "dq_probs"}
