@@ -6,8 +6,9 @@
 //       ref: plugin/bertQKVToContextPlugin/qkvToContextPlugin.cpp, qkvToContextInt8InterleavedPlugin.cpp
 //   CustomSkipLayerNormPluginDynamic  "5" (fixed), "6" (any rank), "7" / "8" (INT8 CHW32-interleaved HFace / MTron)
 //       ref: plugin/skipLayerNormPlugin/skipLayerNormPlugin.cpp, skipLayerNormInt8InterleavedPlugin.cpp
-//   CustomFCPluginDynamic             "1"  ref: plugin/fcPlugin/fcPlugin.cpp (IPluginV2DynamicExt there; same name,
-//       version and fields here on the V3 interfaces, plus optional bias / activation / INT8 extension fields)
+//   CustomFCPluginDynamic             "2"  the fields of the reference's version 1 (plugin/fcPlugin/fcPlugin.cpp, an
+//       IPluginV2DynamicExt) on the V3 interfaces, plus optional bias / activation / INT8 extension fields. Version 1
+//       itself, with the reference's interface kind and serialisation buffer, is the adapter in legacy_plugins.cpp.
 // Every enqueue() only translates descriptors into C-ABI calls (include/bert_b200.h).
 #include "plugin_common.h"
 
@@ -1268,7 +1269,7 @@ class FullyConnected : public PluginBase
 {
 public:
     explicit FullyConnected(std::string const& name)
-        : PluginBase(name, kFcName, "1")
+        : PluginBase(name, kFcName, "2")
     {
     }
     int32_t type{0};
@@ -1458,7 +1459,7 @@ class FullyConnectedCreator : public CreatorBase
 {
 public:
     FullyConnectedCreator()
-        : CreatorBase(kFcName, "1",
+        : CreatorBase(kFcName, "2",
             {PluginField("out_dims", nullptr, PluginFieldType::kINT32, 1), PluginField("type_id", nullptr, PluginFieldType::kINT32, 1),
                 PluginField("W", nullptr, PluginFieldType::kFLOAT32, 1), PluginField("bias", nullptr, PluginFieldType::kFLOAT32, 1),
                 PluginField("activation", nullptr, PluginFieldType::kINT32, 1)})

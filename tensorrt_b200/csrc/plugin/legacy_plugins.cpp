@@ -2,17 +2,20 @@
 //   CustomQKVToContextPluginDynamic   1 (fixed), 2 (variable sequence length), 3 (INT8 interleaved)
 //   CustomEmbLayerNormPluginDynamic   1 (fixed), 2 / 3 (variable sequence length, HFace / MTron)
 //   CustomSkipLayerNormPluginDynamic  1 / 2 (linear), 3 / 4 (INT8 interleaved, HFace / MTron)
+//   CustomFCPluginDynamic             1 (the only version the reference has)
 // Networks and serialised engines that still name these versions load them from this library. Each legacy version has
 // the same inputs, outputs, formats and fields as one IPluginV3 version (QKV 1/2/3 = 4/5/6, Emb 1/2/3 = 6/4/5,
-// SkipLN 1/2/3/4 = 5/6/7/8), so an adapter object owns the IPluginV3 object of that version and forwards every call;
-// what is specific to the legacy versions is the flat serialisation buffer, written and read here in the reference's
-// field order and field widths:
+// SkipLN 1/2/3/4 = 5/6/7/8, FC 1 = this library's 2), so an adapter object owns the IPluginV3 object of that version
+// and forwards every call; what is specific to the legacy versions is the flat serialisation buffer, written and read
+// here in the reference's field order and field widths:
 //   ref: plugin/bertQKVToContextPlugin/qkvToContextPluginLegacy.cpp:399-422, 909-925 (+ mhaRunner.cu:461-466, 494-499),
 //        plugin/bertQKVToContextPlugin/qkvToContextInt8InterleavedPluginLegacy.cpp:203-216,
 //        plugin/embLayerNormPlugin/embLayerNormPluginLegacy.cpp:451-470,
 //        plugin/embLayerNormPlugin/embLayerNormVarSeqlenPluginLegacy.cpp:545-562,
 //        plugin/skipLayerNormPlugin/skipLayerNormPluginLegacy.cpp:381-397, 900-916,
-//        plugin/skipLayerNormPlugin/skipLayerNormInt8InterleavedPluginLegacy.cpp:426-435.
+//        plugin/skipLayerNormPlugin/skipLayerNormInt8InterleavedPluginLegacy.cpp:426-435,
+//        plugin/fcPlugin/fcPlugin.cpp:661-673 (the cuBLASLt algorithm blob is written as zeros; optional bias /
+//        activation of this library follow the weights in a tagged extension block the reference never reads).
 // The reference's runner state at the end of the attention buffers (cuBLAS algorithm ids, S, B, head size) is written
 // with neutral values and skipped on reading: no kernel here has tunable state.
 #include "plugin_common.h"
@@ -37,7 +40,8 @@ enum class LegacyKind
     kEmbFixed,
     kEmbVarSeqlen,
     kSkip,
-    kSkipInterleaved
+    kSkipInterleaved,
+    kFc
 };
 
 struct LegacySpec
@@ -51,6 +55,9 @@ struct LegacySpec
 constexpr char const* kQkv = "CustomQKVToContextPluginDynamic";
 constexpr char const* kEmb = "CustomEmbLayerNormPluginDynamic";
 constexpr char const* kSkip = "CustomSkipLayerNormPluginDynamic";
+constexpr char const* kFc = "CustomFCPluginDynamic";
+constexpr uint32_t kFcExtensionTag = 0x30303242u; // "B200"
+constexpr size_t kLtAlgoBytes = 64;              // sizeof(cublasLtMatmulAlgo_t): uint64_t data[8]
 
 LegacySpec const kSpecs[] = {
     {kQkv, "1", "4", LegacyKind::kQkvFixed},
@@ -63,6 +70,7 @@ LegacySpec const kSpecs[] = {
     {kSkip, "2", "6", LegacyKind::kSkip},
     {kSkip, "3", "7", LegacyKind::kSkipInterleaved},
     {kSkip, "4", "8", LegacyKind::kSkipInterleaved},
+    {kFc, "1", "2", LegacyKind::kFc},
 };
 
 CreatorBase* coreCreator(LegacySpec const& spec)
@@ -298,6 +306,32 @@ void writeFlat(LegacyKind kind, PluginFieldCollection const& fc, Writer& w)
         putArray(gamma);
         break;
     }
+    case LegacyKind::kFc:
+    {
+        PluginField const& W = array("W");
+        PluginField const* bias = findField(fc, "bias");
+        int32_t const outDim = fieldInt(fc, "out_dims", 0);
+        int32_t const activation = fieldInt(fc, "activation", 0);
+        PLG_VALIDATE(outDim > 0);
+        w.put<int32_t>(fieldInt(fc, "type_id", 0));
+        w.put<uint64_t>(static_cast<uint64_t>(outDim));
+        w.put<uint64_t>(static_cast<uint64_t>(W.length));
+        w.put<int32_t>(0);                        // Nmax: only used by the reference's algorithm search
+        w.put<int32_t>(W.length / outDim);        // K
+        uint8_t const noAlgo[kLtAlgoBytes] = {};
+        w.putRaw(noAlgo, sizeof(noAlgo));
+        putArray(W);
+        bool const hasBias = bias != nullptr && bias->data != nullptr;
+        if (hasBias || activation != 0)
+        {
+            w.put<uint32_t>(kFcExtensionTag);
+            w.put<int32_t>(activation);
+            w.putBool(hasBias);
+            if (hasBias)
+                putArray(*bias);
+        }
+        break;
+    }
     }
 }
 
@@ -417,6 +451,34 @@ void readFlat(LegacySpec const& spec, Reader& r, FieldList& f)
         PLG_VALIDATE(ld > 0 && ld < (1ull << 24));
         f.addArray("beta", r.raw(ld * 2), true, static_cast<int64_t>(ld));
         f.addArray("gamma", r.raw(ld * 2), true, static_cast<int64_t>(ld));
+        break;
+    }
+    case LegacyKind::kFc:
+    {
+        int32_t const type = r.get<int32_t>();
+        uint64_t const outDim = r.get<uint64_t>();
+        uint64_t const numParams = r.get<uint64_t>();
+        r.get<int32_t>(); // Nmax
+        r.get<int32_t>(); // K
+        r.raw(kLtAlgoBytes);
+        PLG_VALIDATE(type >= 0 && type <= kInt8 && outDim > 0 && outDim < (1ull << 31) && numParams < (1ull << 31));
+        bool const half = type == kHalf; // FP32 and (this library's) INT8 objects keep FP32 weights
+        f.addInt("out_dims", static_cast<int32_t>(outDim));
+        f.addInt("type_id", type);
+        f.addArray("W", r.raw(numParams * (half ? 2 : 4)), half, static_cast<int64_t>(numParams));
+        if (r.left >= 9)
+        {
+            Reader ext = r;
+            if (ext.get<uint32_t>() == kFcExtensionTag)
+            {
+                int32_t const activation = ext.get<int32_t>();
+                bool const hasBias = ext.getBool();
+                if (activation != 0)
+                    f.addInt("activation", activation);
+                if (hasBias)
+                    f.addArray("bias", ext.raw(outDim * 4), false, static_cast<int64_t>(outDim));
+            }
+        }
         break;
     }
     }

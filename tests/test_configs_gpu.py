@@ -46,7 +46,7 @@ def test_config1_single_layer_through_plugins(cuda):
     ref, _ = O.encoder_layer_fp(x_packed.astype(np.float64), lp, B, S, N, cu, round_fp16=True)
     ref = ref.reshape(B, S, E).transpose(1, 0, 2)
 
-    fc = lambda W, out, extra=(): H.Plugin(FC, "1", [("out_dims", out), ("type_id", 1), ("W", W.astype(np.float32).ravel())] + list(extra)).attach()
+    fc = lambda W, out, extra=(): H.Plugin(FC, "2", [("out_dims", out), ("type_id", 1), ("W", W.astype(np.float32).ravel())] + list(extra)).attach()
     p_qkv = fc(lp.w_qkv, 3 * E, [("bias", lp.b_qkv)])
     p_att = H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", E), ("num_heads", N), ("has_mask", 1)]).attach()
     p_out = fc(lp.w_out, E)

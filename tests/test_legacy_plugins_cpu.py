@@ -148,3 +148,38 @@ def test_emb_legacy_flat_buffers():
         assert q.ok and q.serialize() == blob
         p.close()
         q.close()
+
+
+def test_fc_v1_flat_buffer():
+    """CustomFCPluginDynamic version 1 is an IPluginV2DynamicExt as in the reference, serialised as
+    type, out_dims (8 bytes), number of weights (8 bytes), Nmax, K, the 64-byte cuBLASLt algorithm blob, then W
+    (plugin/fcPlugin/fcPlugin.cpp:661-673); bias / activation of this library follow in a tagged block."""
+    FC = "CustomFCPluginDynamic"
+    rng = np.random.default_rng(3)
+    K, out = 48, 32
+    W = rng.standard_normal(K * out).astype(np.float32)
+    p = H.LegacyPlugin(FC, "1", [("out_dims", out), ("type_id", 1), ("W", W)])
+    assert p.ok and p.info() == (FC, "1", "") and p.nb_outputs() == 1
+    assert p.output_dims(0, [(7, 3, K, 1, 1)]) == (7, 3, out, 1, 1)
+    blob = p.serialize()
+    head = struct.calcsize("<iQQii")
+    assert struct.unpack("<iQQii", blob[:head]) == (1, out, K * out, 0, K)
+    assert blob[head:head + 64] == bytes(64)
+    assert blob[head + 64:] == W.astype(np.float16).tobytes()
+    q = H.LegacyPlugin(FC, "1", serialized=blob)
+    assert q.ok and q.serialize() == blob
+    # a buffer written by the reference carries a non-zero algorithm blob: accepted
+    ref_blob = blob[:head] + bytes(range(64)) + blob[head + 64:]
+    r = H.LegacyPlugin(FC, "1", serialized=ref_blob)
+    assert r.ok and r.serialize() == blob
+    for o in (p, q, r):
+        o.close()
+    bias = rng.standard_normal(out).astype(np.float32)
+    p = H.LegacyPlugin(FC, "1", [("out_dims", out), ("type_id", 0), ("W", W), ("bias", bias), ("activation", 1)])
+    blob = p.serialize()
+    assert blob[head + 64:head + 64 + W.nbytes] == W.tobytes()
+    assert blob[head + 64 + W.nbytes:] == struct.pack("<IiB", 0x30303242, 1, 1) + bias.tobytes()
+    q = H.LegacyPlugin(FC, "1", serialized=blob)
+    assert q.ok and q.serialize() == blob
+    p.close()
+    q.close()

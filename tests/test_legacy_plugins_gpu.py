@@ -107,3 +107,27 @@ def test_emb_var_seqlen_legacy_matches_v4(cuda):
         assert torch.equal(got[0], want[0])
         p.close()
     v4.close()
+
+
+def test_fc_v1_matches_v2(cuda):
+    from tensorrt_b200 import plugin_harness as H
+
+    FC = "CustomFCPluginDynamic"
+    rng = np.random.default_rng(3)
+    S, B, K, out = 40, 8, 256, 384
+    W = (0.05 * rng.standard_normal(K * out)).astype(np.float32)
+    bias = rng.standard_normal(out).astype(np.float32)
+    items = [("out_dims", out), ("type_id", 1), ("W", W), ("bias", bias), ("activation", 1)]
+    x = _t(rng.standard_normal((S, B, K, 1, 1)).astype(np.float16), cuda)
+    ind, outd = [H.make_desc((S, B, K, 1, 1), H.HALF)], [H.make_desc((S, B, out, 1, 1), H.HALF)]
+    v2 = H.Plugin(FC, "2", items).attach()
+    want = torch.empty((S, B, out, 1, 1), dtype=torch.float16, device=cuda)
+    _enqueue(v2, [x], [want], ind, outd)
+    v1 = H.LegacyPlugin(FC, "1", items)
+    again = H.LegacyPlugin(FC, "1", serialized=v1.serialize())
+    for p in (v1, again):
+        got = torch.zeros_like(want)
+        _enqueue(p, [x], [got], ind, outd)
+        assert torch.equal(got, want)
+        p.close()
+    v2.close()

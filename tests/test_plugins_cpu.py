@@ -24,9 +24,9 @@ def _emb_fields(E=64, vocab=50, fp16=1, extra=()):
 def test_creator_inventory():
     got = {(n, v) for n, v, ns, _ in H.creators()}
     want = {(EMB, "4"), (EMB, "5"), (EMB, "6"), (QKV, "4"), (QKV, "5"), (QKV, "6"), (SKIP, "5"), (SKIP, "6"),
-            (SKIP, "7"), (SKIP, "8"), (FC, "1")}
+            (SKIP, "7"), (SKIP, "8"), (FC, "2")}
     legacy = {(QKV, "1"), (QKV, "2"), (QKV, "3"), (EMB, "1"), (EMB, "2"), (EMB, "3"), (SKIP, "1"), (SKIP, "2"),
-              (SKIP, "3"), (SKIP, "4")}
+              (SKIP, "3"), (SKIP, "4"), (FC, "1")}
     assert got == want | legacy
     assert set(H.legacy_creators()) == legacy
     assert all(ns == "" for _, _, ns, _ in H.creators())
@@ -37,14 +37,14 @@ def test_creator_inventory():
     assert {"ld", "type_id", "beta", "gamma", "bias"} == set(fields[(SKIP, "5")])
     assert "ld" not in fields[(SKIP, "6")]
     assert set(fields[(SKIP, "7")]) == {"beta", "gamma"}
-    assert {"out_dims", "type_id", "W"} <= set(fields[(FC, "1")])
+    assert {"out_dims", "type_id", "W"} <= set(fields[(FC, "2")])
     assert {"full_mask", "mha_type_id", "output_fp16"} <= set(fields[(EMB, "6")])
 
 
 def test_missing_required_fields_return_null():
     assert not H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", 768)]).ok
     assert not H.Plugin(SKIP, "5", [("type_id", 1), ("ld", 8)]).ok
-    assert not H.Plugin(FC, "1", [("out_dims", 8), ("type_id", 1)]).ok
+    assert not H.Plugin(FC, "2", [("out_dims", 8), ("type_id", 1)]).ok
     assert not H.Plugin(EMB, "6", [("output_fp16", 1)]).ok
     assert not H.Plugin(QKV, "4", [("type_id", 7), ("hidden_size", 768), ("num_heads", 12), ("has_mask", 1)]).ok
     assert not H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", 770), ("num_heads", 12), ("has_mask", 1)]).ok
@@ -178,7 +178,7 @@ def test_skip_ln_variants():
 def test_fc_plugin_host_side():
     K, out = 96, 48
     W = np.random.default_rng(0).standard_normal(K * out).astype(np.float32)
-    p = H.Plugin(FC, "1", [("out_dims", out), ("type_id", 1), ("W", W)])
+    p = H.Plugin(FC, "2", [("out_dims", out), ("type_id", 1), ("W", W)])
     assert p.ok
     assert p.output_shapes([(128, 2, K, 1, 1)], 1) == [(128, 2, out, 1, 1)]
     d = [H.make_dyn((128, 2, K, 1, 1), H.HALF), H.make_dyn((128, 2, out, 1, 1), H.HALF)]
@@ -189,4 +189,4 @@ def test_fc_plugin_host_side():
     assert ser["W"].dtype == np.float16 and ser["W"].size == K * out and int(ser["out_dims"][0]) == out
     assert np.array_equal(ser["W"], W.astype(np.float16))
     p.close()
-    assert not H.Plugin(FC, "1", [("out_dims", 50), ("type_id", 1), ("W", W)]).ok  # W.count % out_dims != 0
+    assert not H.Plugin(FC, "2", [("out_dims", 50), ("type_id", 1), ("W", W)]).ok  # W.count % out_dims != 0

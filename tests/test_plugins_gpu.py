@@ -251,7 +251,7 @@ def test_fc_plugin(cuda, mode):
     bias = (0.02 * rng.standard_normal(out_dim)).astype(np.float32)
     x = rng.standard_normal((S * B, K))
     if mode == "fp32":
-        p = H.Plugin(FC, "1", [("out_dims", out_dim), ("type_id", 0), ("W", W.ravel())])
+        p = H.Plugin(FC, "2", [("out_dims", out_dim), ("type_id", 0), ("W", W.ravel())])
         a = x.astype(np.float32)
         ref = O.fc(a, W)
         out = torch.empty((S * B, out_dim), dtype=torch.float32, device=cuda)
@@ -262,7 +262,7 @@ def test_fc_plugin(cuda, mode):
         items = [("out_dims", out_dim), ("type_id", 1), ("W", W.ravel())]
         if mode.endswith("gelu"):
             items += [("bias", bias), ("activation", 1)]
-        p = H.Plugin(FC, "1", items).attach()
+        p = H.Plugin(FC, "2", items).attach()
         a = x.astype(np.float16)
         ref = O.fc(a, W.astype(np.float16), bias if mode.endswith("gelu") else None, "gelu" if mode.endswith("gelu") else None)
         out = torch.empty((S * B, out_dim), dtype=torch.float16, device=cuda)
@@ -270,7 +270,7 @@ def test_fc_plugin(cuda, mode):
         _run(p, H, [_t(a, cuda)], [out], ind, outd)
         assert O.close_abs_or_rel(out.cpu().numpy(), ref, 2e-3, 2e-3)[0]
     else:
-        p = H.Plugin(FC, "1", [("out_dims", out_dim), ("type_id", 2), ("W", W.ravel()), ("bias", bias)])
+        p = H.Plugin(FC, "2", [("out_dims", out_dim), ("type_id", 2), ("W", W.ravel()), ("bias", bias)])
         s_in, s_out = O.amax_scale(x), 0.05
         a = O.quantize(x, 1.0 / s_in)
         s_w = O.amax_scale(W)
