@@ -1,0 +1,74 @@
+"""BERT checkpoint -> encoder parameters.
+
+Takes a state dict in the Hugging Face `BertModel` naming (`embeddings.word_embeddings.weight`,
+`encoder.layer.{i}.attention.self.query.weight`, ...; an optional leading `bert.` is stripped) and packs it the way
+the plugins expect it: FC weights as [in, out] (the checkpoint stores [out, in]), and the three attention projections
+of a layer fused into one [E, 3E] matrix whose output channels are ordered [head][q | k | v][d]
+(ref: plugin/bertQKVToContextPlugin/README.md:26-30). The result has the attributes `BertEncoder` reads
+(`synthetic.make_params` builds the same object from random numbers).
+
+This is the step the removed `demo/BERT` builder performed before it wired the plugins into a network; the wiring
+itself is `BertEncoder` / `bert_b200_encoder_forward`.
+"""
+from __future__ import annotations
+
+from types import SimpleNamespace
+
+import numpy as np
+
+
+def _np(a) -> np.ndarray:
+    if hasattr(a, "detach"):
+        a = a.detach().cpu().float().numpy()
+    return np.asarray(a, dtype=np.float32)
+
+
+def params_from_bert_state_dict(state_dict, num_heads: int) -> SimpleNamespace:
+    sd = {}
+    for k, v in state_dict.items():
+        k = k[5:] if k.startswith("bert.") else k
+        sd[k] = v
+    get = lambda name: _np(sd[name])
+    word = get("embeddings.word_embeddings.weight")
+    hidden = word.shape[1]
+    if hidden % num_heads:
+        raise ValueError(f"hidden size {hidden} is not a multiple of num_heads {num_heads}")
+    d = hidden // num_heads
+    layers = []
+    i = 0
+    while f"encoder.layer.{i}.attention.self.query.weight" in sd:
+        p = f"encoder.layer.{i}."
+        # checkpoint [out, in] -> [in, out]; output channels regrouped per head as (q, k, v)
+        q, k, v = (get(p + f"attention.self.{n}.weight").T.reshape(hidden, num_heads, d) for n in ("query", "key", "value"))
+        bq, bk, bv = (get(p + f"attention.self.{n}.bias").reshape(num_heads, d) for n in ("query", "key", "value"))
+        w_qkv = np.stack([q, k, v], axis=2).reshape(hidden, 3 * hidden)
+        b_qkv = np.stack([bq, bk, bv], axis=1).reshape(3 * hidden)
+        h16 = lambda a: np.ascontiguousarray(a).astype(np.float16)
+        layers.append(SimpleNamespace(
+            w_qkv=h16(w_qkv), b_qkv=b_qkv.astype(np.float32),
+            w_out=h16(get(p + "attention.output.dense.weight").T), b_out=h16(get(p + "attention.output.dense.bias")),
+            ln1_gamma=h16(get(p + "attention.output.LayerNorm.weight")), ln1_beta=h16(get(p + "attention.output.LayerNorm.bias")),
+            w_ffn1=h16(get(p + "intermediate.dense.weight").T), b_ffn1=get(p + "intermediate.dense.bias"),
+            w_ffn2=h16(get(p + "output.dense.weight").T), b_ffn2=h16(get(p + "output.dense.bias")),
+            ln2_gamma=h16(get(p + "output.LayerNorm.weight")), ln2_beta=h16(get(p + "output.LayerNorm.bias")), scales={}))
+        i += 1
+    if not layers:
+        raise ValueError("no encoder.layer.* entries in the state dict")
+    ffn = layers[0].w_ffn1.shape[1]
+    return SimpleNamespace(
+        hidden=hidden, heads=num_heads, ffn=ffn, word_emb=word.astype(np.float16),
+        pos_emb=get("embeddings.position_embeddings.weight").astype(np.float16),
+        tok_emb=get("embeddings.token_type_embeddings.weight").astype(np.float16),
+        emb_gamma=get("embeddings.LayerNorm.weight"), emb_beta=get("embeddings.LayerNorm.bias"), layers=layers,
+        dq_probs=1.0 / 127.0)
+
+
+def pack_padded_batch(input_ids, token_type_ids, attention_mask):
+    """[B, S] padded arrays (mask 1 = valid, valid tokens first) -> packed (ids, segment ids, cu_seqlens) int32."""
+    ids, seg, mask = (np.asarray(a) for a in (input_ids, token_type_ids, attention_mask))
+    lengths = mask.astype(np.int64).sum(axis=1)
+    cu = np.zeros(len(lengths) + 1, dtype=np.int32)
+    cu[1:] = np.cumsum(lengths)
+    pid = np.concatenate([ids[b, :lengths[b]] for b in range(len(lengths))]).astype(np.int32)
+    pseg = np.concatenate([seg[b, :lengths[b]] for b in range(len(lengths))]).astype(np.int32)
+    return pid, pseg, cu

@@ -1,0 +1,44 @@
+"""End to end against an independent implementation: a randomly initialised Hugging Face BertModel (FP32, CPU) and
+this library's encoder built from its state dict (tensorrt_b200/checkpoint.py), FP16 and INT8."""
+import numpy as np
+import pytest
+import torch
+
+from tests.test_checkpoint_cpu import make_hf, padded_batch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_encoder_from_checkpoint_matches_huggingface(cuda):
+    import tensorrt_b200 as T
+    from tensorrt_b200 import synthetic
+    from tensorrt_b200.checkpoint import pack_padded_batch, params_from_bert_state_dict
+
+    model = make_hf(layers=3, hidden=256, heads=4, ffn=1024, vocab=800, max_pos=128)
+    rng = np.random.default_rng(1)
+    B, S = 6, 128
+    ids, seg, mask, lengths = padded_batch(rng, B, S, 800)
+    with torch.no_grad():
+        want = model(input_ids=torch.from_numpy(ids), token_type_ids=torch.from_numpy(seg),
+                     attention_mask=torch.from_numpy(mask)).last_hidden_state.numpy()
+    want = np.concatenate([want[b, :lengths[b]] for b in range(B)])
+    p = params_from_bert_state_dict(model.state_dict(), num_heads=4)
+    pid, pseg, cu = pack_padded_batch(ids, seg, mask)
+    dev = lambda a: torch.from_numpy(a).to(cuda)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    got = enc.forward(dev(pid), dev(pseg), dev(cu), S).float().cpu().numpy()
+    err = np.abs(got - want)
+    # FP16 storage of every activation through three layers; outputs are O(1) after the final LayerNorm
+    assert err.max() < 5e-2 and err.mean() < 4e-3, (err.max(), err.mean())
+    # INT8 with max calibration on the same batch: statistical agreement (per-tensor 8-bit activations)
+    amax = enc.calibrate(dev(pid), dev(pseg), dev(cu), S)
+    for lp in p.layers:  # the scale assignment works on torch tensors
+        for name in ("w_qkv", "w_out", "w_ffn1", "w_ffn2"):
+            setattr(lp, name, torch.from_numpy(getattr(lp, name)))
+    synthetic.assign_int8_scales(p, amax)
+    enc8 = T.BertEncoder(p, T.INT8, cuda)
+    got8 = enc8.forward(dev(pid), dev(pseg), dev(cu), S).float().cpu().numpy()
+    cos = float((got8 * want).sum() / np.sqrt((got8 ** 2).sum() * (want ** 2).sum()))
+    assert cos > 0.98, cos
+    enc.close()
+    enc8.close()
