@@ -119,7 +119,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "seq/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, profile_steps=3):
@@ -312,12 +312,35 @@ def run_b200(args):
                                 "sample": f"{b} sequences x 24 layers x S=384 (one forward), FP32 torch-CPU port of the reference math"}
     else:
         line["cpu_baseline"] = None
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
 
+_JSON_FD = None
+
+
+def _claim_stdout():
+    """Keeps a private handle on stdout for the one JSON line and points file descriptor 1 at stderr, so that text
+    printed by libraries (NCCL's version banner, for one) cannot end up next to the result."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
