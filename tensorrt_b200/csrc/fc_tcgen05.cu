@@ -110,6 +110,7 @@ __device__ __forceinline__ void geluErfPair(float& a, float& b, float halfScale)
 struct QuantStep
 {
     float s, lo, hi;
+    bool useConvert; // round with cvt.rni.sat (conversion unit) instead of clamp + FMA
 };
 
 template <typename Out>
@@ -198,9 +199,9 @@ __device__ __forceinline__ QuantStep fcEpilogueMath(uint32_t const (&r)[32], flo
             for (int j = 0; j < 32; ++j)
                 v[j] = geluErf(v[j], 0.5f);
         }
-        return QuantStep{1.f, -128.f, 127.f};
+        return QuantStep{1.f, -128.f, 127.f, false};
     }
-    return QuantStep{args.outScale, args.qLo, args.qHi};
+    return QuantStep{args.outScale, args.qLo, args.qHi, true};
 }
 
 // ... then 128-bit stores straight from the registers of the row's thread (one-CTA kernel).
@@ -248,7 +249,13 @@ __device__ __forceinline__ void stageChunk32<int8_t>(uint8_t* tile, int lane, fl
         uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            w[j] = packChar4Scaled(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s, q.lo, q.hi);
+        {
+            // Without GELU the conversion unit is idle and issue slots are scarce: multiply + saturating convert.
+            // With GELU the unit is busy with tanh: clamp + rounding FMA on the FMA pipe instead. Same results.
+            w[j] = q.useConvert
+                ? packChar4Cvt(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s)
+                : packChar4Scaled(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s, q.lo, q.hi);
+        }
         *reinterpret_cast<uint4*>(rowPtr + ((g ^ x) << 4)) = o;
     }
 }
