@@ -172,6 +172,17 @@ __device__ __forceinline__ uint32_t packChar4Cvt(float a, float b, float c, floa
     return __byte_perm(__byte_perm(ia, ib, 0x0040), __byte_perm(ic, id, 0x0040), 0x5410);
 }
 
+// ... and without the multiply, for values that are already on the INT8 grid's scale.
+__device__ __forceinline__ uint32_t packChar4Cvt(float a, float b, float c, float d)
+{
+    int32_t ia, ib, ic, id;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ia) : "f"(a));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ib) : "f"(b));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(ic) : "f"(c));
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(id) : "f"(d));
+    return __byte_perm(__byte_perm(ia, ib, 0x0040), __byte_perm(ic, id, 0x0040), 0x5410);
+}
+
 __device__ __forceinline__ int8_t quantChar(float a)
 {
     int32_t ia;

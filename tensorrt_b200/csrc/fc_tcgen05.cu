@@ -111,6 +111,7 @@ struct QuantStep
 {
     float s, lo, hi;
     bool useConvert; // round with cvt.rni.sat (conversion unit) instead of clamp + FMA
+    bool unitScale;  // s == 1: the values are already scaled
 };
 
 template <typename Out>
@@ -157,6 +158,8 @@ __device__ __forceinline__ void storeChunk32<int8_t>(int8_t* dst, float const (&
 template <bool kInt8, typename Out>
 __device__ __forceinline__ QuantStep fcEpilogueMath(uint32_t const (&r)[32], float (&v)[32], FcArgs const& args, int64_t col, int validCols)
 {
+    constexpr bool kQuant = sizeof(Out) == 1;
+    bool const foldScale = kQuant && args.bias == nullptr && args.act != BERT_B200_ACT_GELU_ERF;
     if (args.bias)
     {
 #pragma unroll
@@ -176,14 +179,15 @@ __device__ __forceinline__ QuantStep fcEpilogueMath(uint32_t const (&r)[32], flo
     }
     else
     {
+        // nothing between the accumulator and the quantisation: one multiply by alpha * out_scale
+        float const a1 = foldScale ? args.alpha * args.outScale : args.alpha;
 #pragma unroll
         for (int j = 0; j < 32; ++j)
         {
             float const a = kInt8 ? static_cast<float>(static_cast<int32_t>(r[j])) : __uint_as_float(r[j]);
-            v[j] = a * args.alpha;
+            v[j] = a * a1;
         }
     }
-    constexpr bool kQuant = sizeof(Out) == 1;
     if (args.act == BERT_B200_ACT_GELU_ERF)
     {
         if (kQuant)
@@ -199,9 +203,11 @@ __device__ __forceinline__ QuantStep fcEpilogueMath(uint32_t const (&r)[32], flo
             for (int j = 0; j < 32; ++j)
                 v[j] = geluErf(v[j], 0.5f);
         }
-        return QuantStep{1.f, -128.f, 127.f, false};
+        return QuantStep{1.f, -128.f, 127.f, false, true};
     }
-    return QuantStep{args.outScale, args.qLo, args.qHi, true};
+    if (foldScale)
+        return QuantStep{1.f, -128.f, 127.f, true, true};
+    return QuantStep{args.outScale, args.qLo, args.qHi, true, false};
 }
 
 // ... then 128-bit stores straight from the registers of the row's thread (one-CTA kernel).
@@ -253,7 +259,8 @@ __device__ __forceinline__ void stageChunk32<int8_t>(uint8_t* tile, int lane, fl
             // Without GELU the conversion unit is idle and issue slots are scarce: multiply + saturating convert.
             // With GELU the unit is busy with tanh: clamp + rounding FMA on the FMA pipe instead. Same results.
             w[j] = q.useConvert
-                ? packChar4Cvt(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s)
+                ? (q.unitScale ? packChar4Cvt(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3])
+                               : packChar4Cvt(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s))
                 : packChar4Scaled(v[g * 16 + 4 * j], v[g * 16 + 4 * j + 1], v[g * 16 + 4 * j + 2], v[g * 16 + 4 * j + 3], q.s, q.lo, q.hi);
         }
         *reinterpret_cast<uint4*>(rowPtr + ((g ^ x) << 4)) = o;
