@@ -100,6 +100,13 @@ def cpu_forward_rate(batch_hint=None, budget_s=15.0, steps=1, warmup=0):
     return batch_hint, times, torch.get_num_threads()
 
 
+def _workload(dtype):
+    if dtype == "int8":
+        return ("BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, batch 64 per GPU "
+                "(BASELINE configs[2]); explicit INT8 with amax/127 scales from one seeded calibration batch")
+    return "BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, batch 64 per GPU, FP16"
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -108,13 +115,15 @@ def run_reference(args):
     _, times, cores = cpu_forward_rate(batch_hint=b, steps=args.steps, warmup=args.warmup)
     ms = 1e3 * sum(times) / len(times)
     value = b / (ms / 1e3)
-    sample = f"{b} of the {BATCH} sequences per step (24 layers, S=384), FP32 torch-CPU port of the reference math"
+    sample = (f"{b} of the {BATCH} sequences per step (24 layers, S=384), FP32 torch-CPU port of the reference math "
+              "(the reference has no CPU implementation of its plugins; the same network in FP32)")
+    # same metric / unit / workload as the GPU arm, so that the two lines divide
     line = {
-        "impl": "reference", "metric": "BERT-large s384 encoder sequences/s", "value": value, "unit": "seq/s",
+        "impl": "reference", "metric": f"BERT-large s384 {args.dtype.upper()} encoder sequences/s", "value": value, "unit": "seq/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "BERT-large 24 layers, hidden 1024, 16 heads, FFN 4096, seq 384 (BASELINE configs[2]); "
-                               "CPU arm: bounded sample", "per_gpu_batch": BATCH, "seq_len": SEQ},
+        "config": {"workload": _workload(args.dtype), "layers": LAYERS, "per_gpu_batch": BATCH, "seq_len": SEQ,
+                   "cpu_arm": "bounded sample of the workload on the host cores"},
         "cpu_baseline": {"value": value, "unit": "seq/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "seq/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -286,10 +295,7 @@ def run_b200(args):
         "unit": "seq/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8" if args.dtype == "int8" else "f16",
         "data": "synthetic",
-        "config": {"workload": "BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, "
-                               "batch 64 per GPU (BASELINE configs[2]); explicit INT8 with amax/127 scales from one "
-                               "seeded calibration batch" if args.dtype == "int8" else
-                               "BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, batch 64 per GPU, FP16",
+        "config": {"workload": _workload(args.dtype),
                    "layers": LAYERS, "per_gpu_batch": BATCH, "global_batch": n * BATCH, "seq_len": SEQ, "parallelism": f"dp{n} (batch sharding, no collective)",
                    "l2": "working set per step (activations > 250 MB + weights > 300 MB) exceeds the 126 MB L2"},
         "e2e": {"value": n * BATCH / (main["ms_e2e"] * 1e-3), "unit": "seq/s", "ms_per_step": main["ms_e2e"],
