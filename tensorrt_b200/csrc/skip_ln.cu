@@ -315,9 +315,10 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         y[j] = fmaf(g[j] * rsigma, x[i][8 * h + j] - mu, bt[j]);
-                    // the output scale is folded into the rounding FMA of the pack
-                    ow[2 * h] = packChar4Scaled(y[0], y[1], y[2], y[3], qScale, qLo, qHi);
-                    ow[2 * h + 1] = packChar4Scaled(y[4], y[5], y[6], y[7], qScale, qLo, qHi);
+                    // multiply + saturating convert: the conversion unit has nothing else to do in this kernel and
+                    // the kernel is bound by issue slots (one slot less per value than clamp + rounding FMA)
+                    ow[2 * h] = packChar4Cvt(y[0], y[1], y[2], y[3], qScale);
+                    ow[2 * h + 1] = packChar4Cvt(y[4], y[5], y[6], y[7], qScale);
                 }
                 stgStream(out + row * ld + c * E, o);
             }
