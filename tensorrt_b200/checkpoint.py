@@ -72,3 +72,27 @@ def pack_padded_batch(input_ids, token_type_ids, attention_mask):
     pid = np.concatenate([ids[b, :lengths[b]] for b in range(len(lengths))]).astype(np.int32)
     pseg = np.concatenate([seg[b, :lengths[b]] for b in range(len(lengths))]).astype(np.int32)
     return pid, pseg, cu
+
+
+class QaHead:
+    """The span-prediction head of `BertForQuestionAnswering` (`qa_outputs`: hidden -> start / end logits) on top of
+    the encoder output, run through the FC kernel. The two output channels are padded to 16 (the kernel's granularity);
+    the padding rows are zero and dropped from the result."""
+
+    def __init__(self, state_dict, device="cuda:0"):
+        import torch
+
+        w = _np(state_dict["qa_outputs.weight"])  # [2, hidden]
+        b = _np(state_dict["qa_outputs.bias"])
+        wt = np.zeros((16, w.shape[1]), dtype=np.float16)
+        wt[:2] = w.astype(np.float16)
+        bias = np.zeros(16, dtype=np.float32)
+        bias[:2] = b
+        self.wt = torch.from_numpy(wt).to(device)      # already [out, in], the layout the FC kernel reads
+        self.bias = torch.from_numpy(bias).to(device)
+
+    def __call__(self, hidden):
+        """hidden: FP16 [total, hidden] (packed tokens) -> FP16 [total, 2] (start logit, end logit)."""
+        from . import ops
+
+        return ops.fc(hidden, self.wt, bias=self.bias)[:, :2]

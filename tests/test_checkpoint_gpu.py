@@ -42,3 +42,37 @@ def test_encoder_from_checkpoint_matches_huggingface(cuda):
     assert cos > 0.98, cos
     enc.close()
     enc8.close()
+
+
+def test_question_answering_head_matches_huggingface(cuda):
+    """BertForQuestionAnswering end to end: encoder + span head against Hugging Face on the valid tokens."""
+    import transformers
+
+    import tensorrt_b200 as T
+    from tensorrt_b200.checkpoint import QaHead, pack_padded_batch, params_from_bert_state_dict
+
+    torch.manual_seed(3)
+    cfg = transformers.BertConfig(vocab_size=600, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                  intermediate_size=1024, max_position_embeddings=128, hidden_act="gelu",
+                                  hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    model = transformers.BertForQuestionAnswering(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.copy_((p + 0.05 * torch.randn_like(p)).half().float())
+    rng = np.random.default_rng(4)
+    B, S = 4, 96
+    ids, seg, mask, lengths = padded_batch(rng, B, S, 600)
+    with torch.no_grad():
+        out = model(input_ids=torch.from_numpy(ids), token_type_ids=torch.from_numpy(seg), attention_mask=torch.from_numpy(mask))
+    want = torch.stack([out.start_logits, out.end_logits], dim=-1).numpy()
+    want = np.concatenate([want[b, :lengths[b]] for b in range(B)])
+    sd = model.state_dict()
+    p = params_from_bert_state_dict(sd, num_heads=4)
+    pid, pseg, cu = pack_padded_batch(ids, seg, mask)
+    dev = lambda a: torch.from_numpy(a).to(cuda)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    hidden = enc.forward(dev(pid), dev(pseg), dev(cu), S)
+    got = QaHead(sd, cuda)(hidden).float().cpu().numpy()
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() < 5e-2, np.abs(got - want).max()
+    enc.close()
