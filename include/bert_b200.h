@@ -215,7 +215,12 @@ BERT_B200_API int32_t bert_b200_fc(bert_b200_fc_params const* params, void* stre
  * ------------------------------------------------------------------------------------------ */
 
 /*
- * O = softmax(Q K^T * scale, keys < len_b) V per (sequence b, head n), head size 64 (32 too for FP32).
+ * O = softmax(Q K^T * scale, keys < len_b) V per (sequence b, head n).
+ * Tensor-core kernel (FP16, INT8): head sizes 16, 32, 48, 64 (32, 64 when interleaved), S <= 512; smaller heads
+ * ride the 64-wide tiles with the missing channels zero-filled by the TMA unit, which replaces the reference's
+ * pad / unpad copies (plugin/bertQKVToContextPlugin/zeroPadding2d.cu:190-204). FP32 always, and FP16 outside
+ * those shapes, run a SIMT kernel (the reference's unfused runner, mhaRunner.cu:533-601); INT8 outside them is
+ * BERT_B200_NOT_SUPPORTED as in the reference (qkvToContextPlugin.cpp:530).
  *
  * Layouts (ref: plugin/bertQKVToContextPlugin/README.md:26-30, mhaRunner.cu:550-552, 1006, 1171):
  *  - fixed  (cu_seqlens == NULL): qkv [S][B][N][3][d], out [S][B][N][d]; valid keys of sequence b

@@ -164,8 +164,9 @@ int32_t checkConfig(bert_b200_encoder_config const* c)
     B200_REQUIRE(c != nullptr, "encoder: null config");
     B200_REQUIRE(c->type_id == BERT_B200_FP16 || c->type_id == BERT_B200_INT8, "encoder: type_id %d", c->type_id);
     B200_REQUIRE(c->num_layers > 0 && c->hidden_size > 0 && c->num_heads > 0 && c->ffn_size > 0, "encoder: bad sizes");
-    B200_REQUIRE(c->hidden_size == c->num_heads * 64, "encoder: head size must be 64 (hidden %d, heads %d)", c->hidden_size,
-        c->num_heads);
+    B200_REQUIRE(c->hidden_size % c->num_heads == 0 && c->hidden_size / c->num_heads <= 64
+            && (c->hidden_size / c->num_heads) % 16 == 0,
+        "encoder: head size must be 16, 32, 48 or 64 (hidden %d, heads %d)", c->hidden_size, c->num_heads);
     B200_REQUIRE(c->ffn_size % 16 == 0, "encoder: ffn_size must be a multiple of 16");
     B200_REQUIRE(c->word_emb && c->pos_emb && c->tok_emb && c->emb_gamma && c->emb_beta && c->layers_host,
         "encoder: null weight pointer");
@@ -282,7 +283,8 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         c.emb_gamma, c.word_emb, c.pos_emb, c.tok_emb, c.vocab_size, c.type_vocab_size, i8 ? static_cast<void*>(w.xf16) : w.x,
         nullptr, i8 ? reinterpret_cast<int8_t*>(w.x) : nullptr, i8 ? 1.f / enc->layers[0].s_in : 0.f));
 
-    float const rsqrtD = 0.125f; // head size 64
+    int32_t const headSize = c.hidden_size / c.num_heads;
+    float const rsqrtD = 1.f / std::sqrt(static_cast<float>(headSize));
     for (int32_t li = 0; li < c.num_layers; ++li)
     {
         bert_b200_layer_weights const& l = enc->layers[li];
@@ -313,7 +315,7 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         mha.B = B;
         mha.S = maxSeqlen;
         mha.num_heads = c.num_heads;
-        mha.head_size = 64;
+        mha.head_size = headSize;
         mha.total = total;
         mha.qkv = w.qkv;
         mha.out = w.ctx;

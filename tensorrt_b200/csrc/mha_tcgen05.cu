@@ -26,7 +26,7 @@
 namespace b200
 {
 
-int32_t mhaF32(bert_b200_mha_params const& p, cudaStream_t stream);
+int32_t mhaSimt(bert_b200_mha_params const& p, cudaStream_t stream);
 
 namespace
 {
@@ -43,6 +43,7 @@ constexpr uint32_t kOColumn = 384;   // context accumulator when the scores need
 struct MhaArgs
 {
     int32_t B, S, N, total;
+    int32_t d; // head size: 16, 32, 48 or 64; the tiles are always 64 wide, TMA fills the missing channels with zeros
     int32_t fixedLayout;
     void* out;
     int32_t const* cu;
@@ -256,12 +257,12 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             for (int item = nextWork(blockIdx.x, it); item < numItems && ok; item = nextWork(item + gridDim.x, it))
             {
                 int32_t const rowK = args.fixedLayout ? 0 : it.rowBase;
-                // linear: (column of the token row, batch, row). interleaved: (0, row, 32-channel group of [3][N][2])
+                // linear: (channel, which of [N][3], batch, row). interleaved: (channel, row, 32-channel group, which of [3][N])
                 auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
                     if (IL)
-                        tmaLoad3d(dst, &mapQkv, bar, 0, row, (which * args.N + it.head) * 2);
+                        tmaLoad4d(dst, &mapQkv, bar, 0, row, 0, which * args.N + it.head);
                     else
-                        tmaLoad3d(dst, &mapQkv, bar, (it.head * 3 + which) * kHeadSize, args.fixedLayout ? it.b : 0, row);
+                        tmaLoad4d(dst, &mapQkv, bar, 0, it.head * 3 + which, args.fixedLayout ? it.b : 0, row);
                 };
                 for (int t = 0; t < it.nq && ok; ++t)
                 {
@@ -559,21 +560,22 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         for (int item = blockIdx.x; item < numItems; item += gridDim.x)
         {
             bool const work = getItem(item, it);
-            int64_t const outRowStride = static_cast<int64_t>(args.N) * kHeadSize; // elements
-            T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(it.head) * kHeadSize;
-            // linear layouts: the 64 values of (token, head) are contiguous
+            int64_t const outRowStride = static_cast<int64_t>(args.N) * args.d; // elements
+            T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(it.head) * args.d;
+            // linear layouts: the d values of (token, head) are contiguous
             auto outRow = [&](int q) -> T* {
                 int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + it.b : static_cast<int64_t>(it.rowBase) + q;
                 return outBase + rr * outRowStride;
             };
-            // interleaved output [N][2][total][32]: 32-channel group `grp` of (token, head)
+            // interleaved output [N][d/32][total][32]: 32-channel group `grp` of (token, head)
             auto outPtrIl = [&](int q, int grp) -> T* {
-                return static_cast<T*>(args.out) + ((static_cast<int64_t>(it.head) * 2 + grp) * args.total + it.rowBase + q) * 32;
+                return static_cast<T*>(args.out)
+                    + ((static_cast<int64_t>(it.head) * (args.d / 32) + grp) * args.total + it.rowBase + q) * 32;
             };
             if (!work)
             {
                 // no valid key: every probability is zero and so is the context row
-                constexpr int kChunks = L::kRowBytes / 16;
+                int const kChunks = args.d * L::kElem / 16;
                 for (int i = threadIdx.x - 64; i < it.rows * kChunks; i += kSoftmaxThreads)
                 {
                     int const q = i / kChunks;
@@ -739,7 +741,10 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 }
                 sBits ^= (1u << nb) - 1u; // every block of this tile used its sFull / pReady phase
                 int const q = t * kQTile + r;
-                T* const dst = q >= it.rows ? nullptr : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16);
+                // this thread's 16 of the 64 context columns; columns >= d are the zero padding
+                T* const dst = q >= it.rows || sub * 16 >= args.d
+                    ? nullptr
+                    : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16);
                 ++tiles;
                 if (deferEpilogue)
                 {
@@ -780,29 +785,33 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
 {
     using L = MhaSmem<T>;
     bool const fixedLayout = p.cu_seqlens == nullptr;
-    int64_t const rowElems = static_cast<int64_t>(3) * p.num_heads * kHeadSize;
+    uint64_t const d = static_cast<uint64_t>(p.head_size);
+    uint64_t const rowElems = 3ull * static_cast<uint64_t>(p.num_heads) * d;
+    // The boxes are always 64 channels wide (two 32-channel groups when interleaved); for a smaller head the channels
+    // beyond d lie outside the tensor's channel dimension and arrive as zeros, which change neither Q.K nor P.V.
     CUtensorMap map;
     if (IL)
     {
-        // [3][N][2][total][32]: dim0 the 32 channels of a group, dim1 the token, dim2 the group
-        uint64_t const dims[3] = {32, static_cast<uint64_t>(p.total), static_cast<uint64_t>(6) * p.num_heads};
-        uint64_t const strides[2] = {32, static_cast<uint64_t>(p.total) * 32};
-        uint32_t const box[3] = {32, kKeyBlock, 2};
-        int32_t const st = makeTensorMap(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, p.qkv, dims, strides, box,
+        // [3][N][d/32][total][32]: dim0 the 32 channels of a group, dim1 the token, dim2 the group, dim3 which of [3][N]
+        uint64_t const dims[4] = {32, static_cast<uint64_t>(p.total), d / 32, 3ull * static_cast<uint64_t>(p.num_heads)};
+        uint64_t const strides[3] = {32, static_cast<uint64_t>(p.total) * 32, (d / 32) * static_cast<uint64_t>(p.total) * 32};
+        uint32_t const box[4] = {32, kKeyBlock, 2, 1};
+        int32_t const st = makeTensorMap(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, p.qkv, dims, strides, box,
             CU_TENSOR_MAP_SWIZZLE_32B);
         if (st != BERT_B200_OK)
             return st;
     }
     else
     {
-        // dim0: the 3*N*d values of one token; dim1: batch (fixed layout only); dim2: sequence position / packed row
-        uint64_t const dims[3] = {static_cast<uint64_t>(rowElems), fixedLayout ? static_cast<uint64_t>(p.B) : 1ull,
+        // dim0: the d channels of one of Q, K, V of a head; dim1: which of [N][3]; dim2: batch (fixed layout only);
+        // dim3: sequence position / packed row
+        uint64_t const dims[4] = {d, 3ull * static_cast<uint64_t>(p.num_heads), fixedLayout ? static_cast<uint64_t>(p.B) : 1ull,
             fixedLayout ? static_cast<uint64_t>(p.S) : static_cast<uint64_t>(p.total)};
-        uint64_t const strides[2] = {static_cast<uint64_t>(rowElems) * sizeof(T),
-            (fixedLayout ? static_cast<uint64_t>(p.B) : 1ull) * static_cast<uint64_t>(rowElems) * sizeof(T)};
-        uint32_t const box[3] = {kHeadSize, 1, kKeyBlock};
+        uint64_t const strides[3] = {d * sizeof(T), rowElems * sizeof(T),
+            (fixedLayout ? static_cast<uint64_t>(p.B) : 1ull) * rowElems * sizeof(T)};
+        uint32_t const box[4] = {kHeadSize, 1, 1, kKeyBlock};
         int32_t const st = makeTensorMap(&map, sizeof(T) == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-            3, p.qkv, dims, strides, box, sizeof(T) == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+            4, p.qkv, dims, strides, box, sizeof(T) == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
         if (st != BERT_B200_OK)
             return st;
     }
@@ -812,7 +821,7 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    MhaArgs args{p.B, p.S, p.num_heads, p.total, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
+    MhaArgs args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
         p.scale_softmax, p.scale_bmm2, p.status_word};
     // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
     int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
@@ -839,12 +848,19 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
     B200_REQUIRE(p.B <= 65535 && p.num_heads <= 65535, "mha: B and num_heads are limited to 65535");
     auto s = static_cast<cudaStream_t>(stream);
     if (p.type_id == BERT_B200_FP32)
-        return mhaF32(p, s);
+        return mhaSimt(p, s);
     B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "mha: type_id %d", p.type_id);
-    if (p.head_size != kHeadSize)
-        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: the tensor-core path needs head_size 64 (got %d)", p.head_size);
-    if (p.S > kMaxBlocks * kKeyBlock)
-        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: S=%d exceeds %d", p.S, kMaxBlocks * kKeyBlock);
+    bool const headOk = p.head_size <= kHeadSize && p.head_size % 16 == 0 && (!p.interleaved || p.head_size % 32 == 0);
+    bool const lengthOk = p.S <= kMaxBlocks * kKeyBlock;
+    // Outside the tensor-core kernel's shapes FP16 takes the SIMT kernel, like the reference's unfused runner
+    // (qkvToContextPlugin.cpp:335-341, 522-531); INT8 has no such path there either (qkvToContextPlugin.cpp:530).
+    if ((!headOk || !lengthOk) && p.type_id == BERT_B200_FP16)
+        return mhaSimt(p, s);
+    if (!headOk)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED,
+            "mha: INT8 takes head sizes 16, 32, 48 and 64 (32 and 64 when interleaved), got %d", p.head_size);
+    if (!lengthOk)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: INT8 takes S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
     B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
     if (p.interleaved)
     {

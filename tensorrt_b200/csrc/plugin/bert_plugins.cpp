@@ -640,8 +640,9 @@ public:
         PLG_VALIDATE(dtype() == DataType::kFLOAT || dtype() == DataType::kHALF || dtype() == DataType::kINT8);
         if (dtype() == DataType::kINT8 && dqProbs < 0)
             dqProbs = 1.f / 127.f; // ref: qkvToContextPlugin.cpp:715-719
-        if (dtype() != DataType::kFLOAT)
-            PLG_VALIDATE(headSize == 64 && "the sm_100a tensor-core attention kernel needs head size 64");
+        if (dtype() == DataType::kINT8) // FP16 outside these shapes takes the SIMT kernel
+            PLG_VALIDATE(headSize <= 64 && headSize % (kind == QkvKind::kInterleaved ? 32 : 16) == 0
+                && "INT8 attention takes head sizes 16, 32, 48, 64 (32, 64 interleaved)");
         if (kind == QkvKind::kVarSeqlen && varSeqlen)
             PLG_VALIDATE(dtype() != DataType::kFLOAT && hasMask); // ref: qkvToContextPlugin.cpp:877-881
     }

@@ -2,8 +2,11 @@
 // full precision (TF32 would break the 1e-5 tolerance the reference configuration states for FP32,
 // plugin/bertQKVToContextPlugin/CustomQKVToContextPluginDynamic_PluginConfig.yaml:72-76), so these
 // are plain SIMT kernels; the FP16 / INT8 paths live in fc_tcgen05.cu and mha_tcgen05.cu.
+// The attention kernel also serves FP16 tensors (FP32 arithmetic) for the shapes the tensor-core kernel does not
+// take - heads wider than 64 or not a multiple of 16, sequences longer than 512 - the shapes the reference sends
+// to its unfused runner as well.
 //
-// Replaces cublasSgemmStridedBatched + softmax kernels of UnfusedMHARunner::run
+// Replaces cublas{S,H}gemmStridedBatched + softmax kernels of UnfusedMHARunner::run
 // (plugin/bertQKVToContextPlugin/mhaRunner.cu:533-601) and the FP32 cublasLtMatmul of the FC plugin
 // (plugin/fcPlugin/fcPlugin.cpp:551-610).
 #include "common.cuh"
@@ -82,9 +85,27 @@ __global__ void __launch_bounds__(256) fcF32Kernel(int64_t const M, int64_t cons
     }
 }
 
-// One warp per query row. Scores of the row live in shared memory ([warps][S]).
-__global__ void __launch_bounds__(128) mhaF32Kernel(int32_t const B, int32_t const S, int32_t const N, int32_t const d,
-    float const* __restrict__ qkv, float* __restrict__ out, int32_t const* __restrict__ cu,
+__device__ __forceinline__ float toFloat(float v)
+{
+    return v;
+}
+__device__ __forceinline__ float toFloat(__half v)
+{
+    return __half2float(v);
+}
+__device__ __forceinline__ void fromFloat(float& dst, float v)
+{
+    dst = v;
+}
+__device__ __forceinline__ void fromFloat(__half& dst, float v)
+{
+    dst = __float2half_rn(v);
+}
+
+// One warp per query row. Scores of the row live in shared memory ([warps][S]); all arithmetic in FP32.
+template <typename T>
+__global__ void __launch_bounds__(128) mhaSimtKernel(int32_t const B, int32_t const S, int32_t const N, int32_t const d,
+    T const* __restrict__ qkv, T* __restrict__ out, int32_t const* __restrict__ cu,
     int32_t const* __restrict__ maskIdx, float const scale)
 {
     extern __shared__ float sm[];
@@ -115,17 +136,17 @@ __global__ void __launch_bounds__(128) mhaF32Kernel(int32_t const B, int32_t con
     int64_t const headOff = static_cast<int64_t>(n) * 3 * d;
     for (int s = blockIdx.z * 4 + warp; s < rows; s += gridDim.z * 4)
     {
-        float const* q = qkv + (row0 + s * rowStride) * tokStride + headOff;
+        T const* q = qkv + (row0 + s * rowStride) * tokStride + headOff;
         for (int i = lane; i < d; i += 32)
-            qs[i] = q[i];
+            qs[i] = toFloat(q[i]);
         __syncwarp();
         float mx = -INFINITY;
         for (int j = lane; j < len; j += 32)
         {
-            float const* k = qkv + (row0 + j * rowStride) * tokStride + headOff + d;
+            T const* k = qkv + (row0 + j * rowStride) * tokStride + headOff + d;
             float acc = 0.f;
             for (int i = 0; i < d; ++i)
-                acc = fmaf(qs[i], k[i], acc);
+                acc = fmaf(qs[i], toFloat(k[i]), acc);
             acc *= scale;
             scores[j] = acc;
             mx = fmaxf(mx, acc);
@@ -141,13 +162,13 @@ __global__ void __launch_bounds__(128) mhaF32Kernel(int32_t const B, int32_t con
         sum = warpSum(sum);
         float const inv = len > 0 ? 1.f / sum : 0.f;
         __syncwarp();
-        float* o = out + (row0 + s * rowStride) * (static_cast<int64_t>(N) * d) + static_cast<int64_t>(n) * d;
+        T* o = out + (row0 + s * rowStride) * (static_cast<int64_t>(N) * d) + static_cast<int64_t>(n) * d;
         for (int i = lane; i < d; i += 32)
         {
             float acc = 0.f;
             for (int j = 0; j < len; ++j)
-                acc = fmaf(scores[j], qkv[(row0 + j * rowStride) * tokStride + headOff + 2 * d + i], acc);
-            o[i] = acc * inv;
+                acc = fmaf(scores[j], toFloat(qkv[(row0 + j * rowStride) * tokStride + headOff + 2 * d + i]), acc);
+            fromFloat(o[i], acc * inv);
         }
         __syncwarp();
     }
@@ -164,16 +185,35 @@ int32_t fcF32(bert_b200_fc_params const& p, cudaStream_t stream)
     return checkLaunch("fcF32Kernel");
 }
 
-int32_t mhaF32(bert_b200_mha_params const& p, cudaStream_t stream)
+namespace
 {
-    B200_REQUIRE(!p.interleaved, "mha (FP32): interleaved layout is INT8 only");
+
+template <typename T>
+int32_t launchMhaSimt(bert_b200_mha_params const& p, cudaStream_t stream)
+{
     size_t const smem = 4 * static_cast<size_t>(p.S + p.head_size) * sizeof(float);
-    B200_REQUIRE(smem <= 48 * 1024, "mha (FP32): S=%d too long", p.S);
+    B200_REQUIRE(smem <= 200 * 1024, "mha (SIMT): S=%d with head size %d does not fit shared memory", p.S, p.head_size);
+    auto kernel = mhaSimtKernel<T>;
+    if (smem > 48 * 1024)
+    {
+        cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess)
+            B200_FAIL(BERT_B200_CUDA_ERROR, "mha (SIMT): cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
     int const z = (p.S + 3) / 4 < 32 ? (p.S + 3) / 4 : 32;
     dim3 const grid(p.num_heads, p.B, z > 0 ? z : 1);
-    mhaF32Kernel<<<grid, 128, smem, stream>>>(p.B, p.S, p.num_heads, p.head_size, static_cast<float const*>(p.qkv),
-        static_cast<float*>(p.out), p.cu_seqlens, p.mask_idx, p.scale_bmm1);
-    return checkLaunch("mhaF32Kernel");
+    kernel<<<grid, 128, smem, stream>>>(p.B, p.S, p.num_heads, p.head_size, static_cast<T const*>(p.qkv),
+        static_cast<T*>(p.out), p.cu_seqlens, p.mask_idx, p.scale_bmm1);
+    return checkLaunch("mhaSimtKernel");
+}
+
+} // namespace
+
+// FP32 always; FP16 for the shapes outside the tensor-core kernel.
+int32_t mhaSimt(bert_b200_mha_params const& p, cudaStream_t stream)
+{
+    B200_REQUIRE(!p.interleaved, "mha (SIMT): the interleaved layout is INT8 only");
+    return p.type_id == BERT_B200_FP16 ? launchMhaSimt<__half>(p, stream) : launchMhaSimt<float>(p, stream);
 }
 
 } // namespace b200

@@ -146,12 +146,12 @@ __device__ __forceinline__ void tmaLoad2d(void* dst, CUtensorMap const* map, uin
         : "memory");
 }
 
-__device__ __forceinline__ void tmaLoad3d(
-    void* dst, CUtensorMap const* map, uint64_t* bar, int32_t c0, int32_t c1, int32_t c2)
+__device__ __forceinline__ void tmaLoad4d(
+    void* dst, CUtensorMap const* map, uint64_t* bar, int32_t c0, int32_t c1, int32_t c2, int32_t c3)
 {
     asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2)
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
 

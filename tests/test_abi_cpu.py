@@ -43,10 +43,13 @@ def test_fc_and_mha_validation():
     assert _lib.lib.bert_b200_fc(C.byref(p), None) == 2
     assert _lib.lib.bert_b200_fc(None, None) == 2
     m = _lib.MhaParams()
-    m.type_id, m.B, m.S, m.num_heads, m.head_size = 1, 1, 1024, 2, 64
+    # INT8 outside the tensor-core kernel's shapes (FP16 would take the SIMT kernel there)
+    m.type_id, m.B, m.S, m.num_heads, m.head_size = 2, 1, 1024, 2, 64
     m.qkv = m.out = C.c_void_p(0x1000)
     assert _lib.lib.bert_b200_mha(C.byref(m), None) == 3  # BERT_B200_NOT_SUPPORTED: S > 512
     m.S, m.head_size = 128, 80
+    assert _lib.lib.bert_b200_mha(C.byref(m), None) == 3
+    m.head_size = 24
     assert _lib.lib.bert_b200_mha(C.byref(m), None) == 3
 
 

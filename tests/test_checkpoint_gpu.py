@@ -9,12 +9,14 @@ from tests.test_checkpoint_cpu import make_hf, padded_batch
 pytestmark = pytest.mark.gpu
 
 
-def test_encoder_from_checkpoint_matches_huggingface(cuda):
+# head sizes 64, 32 and 48 (the tiles are 64 channels wide; smaller heads are zero-filled by the TMA unit)
+@pytest.mark.parametrize("hidden,heads", [(256, 4), (256, 8), (192, 4)])
+def test_encoder_from_checkpoint_matches_huggingface(cuda, hidden, heads):
     import tensorrt_b200 as T
     from tensorrt_b200 import synthetic
     from tensorrt_b200.checkpoint import pack_padded_batch, params_from_bert_state_dict
 
-    model = make_hf(layers=3, hidden=256, heads=4, ffn=1024, vocab=800, max_pos=128)
+    model = make_hf(layers=3, hidden=hidden, heads=heads, ffn=1024, vocab=800, max_pos=128)
     rng = np.random.default_rng(1)
     B, S = 6, 128
     ids, seg, mask, lengths = padded_batch(rng, B, S, 800)
@@ -22,7 +24,7 @@ def test_encoder_from_checkpoint_matches_huggingface(cuda):
         want = model(input_ids=torch.from_numpy(ids), token_type_ids=torch.from_numpy(seg),
                      attention_mask=torch.from_numpy(mask)).last_hidden_state.numpy()
     want = np.concatenate([want[b, :lengths[b]] for b in range(B)])
-    p = params_from_bert_state_dict(model.state_dict(), num_heads=4)
+    p = params_from_bert_state_dict(model.state_dict(), num_heads=heads)
     pid, pseg, cu = pack_padded_batch(ids, seg, mask)
     dev = lambda a: torch.from_numpy(a).to(cuda)
     enc = T.BertEncoder(p, T.FP16, cuda)

@@ -138,6 +138,79 @@ def test_mha_interleaved_int8(cuda, lengths, N):
     _assert_int8_attention(lin, ref)
 
 
+@pytest.mark.parametrize("d", [16, 32, 48])
+@pytest.mark.parametrize("packed", [False, True])
+def test_mha_fp16_small_heads(cuda, d, packed):
+    """Head sizes below 64 ride the 64-wide tiles: the missing channels are zero-filled by the TMA unit."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(d + packed)
+    N = 5
+    lengths = np.array([300, 128, 0, 77, 1], dtype=np.int32)
+    B, S = len(lengths), 320
+    st = _status(cuda)
+    if packed:
+        cu = O.cu_seqlens(lengths)
+        qkv = rng.standard_normal((int(cu[-1]), 3 * N * d)).astype(np.float16)
+        ref = O.mha(qkv, B, S, N, d, cu=cu)
+        out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda), status=st)
+    else:
+        qkv = rng.standard_normal((S, B, 3 * N * d)).astype(np.float16)
+        ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+        out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, mask_idx=_t(lengths, cuda), status=st)
+    assert int(st[0]) == 0
+    assert out.shape == ref.shape
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+
+
+@pytest.mark.parametrize("d,interleaved", [(16, False), (32, False), (48, False), (32, True)])
+def test_mha_int8_small_heads(cuda, d, interleaved):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(d + 3)
+    N = 6
+    lengths = np.array([260, 128, 0, 77, 1], dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, B, S = int(cu[-1]), len(lengths), 260
+    q8, s_qkv = _int8_case(rng, total, N, d)
+    dq_probs = 1.0 / 127.0
+    s_ctx = s_qkv * 0.5
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(1.0 / np.sqrt(d)))
+    s2 = dq_probs * s_qkv / s_ctx
+    ref = O.mha_int8(q8, B, S, N, d, s1, 1.0 / dq_probs, s2, cu=cu)
+    st = _status(cuda)
+    kw = dict(head_size=d, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=1.0 / dq_probs, scale_bmm2=s2, status=st)
+    if interleaved:
+        g = d // 32
+        il = np.ascontiguousarray(q8.reshape(total, N, 3, g, 32).transpose(2, 1, 3, 0, 4)).reshape(3 * N * g, total, 32)
+        out = T.mha(_t(il, cuda), B, S, N, interleaved=True, **kw)
+        out = out.cpu().numpy().reshape(N, g, total, 32).transpose(2, 0, 1, 3).reshape(total, N * d)
+    else:
+        out = T.mha(_t(q8, cuda), B, S, N, **kw).cpu().numpy()
+    assert int(st[0]) == 0
+    _assert_int8_attention(out, ref)
+
+
+@pytest.mark.parametrize("S,d", [(40, 80), (64, 24), (700, 64), (1100, 128)])
+def test_mha_fp16_outside_tensor_core_shapes(cuda, S, d):
+    """Heads wider than 64 or not a multiple of 16, sequences beyond 512: FP16 I/O through the SIMT kernel (the
+    shapes the reference gives to its unfused runner); INT8 is refused there, as in the reference."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S + d)
+    B, N = 2, 2
+    lengths = np.array([S, S // 3], dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    qkv = rng.standard_normal((int(cu[-1]), 3 * N * d)).astype(np.float16)
+    ref = O.mha(qkv, B, S, N, d, cu=cu)
+    out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda))
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+    with pytest.raises(RuntimeError, match="INT8 takes"):
+        T.mha(torch.zeros_like(_t(qkv, cuda), dtype=torch.int8), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda))
+
+
 @pytest.mark.parametrize("d", [32, 64])
 def test_mha_fp32(cuda, d):
     import tensorrt_b200 as T
