@@ -23,6 +23,8 @@
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
 #include "sm100.cuh"
 
+#include <type_traits>
+
 namespace b200
 {
 
@@ -35,7 +37,7 @@ constexpr int kQTile = 128;
 constexpr int kKeyBlock = 128;
 constexpr int kHeadSize = 64;
 constexpr int kMaxBlocks = 4; // S <= 512
-constexpr int kMhaThreads = 576;     // TMA warp, MMA warp, 16 softmax warps
+constexpr int kMhaThreads = 608;     // TMA warp, MMA warp, 16 softmax warps, second MMA warp (FP16)
 constexpr int kSoftmaxThreads = 512;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kOColumn = 384;   // context accumulator when the scores need at most 384 columns
@@ -299,49 +301,45 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             }
         }
     }
-    else if (warp == 1)
+    else if (warp == 1 || warp == kMhaThreads / 32 - 1)
     {
-        if (lane == 0)
-        {
+        // ---- MMA issue: scores S_j = Q K_j^T of the tile after the one the softmax warps work on, and
+        //      context_t += P_j V_j as they hand over P_j ----
+        // Every tcgen05.mma / tcgen05.commit keeps its issuing thread busy for some 50 cycles (measured), and one
+        // thread issuing both products of a tile was the slowest link of the tile pipeline: the scores are issued by
+        // a second thread in the last warp (+11 % at S = 384). Sequences of a single key block have too few MMAs per
+        // tile for that to pay (INT8, S = 128: -7 %) and keep one issuer.
+        bool const twoIssuers = !kInt8 || nbMax > 1;
+        // Operand descriptors are formed arithmetically: one low word per operand tile (+ bytes >> 4 per key block
+        // and MMA step, compile-time constants of the unrolled loops) and one high word per operand kind (mmaLoHi).
+        auto issuer = [&](auto doScoresTag, auto doContextTag) {
+            constexpr bool kDoScores = decltype(doScoresTag)::value;
+            constexpr bool kDoContext = decltype(doContextTag)::value;
             bool ok = true;
-            // All operand descriptors are fixed for the life of the CTA: build them once, outside the issue loops.
-            uint64_t qDesc[kQkMmas], kDesc[kMaxBlocks][kQkMmas], pDesc[kMaxBlocks][kPvMmas], vDesc[kMaxBlocks][kPvMmas];
-#pragma unroll
-            for (int k = 0; k < kQkMmas; ++k)
-                qDesc[k] = makeSmemDesc(smemAddr(sQ) + (IL ? k * kSubTile : k * 32), 16, kAtomBytes, kSwz);
-#pragma unroll
-            for (int j = 0; j < kMaxBlocks; ++j)
-            {
-                uint32_t const kAddr = smemAddr(sK + j * L::kTileBytes);
-                uint32_t const vAddr = smemAddr(sV + j * L::kTileBytes);
-                uint32_t const pAddr = smemAddr(sP + slotOf(j) * L::kPBytes);
-#pragma unroll
-                for (int k = 0; k < kQkMmas; ++k) // next 32 bytes of the head dimension
-                    kDesc[j][k] = makeSmemDesc(kAddr + (IL ? k * kSubTile : k * 32), 16, kAtomBytes, kSwz);
-#pragma unroll
-                for (int k = 0; k < kPvMmas; ++k)
-                {
-                    // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
-                    uint32_t const pOff = kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32;
-                    pDesc[j][k] = makeSmemDesc(pAddr + pOff, 16, 1024, kSwizzle128B);
-                    // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
-                    // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
-                    vDesc[j][k] = IL ? makeSmemDesc(vAddr + k * 1024, kSubTile, kAtomBytes, kSwz)
-                                     : makeSmemDesc(vAddr + k * 2048, kAtomBytes, kAtomBytes, kSwz);
-                }
-            }
+            uint64_t const dQk = makeSmemDesc(0, 16, kAtomBytes, kSwz);
+            // P: K-major, 128-byte rows, 128-byte swizzle. FP16 holds the block as two 64-key tiles.
+            uint64_t const dP = makeSmemDesc(0, 16, 1024, kSwizzle128B);
+            // V: MN-major (head dimension contiguous), one MMA consumes 16 (FP16) / 32 (INT8) key rows.
+            // Interleaved: the two 32-channel sub-tiles are LBO apart, 32 key rows are 1024 bytes.
+            uint64_t const dV = IL ? makeSmemDesc(0, kSubTile, kAtomBytes, kSwz) : makeSmemDesc(0, kAtomBytes, kAtomBytes, kSwz);
+            uint32_t const hiQk = static_cast<uint32_t>(dQk >> 32), hiP = static_cast<uint32_t>(dP >> 32),
+                           hiV = static_cast<uint32_t>(dV >> 32);
+            uint32_t const qLo = static_cast<uint32_t>(dQk) + (smemAddr(sQ) >> 4);
+            uint32_t const kLo = static_cast<uint32_t>(dQk) + (smemAddr(sK) >> 4);
+            uint32_t const vLo = static_cast<uint32_t>(dV) + (smemAddr(sV) >> 4);
+            uint32_t const pLo = static_cast<uint32_t>(dP) + (smemAddr(sP) >> 4);
+            uint32_t const pPairStep = nbMax <= 3 ? 2u * (L::kPBytes >> 4) : 0u; // slotOf(j) = (j & 1) + (j >> 1) * (2 or 0)
+            constexpr uint32_t kTile16 = L::kTileBytes >> 4;
             uint32_t qkTiles = 0;  // tiles whose scores have been issued
-            uint32_t pvTiles = 0;  // tiles whose context has been issued
+            uint32_t pvTiles = 0;  // tiles of this CTA that the loop below has passed (= whose context has been issued)
             uint32_t kBits = 0, vBits = 0, pBits = 0, fBits = 0; // parity per key block: K landed, V landed, P written, S read
             // scores of key block j for the query tile whose Q is in shared memory; nbOf = key blocks of that tile's item
             auto issueScores = [&](int j, int nbOf) {
 #pragma unroll
                 for (int k = 0; k < kQkMmas; ++k)
                 {
-                    if (kInt8)
-                        mmaI8(tmemBase + j * kKeyBlock, qDesc[k], kDesc[j][k], kIdescQk, k != 0);
-                    else
-                        mmaF16(tmemBase + j * kKeyBlock, qDesc[k], kDesc[j][k], kIdescQk, k != 0);
+                    uint32_t const off = (IL ? k * kSubTile : k * 32) >> 4; // next 32 bytes of the head dimension
+                    mmaLoHi<kInt8>(tmemBase + j * kKeyBlock, qLo + off, hiQk, kLo + j * kTile16 + off, hiQk, kIdescQk, k != 0);
                 }
                 tcCommit(&sFull[j]);
                 if (j == nbOf - 1)
@@ -355,7 +353,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             };
             Item cur, nxt;
             int item = nextWork(blockIdx.x, cur);
-            if (item < numItems)
+            if (kDoScores && item < numItems)
             {
                 ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
 #pragma unroll
@@ -375,7 +373,9 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             }
             while (item < numItems && ok)
             {
-                int const nextItem = nextWork(item + gridDim.x, nxt);
+                // only the scores look one item ahead (its geometry comes from global memory: not in the way of a
+                // thread that only issues context products)
+                int const nextItem = kDoScores ? nextWork(item + gridDim.x, nxt) : numItems;
                 for (int t = 0; t < cur.nq && ok; ++t)
                 {
                     bool const lastT = t + 1 == cur.nq;
@@ -390,7 +390,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                             // Scores of the following tile for this key block first: they only need the softmax warps
                             // to hold this tile's S_j in registers (sFree), not the finished P_j, and the next pass A
                             // waits for them, while this tile's context is not read before the pass after.
-                            if (j < nbFollow && !oAliasesScores)
+                            if (kDoScores && j < nbFollow && !oAliasesScores)
                             {
                                 if (j == 0)
                                     ok = mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
@@ -404,37 +404,42 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                                 }
                             }
                             fBits ^= 1u << j; // the softmax warps complete this phase in every tile that uses block j
-                            if (ok && t == 0)
+                            if (kDoContext)
                             {
-                                ok = mbarWait(&vFull[j], (vBits >> j) & 1u, abortFlag, kWaitTmaFull);
-                                vBits ^= 1u << j;
-                            }
-                            if (ok && j == 0 && pvTiles > 0) // the previous tile's context must have been read out
-                                ok = mbarWait(oFree, (pvTiles - 1) & 1, abortFlag, kWaitAccFree);
-                            ok = ok && mbarWait(&pReady[j], (pBits >> j) & 1u, abortFlag, kWaitSoftmax);
-                            pBits ^= 1u << j;
-                            if (ok)
-                            {
-                                tcFenceAfter();
-#pragma unroll
-                                for (int k = 0; k < kPvMmas; ++k)
+                                if (ok && t == 0)
                                 {
-                                    if (kInt8)
-                                        mmaI8(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
-                                    else
-                                        mmaF16(tmemBase + oCol, pDesc[j][k], vDesc[j][k], kIdescPv, (j | k) != 0);
+                                    ok = mbarWait(&vFull[j], (vBits >> j) & 1u, abortFlag, kWaitTmaFull);
+                                    vBits ^= 1u << j;
                                 }
-                                tcCommit(&pFree[slotOf(j)]);
-                                if (j == cur.nb - 1)
+                                if (ok && j == 0 && pvTiles > 0) // the previous tile's context must have been read out
+                                    ok = mbarWait(oFree, (pvTiles - 1) & 1, abortFlag, kWaitAccFree);
+                                ok = ok && mbarWait(&pReady[j], (pBits >> j) & 1u, abortFlag, kWaitSoftmax);
+                                pBits ^= 1u << j;
+                                if (ok)
                                 {
-                                    tcCommit(oFull);
-                                    if (lastT)
-                                        tcCommit(vFree);
+                                    tcFenceAfter();
+                                    uint32_t const a = pLo + (j & 1) * (L::kPBytes >> 4) + (j >> 1) * pPairStep;
+                                    uint32_t const b = vLo + j * kTile16;
+#pragma unroll
+                                    for (int k = 0; k < kPvMmas; ++k)
+                                    {
+                                        constexpr uint32_t kVStep = (IL ? 1024u : 2048u) >> 4;
+                                        uint32_t const pOff = (kInt8 ? k * 32 : (k / 4) * (kQTile * 128) + (k % 4) * 32) >> 4;
+                                        mmaLoHi<kInt8>(tmemBase + oCol, a + pOff, hiP, b + k * kVStep, hiV, kIdescPv, (j | k) != 0);
+                                    }
+                                    if (oAliasesScores) // otherwise every tile has its own P slots, released with oFull
+                                        tcCommit(&pFree[slotOf(j)]);
+                                    if (j == cur.nb - 1)
+                                    {
+                                        tcCommit(oFull);
+                                        if (lastT)
+                                            tcCommit(vFree);
+                                    }
                                 }
                             }
                         }
                     }
-                    if (ok && !oAliasesScores)
+                    if (kDoScores && ok && !oAliasesScores)
                     {
                         // key blocks the next item has beyond this one's: their score columns are idle
 #pragma unroll
@@ -451,7 +456,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                             }
                         }
                     }
-                    if (ok && nbFollow > 0 && oAliasesScores)
+                    if (kDoScores && ok && nbFollow > 0 && oAliasesScores)
                     {
                         // the context accumulator occupies score columns: wait until the epilogue has read it
                         ok = mbarWait(oFree, pvTiles & 1, abortFlag, kWaitAccFree) && mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
@@ -474,12 +479,29 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         ++qkTiles;
                     ++pvTiles;
                 }
-                cur = nxt;
-                item = nextItem;
+                if (kDoScores)
+                {
+                    cur = nxt;
+                    item = nextItem;
+                }
+                else
+                    item = nextWork(item + gridDim.x, cur);
             }
+        };
+        if (lane == 0)
+        {
+            if (!twoIssuers)
+            {
+                if (warp == 1)
+                    issuer(std::true_type{}, std::true_type{});
+            }
+            else if (warp == 1)
+                issuer(std::false_type{}, std::true_type{});
+            else
+                issuer(std::true_type{}, std::false_type{});
         }
     }
-    else
+    else if (warp < 2 + kSoftmaxThreads / 32)
     {
         int const quad = warp & 3;        // TMEM lanes [32*quad, 32*quad+32) are the ones this warp may touch
         int const sub = (warp - 2) >> 2;  // which 32 of every 128 key columns this thread owns (4 warps per quadrant)
@@ -494,8 +516,13 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         uint32_t sBits = 0;       // parity per key block of sFull (and of this thread's arrivals on pReady)
         uint32_t slotFilled = 0;  // per P slot: has it been filled before ...
         uint32_t slotParity = 0;  // ... and the parity of the pFree phase that ends its latest fill
-        // Before a P slot is refilled, the PV product that read its previous contents must have completed.
+        // Before a P slot is refilled, the PV product that read its previous contents must have completed (pFree is only
+        // signalled when four key blocks share two slots).
         auto acquireP = [&](int j) -> bool {
+            // One slot per key block (up to three blocks): a slot is refilled one tile later, after this thread has
+            // waited for the previous tile's complete context in its (deferred) epilogue - nothing to wait for.
+            if (!oAliasesScores)
+                return true;
             int const slot = slotOf(j);
             bool got = true;
             if ((slotFilled >> slot) & 1u)
@@ -596,8 +623,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 // ---- pass A: row maximum (INT8: integer maximum, no conversions) ----
                 float mx = -INFINITY;
                 int32_t mxi = INT32_MIN;
-#pragma unroll
-                for (int j = 0; j < kMaxBlocks; ++j)
+#pragma unroll 1
+                for (int j = 0; j < nb; ++j)
                 {
                     if (j < nb)
                     {
@@ -648,8 +675,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
 
                 // ---- pass B: exponentials, row sum; FP16 writes P here, INT8 parks exp values in TMEM ----
                 float sum = 0.f;
-#pragma unroll
-                for (int j = 0; j < kMaxBlocks; ++j)
+#pragma unroll 1
+                for (int j = 0; j < nb; ++j)
                 {
                     if (j < nb)
                     {
@@ -710,8 +737,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 {
                     // ---- pass C (INT8): P_q = rni(p / sum * scale_softmax) ----
                     float const pq = inv * args.scaleSoftmax;
-#pragma unroll
-                    for (int j = 0; j < kMaxBlocks; ++j)
+#pragma unroll 1
+                    for (int j = 0; j < nb; ++j)
                     {
                         if (j < nb)
                         {

@@ -216,6 +216,11 @@ __device__ __forceinline__ void tcCommit(uint64_t* bar)
                  : "memory");
 }
 
+__device__ __forceinline__ void tcCommitAddr(uint32_t barAddr)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barAddr) : "memory");
+}
+
 // D[tmem] (+)= A[smem] * B[smem]; issued by a single thread.
 __device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
 {
@@ -239,6 +244,39 @@ __device__ __forceinline__ void mmaI8(uint32_t dTmem, uint64_t aDesc, uint64_t b
         "}" ::"r"(dTmem),
         "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
+}
+
+// The same with the 64-bit descriptors assembled inside the asm block from their 32-bit halves: a thread that issues
+// many small MMAs keeps one low word per operand tile (start address in bits 0-13; + bytes >> 4 moves it) and one
+// constant high word per operand kind in registers instead of rebuilding or holding dozens of 64-bit descriptors.
+template <bool kInt8>
+__device__ __forceinline__ void mmaLoHi(
+    uint32_t dTmem, uint32_t aLo, uint32_t aHi, uint32_t bLo, uint32_t bHi, uint32_t iDesc, bool accumulate)
+{
+    if constexpr (kInt8)
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\t"
+            "mov.b64 da, {%1, %2};\n\t"
+            "mov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t"
+            "}" ::"r"(dTmem),
+            "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            ".reg .b64 da, db;\n\t"
+            "setp.ne.b32 p, %6, 0;\n\t"
+            "mov.b64 da, {%1, %2};\n\t"
+            "mov.b64 db, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t"
+            "}" ::"r"(dTmem),
+            "r"(aLo), "r"(aHi), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
+            : "memory");
 }
 
 // Lane l of the warp receives TMEM lane (base lane + l), 32 consecutive 32-bit columns.
