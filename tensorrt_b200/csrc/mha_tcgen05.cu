@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             if (kDoScores && item < numItems)
             {
                 ok = mbarWait(qFull, 0, abortFlag, kWaitTmaFull);
-#pragma unroll
+#pragma unroll 1
                 for (int j = 0; j < kMaxBlocks; ++j)
                 {
                     if (j < cur.nb && ok)
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     // the scores issued while this tile's context is formed: the item's next tile, or the first tile
                     // of the CTA's next item (whose K then has to have landed), or none
                     int const nbFollow = !lastT ? cur.nb : (nextItem < numItems ? nxt.nb : 0);
-#pragma unroll
+#pragma unroll 1
                     for (int j = 0; j < kMaxBlocks; ++j)
                     {
                         if (j < cur.nb && ok)
@@ -442,7 +442,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     if (kDoScores && ok && !oAliasesScores)
                     {
                         // key blocks the next item has beyond this one's: their score columns are idle
-#pragma unroll
+#pragma unroll 1
                         for (int j = 1; j < kMaxBlocks; ++j)
                         {
                             if (j >= cur.nb && j < nbFollow && ok)
@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     {
                         // the context accumulator occupies score columns: wait until the epilogue has read it
                         ok = mbarWait(oFree, pvTiles & 1, abortFlag, kWaitAccFree) && mbarWait(qFull, qkTiles & 1, abortFlag, kWaitTmaFull);
-#pragma unroll
+#pragma unroll 1
                         for (int j = 0; j < kMaxBlocks; ++j)
                         {
                             if (j < nbFollow && ok)

@@ -100,7 +100,9 @@ __device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
 // returns false. The kernel then drains, frees its TMEM and exits; the host sees the status word.
 constexpr uint64_t kWaitLimitNs = 2000000000ull; // 2 s
 
-__device__ __forceinline__ bool mbarWaitAddr(uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
+// The polling loop is one out-of-line copy per kernel image: inlined at every wait it was a sizeable part of the
+// code of the persistent kernels, whose single-thread roles are sensitive to instruction-cache misses.
+static __device__ __noinline__ bool mbarWaitSlow(uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
 {
     // The clock is only consulted every 256 failed polls (a read of %globaltimer costs far more than a poll, and most
     // waits end within a few polls), so the common case is nothing but try_wait.
@@ -124,6 +126,13 @@ __device__ __forceinline__ bool mbarWaitAddr(uint32_t barAddr, uint32_t parity, 
             }
         }
     }
+}
+
+__device__ __forceinline__ bool mbarWaitAddr(uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
+{
+    if (mbarTryWaitAddr(barAddr, parity))
+        return true;
+    return mbarWaitSlow(barAddr, parity, abortFlag, code);
 }
 
 __device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
