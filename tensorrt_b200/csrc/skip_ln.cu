@@ -39,6 +39,34 @@ __device__ __forceinline__ float rowSum(float v, float (*slots)[WPR > 1 ? WPR : 
     return t;
 }
 
+// Two sums at once (sum and sum of squares): one barrier for both.
+template <int WPR>
+__device__ __forceinline__ float2 rowSum2(float a, float b, float2 (*slots)[WPR > 1 ? WPR : 1], int rowInCta, int wInRow, int lane,
+    int& turn)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (WPR == 1)
+        return make_float2(a, b);
+    float2* const slot = slots[turn];
+    turn ^= 1;
+    if (lane == 0)
+        slot[wInRow] = make_float2(a, b);
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + rowInCta), "n"(WPR * 32) : "memory");
+    float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int w = 0; w < WPR; ++w)
+    {
+        t.x += slot[w].x;
+        t.y += slot[w].y;
+    }
+    return t;
+}
+
 template <typename T>
 struct Vec;
 template <>
@@ -214,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
 {
     constexpr int E = 16;
     constexpr int kRowsPerCta = kWarpsPerCta / WPR;
-    __shared__ float red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
+    __shared__ float2 red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
     int turn = 0;
 
     int const lane = threadIdx.x & 31;
@@ -223,7 +251,6 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
     int const wInRow = warp % WPR;
     int const chunksPerRow = ld / E;
     float const rld = 1.f / static_cast<float>(ld);
-    float const qLo = -128.f / qScale, qHi = 127.f / qScale; // qScale > 0 (checked by the caller)
 
     int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
@@ -239,8 +266,10 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
             a[i] = ok ? ldgStream(in + row * ld + c * E) : make_uint4(0, 0, 0, 0);
             b[i] = ok ? ldgStream(skip + row * ld + c * E) : make_uint4(0, 0, 0, 0);
         }
+        // Statistics in one sweep: FP32 sum and sum of squares (the reference's kernel forms the same two sums, in
+        // FP16: plugin/skipLayerNormPlugin/skipLayerNormKernel.cu:58-74), one block reduction for both.
         float x[CPL][E];
-        float s = 0.f;
+        float s = 0.f, q = 0.f;
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
@@ -277,27 +306,17 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
                 for (int j = 0; j < 4; ++j)
                     x[i][4 * w + j] = fmaf(dqIn, fa[j], fmaf(dqSkip, fb[j], fbias[4 * w + j]));
             }
+            // chunks beyond the row hold zeros (zero inputs, zero bias) and add nothing to either sum
 #pragma unroll
             for (int j = 0; j < E; ++j)
-                s += x[i][j];
-        }
-        float const mu = rowSum<WPR>(s, red[rowInCta], rowInCta, wInRow, lane, turn) * rld;
-        float q = 0.f;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i)
-        {
-            int const c = (i * WPR + wInRow) * 32 + lane;
-            if (c < chunksPerRow)
             {
-#pragma unroll
-                for (int j = 0; j < E; ++j)
-                {
-                    float const d = x[i][j] - mu;
-                    q += d * d;
-                }
+                s += x[i][j];
+                q = fmaf(x[i][j], x[i][j], q);
             }
         }
-        float const rsigma = rsqrtf(rowSum<WPR>(q, red[rowInCta], rowInCta, wInRow, lane, turn) * rld + eps);
+        float2 const sums = rowSum2<WPR>(s, q, red[rowInCta], rowInCta, wInRow, lane, turn);
+        float const mu = sums.x * rld;
+        float const rsigma = rsqrtf(fmaxf(fmaf(sums.y, rld, -mu * mu), 0.f) + eps);
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
