@@ -689,17 +689,31 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                             mbarArrive(&sFree[j]);
                         }
                         int const limit = len - colOf(j);
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
+                        // INT8: (acc - max) is formed exactly (integers through the 2^23 trick, no conversion unit),
+                        // so the exponent carries a single rounding; FP16: one fused multiply-add.
+                        auto expOf = [&](uint32_t v) {
+                            return kInt8 ? ex2Approx((__uint_as_float(v + kMagicBits) - mxMagic) * sl2)
+                                         : ex2Approx(fmaf(__uint_as_float(v), sl2, -mOff));
+                        };
+                        if (limit >= 32) // all 32 keys valid: no per-element select
                         {
-                            // INT8: (acc - max) is formed exactly (integers through the 2^23 trick, no conversion unit),
-                            // so the exponent carries a single rounding; FP16: one fused multiply-add.
-                            float e = kInt8 ? ex2Approx((__uint_as_float(x[i] + kMagicBits) - mxMagic) * sl2)
-                                            : ex2Approx(fmaf(__uint_as_float(x[i]), sl2, -mOff));
-                            if (limit < 32 && i >= limit)
-                                e = 0.f;
-                            sum += e;
-                            x[i] = __float_as_uint(e);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                            {
+                                float const e = expOf(x[i]);
+                                sum += e;
+                                x[i] = __float_as_uint(e);
+                            }
+                        }
+                        else
+                        {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                            {
+                                float const e = i < limit ? expOf(x[i]) : 0.f;
+                                sum += e;
+                                x[i] = __float_as_uint(e);
+                            }
                         }
                         if (kInt8)
                         {
