@@ -101,11 +101,20 @@ __device__ __forceinline__ float ex2Approx(float x)
 // Four non-negative values -> round-to-nearest-even integers saturated at 127, packed into one word.
 // Adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits (the FP32 adder rounds to nearest even,
 // like cvt.rni); the clamp at 127 is the saturation of the reference's conversion for scale_softmax > 127.
+// kClamp = false: the caller knows that no value exceeds 127.49 (scale_softmax <= 127 and p <= 1).
+template <bool kClamp>
 __device__ __forceinline__ uint32_t packProb4(float a, float b, float c, float d)
 {
     constexpr float kMagic = 12582912.f;
-    uint32_t const ua = __float_as_uint(fminf(a, 127.f) + kMagic), ub = __float_as_uint(fminf(b, 127.f) + kMagic);
-    uint32_t const uc = __float_as_uint(fminf(c, 127.f) + kMagic), ud = __float_as_uint(fminf(d, 127.f) + kMagic);
+    if (kClamp)
+    {
+        a = fminf(a, 127.f);
+        b = fminf(b, 127.f);
+        c = fminf(c, 127.f);
+        d = fminf(d, 127.f);
+    }
+    uint32_t const ua = __float_as_uint(a + kMagic), ub = __float_as_uint(b + kMagic);
+    uint32_t const uc = __float_as_uint(c + kMagic), ud = __float_as_uint(d + kMagic);
     return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
@@ -767,10 +776,24 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                             {
                                 uint4 o;
                                 uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+                                // p / sum <= 1 (the sum contains p; a rounded-up reciprocal adds a few ulp at most), so
+                                // with scale_softmax <= 127 nothing can round beyond 127 and the clamp is left out
+                                if (args.scaleSoftmax <= 127.f)
+                                {
 #pragma unroll
-                                for (int i = 0; i < 4; ++i)
-                                    w[i] = packProb4(__uint_as_float(x[g * 16 + 4 * i]) * pq, __uint_as_float(x[g * 16 + 4 * i + 1]) * pq,
-                                        __uint_as_float(x[g * 16 + 4 * i + 2]) * pq, __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                                    for (int i = 0; i < 4; ++i)
+                                        w[i] = packProb4<false>(__uint_as_float(x[g * 16 + 4 * i]) * pq,
+                                            __uint_as_float(x[g * 16 + 4 * i + 1]) * pq, __uint_as_float(x[g * 16 + 4 * i + 2]) * pq,
+                                            __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                                }
+                                else
+                                {
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i)
+                                        w[i] = packProb4<true>(__uint_as_float(x[g * 16 + 4 * i]) * pq,
+                                            __uint_as_float(x[g * 16 + 4 * i + 1]) * pq, __uint_as_float(x[g * 16 + 4 * i + 2]) * pq,
+                                            __uint_as_float(x[g * 16 + 4 * i + 3]) * pq);
+                                }
                                 int const chunk = sub * 2 + g; // 16 keys per 16-byte chunk
                                 *reinterpret_cast<uint4*>(pRow + ((chunk ^ (r & 7)) << 4)) = o;
                             }

@@ -92,6 +92,27 @@ def test_mha_packed_int8(cuda, lengths, N):
     _assert_int8_attention(out.cpu().numpy(), ref)
 
 
+def test_mha_int8_saturating_probabilities(cuda):
+    """scale_softmax > 127: probabilities near 1 saturate at 127 like the reference's conversion (the kernel leaves the
+    clamp out when scale_softmax <= 127)."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(77)
+    N, d = 3, 64
+    lengths = np.array([200, 3, 1, 130], dtype=np.int32)   # short sequences have probabilities close to 1
+    cu = O.cu_seqlens(lengths)
+    total, B, S = int(cu[-1]), len(lengths), 200
+    q8, s_qkv = _int8_case(rng, total, N, d)
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    scale_softmax, s2 = 200.0, 0.4 / 200.0
+    ref = O.mha_int8(q8, B, S, N, d, s1, scale_softmax, s2, cu=cu)
+    st = _status(cuda)
+    out = T.mha(_t(q8, cuda), B, S, N, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=scale_softmax, scale_bmm2=s2,
+                status=st)
+    assert int(st[0]) == 0
+    _assert_int8_attention(out.cpu().numpy(), ref)
+
+
 @pytest.mark.parametrize("S,B,N", [(128, 4, 12), (384, 2, 16)])
 def test_mha_fixed_int8(cuda, S, B, N):
     import tensorrt_b200 as T
