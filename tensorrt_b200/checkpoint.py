@@ -96,3 +96,26 @@ class QaHead:
         from . import ops
 
         return ops.fc(hidden, self.wt, bias=self.bias)[:, :2]
+
+
+class PoolerHead:
+    """The pooler of `BertModel` (`pooler.dense` + tanh on the first token of every sequence) on top of the packed
+    encoder output: the [CLS] rows are gathered with `cu_seqlens`, the dense layer runs through the FC kernel; the tanh
+    of the B x hidden result is left to torch (the FC plugin has no tanh epilogue, neither has the reference's)."""
+
+    def __init__(self, state_dict, device="cuda:0", prefix=""):
+        import torch
+
+        w = _np(state_dict[prefix + "pooler.dense.weight"])  # [hidden, hidden] = [out, in]
+        b = _np(state_dict[prefix + "pooler.dense.bias"])
+        self.wt = torch.from_numpy(np.ascontiguousarray(w.astype(np.float16))).to(device)
+        self.bias = torch.from_numpy(b.astype(np.float32)).to(device)
+
+    def __call__(self, hidden, cu_seqlens):
+        """hidden: FP16 [total, hidden]; cu_seqlens: int32 [B + 1] -> FP16 [B, hidden]."""
+        import torch
+
+        from . import ops
+
+        first = hidden.index_select(0, cu_seqlens[:-1].long()).contiguous()
+        return torch.tanh(ops.fc(first, self.wt, bias=self.bias).float()).half()

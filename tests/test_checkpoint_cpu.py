@@ -11,12 +11,12 @@ from tensorrt_b200.checkpoint import pack_padded_batch, params_from_bert_state_d
 transformers = pytest.importorskip("transformers")
 
 
-def make_hf(layers=2, hidden=128, heads=2, ffn=512, vocab=500, max_pos=64, seed=0):
+def make_hf(layers=2, hidden=128, heads=2, ffn=512, vocab=500, max_pos=64, seed=0, pooler=False):
     torch.manual_seed(seed)
     cfg = transformers.BertConfig(vocab_size=vocab, hidden_size=hidden, num_hidden_layers=layers, num_attention_heads=heads,
                                   intermediate_size=ffn, max_position_embeddings=max_pos, type_vocab_size=2,
                                   hidden_act="gelu", hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
-    model = transformers.BertModel(cfg, add_pooling_layer=False).eval()
+    model = transformers.BertModel(cfg, add_pooling_layer=pooler).eval()
     with torch.no_grad():
         for p in model.parameters():
             p.copy_((p + 0.05 * torch.randn_like(p)).half().float())  # biases / LayerNorm off their trivial init

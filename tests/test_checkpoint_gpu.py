@@ -78,3 +78,28 @@ def test_question_answering_head_matches_huggingface(cuda):
     assert got.shape == want.shape
     assert np.abs(got - want).max() < 5e-2, np.abs(got - want).max()
     enc.close()
+
+
+def test_pooler_head_matches_huggingface(cuda):
+    """BertModel.pooler_output: encoder + pooler (first token of every packed sequence) against Hugging Face."""
+    import tensorrt_b200 as T
+    from tensorrt_b200.checkpoint import PoolerHead, pack_padded_batch, params_from_bert_state_dict
+
+    model = make_hf(layers=2, hidden=256, heads=4, ffn=1024, vocab=700, max_pos=128, pooler=True)
+    rng = np.random.default_rng(9)
+    B, S = 5, 64
+    ids, seg, mask, lengths = padded_batch(rng, B, S, 700)
+    with torch.no_grad():
+        want = model(input_ids=torch.from_numpy(ids), token_type_ids=torch.from_numpy(seg),
+                     attention_mask=torch.from_numpy(mask)).pooler_output.numpy()
+    sd = model.state_dict()
+    p = params_from_bert_state_dict(sd, num_heads=4)
+    pid, pseg, cu = pack_padded_batch(ids, seg, mask)
+    dev = lambda a: torch.from_numpy(a).to(cuda)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    cu_dev = dev(cu)
+    hidden = enc.forward(dev(pid), dev(pseg), cu_dev, S)
+    got = PoolerHead(sd, cuda)(hidden, cu_dev).float().cpu().numpy()
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() < 3e-2, np.abs(got - want).max()
+    enc.close()
