@@ -1,24 +1,31 @@
-// Fused multi-head attention on the sm_100a tensor cores (head size 64, sequence length <= 512),
+// Fused multi-head attention on the sm_100a tensor cores (head sizes 16, 32, 48, 64; sequence length <= 512),
 // FP16 and INT8, fixed [S,B,N,3,d], packed [total,N,3,d] and INT8 CHW32-interleaved layouts.
 //
 // Replaces the precompiled fused attention kernels the reference launches through
-// FusedMHARunnerFP16/Int8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265) and the
-// unfused cuBLAS + softmax path (mhaRunner.cu:533-601).
+// FusedMHARunnerFP16/Int8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265), the head-size
+// padding copies (zeroPadding2d.cu:190-204: here the TMA unit zero-fills the channels beyond the head size) and, for
+// these shapes, the unfused cuBLAS + softmax path (mhaRunner.cu:533-601).
 //
-// One CTA = one (sequence, head); it loops over the 128-query tiles of that sequence so that K and V are loaded
-// once and the tensor pipe works on the next tile while the softmax warps finish the current one. 18 warps:
-//   warp 0    : TMA - every 128-key K / V block of the sequence once, then the Q tile of each iteration
+// Persistent CTAs (one per SM) take (sequence, head) work items round-robin. Per item a CTA loops over the 128-query
+// tiles of the sequence, so that K and V are loaded once and the tensor pipe works on the next tile (of this item or
+// the next) while the softmax warps finish the current one. 19 warps:
+//   warp 0    : TMA - the K / V blocks (128 keys each) of an item once, the Q tile of each iteration
 //               (swizzled shared-memory tiles, one mbarrier each).
-//   warp 1    : TMEM allocation (512 columns); one lane issues tcgen05.mma:
-//                 S_j = Q K_j^T           (128 x 128 per key block, accumulators in TMEM columns 128j..)
+//   warp 1    : TMEM allocation (512 columns); one lane issues the context products
 //                 O  += P_j V_j           (128 x 64, accumulator in TMEM columns 384..447; for S > 384 it re-uses
 //                                          the columns of S_0, which serialises consecutive tiles)
-//               and, right after P_j V_j of tile t, the scores S_j of tile t+1.
+//   warp 18   : one lane issues the scores of the following tile, per key block as soon as the softmax warps hold
+//               the current S_j in registers:
+//                 S_j = Q K_j^T           (128 x 128 per key block, accumulators in TMEM columns 128j..)
+//               (with a single key block per sequence warp 1 issues both and this warp idles).
 //   warps 2-17: softmax, four threads per query row (each owns 32 of every 128 key columns):
 //                 pass A  row maximum over all key blocks straight from TMEM,
 //                 pass B  p = exp2(x*scale*log2e - max) -> FP16 P_j into swizzled shared memory for the PV product
 //                         (INT8: exp values go back to TMEM, pass C quantises p/sum*scale_softmax to INT8 P_j),
-//                 epilogue O / rowsum (INT8: O * scale_bmm2, round, saturate) -> 128-bit global stores.
+//                 epilogue O / rowsum (INT8: O * scale_bmm2, round, saturate) -> 128-bit global stores, deferred
+//                         until after pass A of the next tile.
+//               The passes loop over the key blocks (not unrolled): unrolled, the kernel was bound by instruction
+//               fetch (122 KB of text, 77 % instruction-cache hits).
 // The whole score row lives in TMEM, so the softmax uses the exact row maximum and never rescales O.
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
 #include "sm100.cuh"
