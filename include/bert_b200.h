@@ -221,6 +221,11 @@ BERT_B200_API int32_t bert_b200_fc(bert_b200_fc_params const* params, void* stre
  * pad / unpad copies (plugin/bertQKVToContextPlugin/zeroPadding2d.cu:190-204). FP32 always, and FP16 outside
  * those shapes, run a SIMT kernel (the reference's unfused runner, mhaRunner.cu:533-601); INT8 outside them is
  * BERT_B200_NOT_SUPPORTED as in the reference (qkvToContextPlugin.cpp:530).
+ * FP16 with S > 512 and a head size of the tensor-core kernel stays on the tensor cores when `workspace` holds
+ * bert_b200_mha_workspace_size() bytes (16-byte aligned, contents irrelevant): the keys are processed in chunks of
+ * 384 by the same kernel, which leaves unnormalised FP32 context rows and the row statistics per chunk there, and a
+ * second kernel merges the chunks (the result of one softmax over all keys). The reference's unfused runner gets its
+ * score matrix from the plugin workspace the same way (qkvToContextPlugin.cpp:430-438).
  *
  * Layouts (ref: plugin/bertQKVToContextPlugin/README.md:26-30, mhaRunner.cu:550-552, 1006, 1171):
  *  - fixed  (cu_seqlens == NULL): qkv [S][B][N][3][d], out [S][B][N][d]; valid keys of sequence b
@@ -255,9 +260,15 @@ typedef struct bert_b200_mha_params
     float scale_softmax;
     float scale_bmm2;
     uint32_t* status_word;
+    void* workspace;         /* optional, see bert_b200_mha_workspace_size */
+    int64_t workspace_bytes;
 } bert_b200_mha_params;
 
 BERT_B200_API int32_t bert_b200_mha(bert_b200_mha_params const* params, void* stream);
+
+/* Bytes of `workspace` with which bert_b200_mha keeps this call on the tensor cores although S > 512; 0 when the
+ * call does not need one (or would not use it). ref: UnfusedMHARunner::getWorkspaceSize (mhaRunner.cu:522). */
+BERT_B200_API int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params);
 
 /* ------------------------------------------------------------------------------------------
  * Whole-encoder driver (host layer loop over the kernels above)

@@ -33,7 +33,8 @@ class FcParams(C.Structure):
 class MhaParams(C.Structure):
     _fields_ = [("type_id", i32), ("B", i32), ("S", i32), ("num_heads", i32), ("head_size", i32), ("total", i32),
                 ("qkv", vp), ("out", vp), ("cu_seqlens", vp), ("mask_idx", vp), ("interleaved", i32),
-                ("scale_bmm1", f32), ("scale_softmax", f32), ("scale_bmm2", f32), ("status_word", vp)]
+                ("scale_bmm1", f32), ("scale_softmax", f32), ("scale_bmm2", f32), ("status_word", vp), ("workspace", vp),
+                ("workspace_bytes", i64)]
 
 
 class LayerWeights(C.Structure):
@@ -66,6 +67,7 @@ SIGNATURES = {
     "bert_b200_packed_mask_to_lengths": (i32, [vp, i32, i32, u32, u32, u32, vp, vp]),
     "bert_b200_lengths_to_cu_seqlens": (i32, [vp, i32, vp, vp]),
     "bert_b200_fc": (i32, [C.POINTER(FcParams), vp]),
+    "bert_b200_mha_workspace_size": (i64, [C.POINTER(MhaParams)]),
     "bert_b200_mha": (i32, [C.POINTER(MhaParams), vp]),
     "bert_b200_encoder_workspace_size": (i64, [C.POINTER(EncoderConfig), i32, i32]),
     "bert_b200_encoder_create": (i32, [C.POINTER(EncoderConfig), C.POINTER(vp)]),

@@ -59,6 +59,12 @@ struct MhaArgs
     int32_t const* maskIdx;
     float scaleBmm1, scaleSoftmax, scaleBmm2;
     uint32_t* statusWord;
+    // Sequences longer than the score row that fits TMEM (PARTIAL kernels): the keys are cut into chunks of chunkKeys,
+    // every (sequence, head, chunk) is a work item that leaves its unnormalised context rows (FP32) and the row
+    // statistics (maximum in the log2 domain, sum of exponentials) here; mhaMergeKernel combines the chunks.
+    int32_t chunkKeys, numChunks;
+    float* partO;       // [chunk][row][head][64]
+    float2* partStats;  // [chunk][row][head]
 };
 
 template <typename T>
@@ -150,7 +156,7 @@ __device__ __forceinline__ void tmemStoreWait()
 
 // IL (INT8 only): CHW32-interleaved tensors. Q, K and V tiles then arrive as two 32-channel sub-tiles of
 // [128 tokens][32 B] (32-byte swizzle); the head dimension is covered by one MMA per sub-tile.
-template <typename T, bool IL>
+template <typename T, bool IL, bool PARTIAL>
 __global__ void __launch_bounds__(kMhaThreads, 1)
     mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, MhaArgs const args)
 {
@@ -173,11 +179,19 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     struct Item
     {
         int32_t b, head, rowBase, rows, len, nb, nq;
+        int32_t chunk, keyBase; // PARTIAL: which chunk of the keys, and its first key
     };
-    int const numItems = args.B * args.N;
+    int const numItems = args.B * args.N * (PARTIAL ? args.numChunks : 1);
     // Geometry of item i (uniform over the CTA; every role derives the same values). Returns whether the item has
     // work for the tensor pipeline (at least one query row and one valid key).
     auto getItem = [&](int i, Item& it) -> bool {
+        it.chunk = 0;
+        if (PARTIAL)
+        {
+            it.chunk = i % args.numChunks;
+            i /= args.numChunks;
+        }
+        it.keyBase = it.chunk * args.chunkKeys;
         it.b = i / args.N;
         it.head = i - it.b * args.N;
         if (args.fixedLayout)
@@ -192,6 +206,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             it.len = min(max(__ldg(args.cu + it.b + 1) - it.rowBase, 0), args.S);
             it.rows = it.len;
         }
+        if (PARTIAL)
+            it.len = min(max(it.len - it.keyBase, 0), args.chunkKeys); // this chunk's valid keys
         it.nb = (it.len + kKeyBlock - 1) / kKeyBlock; // key blocks
         it.nq = (it.rows + kQTile - 1) / kQTile;      // query tiles
         return it.rows > 0 && it.len > 0;
@@ -204,7 +220,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     };
 
     // The layout of shared memory and TMEM follows the longest sequence the launch admits.
-    int const nbMax = (args.S + kKeyBlock - 1) / kKeyBlock;
+    int const nbMax = ((PARTIAL ? args.chunkKeys : args.S) + kKeyBlock - 1) / kKeyBlock;
     // S > 384: the context accumulator has to share TMEM columns with the scores of key block 0
     bool const oAliasesScores = nbMax > 3;
     uint32_t const oCol = oAliasesScores ? 0u : kOColumn;
@@ -275,6 +291,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             for (int item = nextWork(blockIdx.x, it); item < numItems && ok; item = nextWork(item + gridDim.x, it))
             {
                 int32_t const rowK = args.fixedLayout ? 0 : it.rowBase;
+                int32_t const rowKv = rowK + it.keyBase; // first key of this item
                 // linear: (channel, which of [N][3], batch, row). interleaved: (channel, row, 32-channel group, which of [3][N])
                 auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
                     if (IL)
@@ -296,7 +313,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         for (int j = 0; j < it.nb; ++j)
                         {
                             mbarArriveExpectTx(&kFull[j], L::kTileBytes);
-                            load(sK + j * L::kTileBytes, &kFull[j], 1, rowK + j * kKeyBlock);
+                            load(sK + j * L::kTileBytes, &kFull[j], 1, rowKv + j * kKeyBlock);
                         }
                         // The PV products of the previous item have read V. (Not oFull: this thread may run ahead of
                         // or behind the per-tile barriers by more than one phase, and a parity wait is only meaningful
@@ -308,7 +325,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                         for (int j = 0; j < it.nb; ++j)
                         {
                             mbarArriveExpectTx(&vFull[j], L::kTileBytes);
-                            load(sV + j * L::kTileBytes, &vFull[j], 2, rowK + j * kKeyBlock);
+                            load(sV + j * L::kTileBytes, &vFull[j], 2, rowKv + j * kKeyBlock);
                         }
                     }
                     ++tiles;
@@ -564,6 +581,16 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             mbarArrive(oFree);
             if (dst == nullptr)
                 return;
+            if (PARTIAL)
+            {
+                // unnormalised FP32 context of this chunk of the keys (dst points into args.partO)
+                float4* const d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    d4[g] = make_float4(__uint_as_float(x[4 * g]), __uint_as_float(x[4 * g + 1]), __uint_as_float(x[4 * g + 2]),
+                        __uint_as_float(x[4 * g + 3]));
+                return;
+            }
             if (kInt8)
             {
                 float const s2 = args.scaleBmm2;
@@ -615,6 +642,19 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 return static_cast<T*>(args.out)
                     + ((static_cast<int64_t>(it.head) * (args.d / 32) + grp) * args.total + it.rowBase + q) * 32;
             };
+            // PARTIAL: row `q` of this item in the [chunk][row][head] arrays of the partial results
+            int64_t const partRows = args.fixedLayout ? static_cast<int64_t>(args.S) * args.B : args.total;
+            auto partIndex = [&](int q) -> int64_t {
+                int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + it.b : static_cast<int64_t>(it.rowBase) + q;
+                return (it.chunk * partRows + rr) * args.N + it.head;
+            };
+            if (PARTIAL && !work)
+            {
+                // no valid key in this chunk: it takes no part in the merge (sum 0)
+                for (int q = threadIdx.x - 64; q < it.rows; q += kSoftmaxThreads)
+                    args.partStats[partIndex(q)] = make_float2(-INFINITY, 0.f);
+                continue;
+            }
             if (!work)
             {
                 // no valid key: every probability is zero and so is the context row
@@ -812,10 +852,13 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 }
                 sBits ^= (1u << nb) - 1u; // every block of this tile used its sFull / pReady phase
                 int const q = t * kQTile + r;
+                if (PARTIAL && sub == 0 && q < it.rows)
+                    args.partStats[partIndex(q)] = make_float2(mOff, sum);
                 // this thread's 16 of the 64 context columns; columns >= d are the zero padding
                 T* const dst = q >= it.rows || sub * 16 >= args.d
                     ? nullptr
-                    : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16);
+                    : (PARTIAL ? reinterpret_cast<T*>(args.partO + partIndex(q) * kHeadSize + sub * 16)
+                               : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16));
                 ++tiles;
                 if (deferEpilogue)
                 {
@@ -851,7 +894,64 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     }
 }
 
-template <typename T, bool IL>
+constexpr int kChunkKeys = 3 * kKeyBlock; // PARTIAL kernels: keys per chunk (the score columns that leave room for O)
+
+// Bytes of [chunks][rows][heads] x (64 FP32 context values + float2 statistics).
+inline int64_t partialBytes(bert_b200_mha_params const& p)
+{
+    int64_t const chunks = (p.S + kChunkKeys - 1) / kChunkKeys;
+    int64_t const rows = p.cu_seqlens ? p.total : static_cast<int64_t>(p.S) * p.B;
+    return chunks * rows * p.num_heads * (kHeadSize * 4 + 8);
+}
+
+// out[row][head][:d] = sum_c w_c O_c / sum_c w_c l_c with w_c = 2^(m_c - max_c m_c): the chunks of the keys combined
+// exactly as one softmax over all keys. One thread per (row, head, 8 channels).
+__global__ void __launch_bounds__(256) mhaMergeKernel(int64_t const rowsHeads, int32_t const numChunks, int32_t const d,
+    float const* __restrict__ partO, float2 const* __restrict__ partStats, __half* __restrict__ out)
+{
+    int const groups = d / 8;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < rowsHeads * groups;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    {
+        int64_t const rh = i / groups;
+        int const g = static_cast<int>(i - rh * groups);
+        float m = -INFINITY;
+        for (int c = 0; c < numChunks; ++c)
+        {
+            float2 const st = partStats[c * rowsHeads + rh];
+            if (st.y > 0.f)
+                m = fmaxf(m, st.x);
+        }
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float l = 0.f;
+        for (int c = 0; c < numChunks; ++c)
+        {
+            float2 const st = partStats[c * rowsHeads + rh];
+            if (st.y > 0.f) // a chunk without valid keys has written no context
+            {
+                float const w = exp2f(st.x - m);
+                l = fmaf(w, st.y, l);
+                float4 const* o = reinterpret_cast<float4 const*>(partO + (c * rowsHeads + rh) * kHeadSize + g * 8);
+                float4 const a = o[0], b = o[1];
+                acc[0] = fmaf(w, a.x, acc[0]);
+                acc[1] = fmaf(w, a.y, acc[1]);
+                acc[2] = fmaf(w, a.z, acc[2]);
+                acc[3] = fmaf(w, a.w, acc[3]);
+                acc[4] = fmaf(w, b.x, acc[4]);
+                acc[5] = fmaf(w, b.y, acc[5]);
+                acc[6] = fmaf(w, b.z, acc[6]);
+                acc[7] = fmaf(w, b.w, acc[7]);
+            }
+        }
+        float const inv = l > 0.f ? 1.f / l : 0.f; // no valid key at all: zero row
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            acc[j] *= inv;
+        *reinterpret_cast<uint4*>(out + rh * d + g * 8) = packHalf8(acc);
+    }
+}
+
+template <typename T, bool IL, bool PARTIAL = false>
 int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
 {
     using L = MhaSmem<T>;
@@ -886,19 +986,35 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
         if (st != BERT_B200_OK)
             return st;
     }
-    int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
+    int const nbMax = ((PARTIAL ? kChunkKeys : p.S) + kKeyBlock - 1) / kKeyBlock;
     int const smem = L::dynamicBytes(nbMax);
-    auto kernel = mhaTcgen05Kernel<T, IL>;
+    auto kernel = mhaTcgen05Kernel<T, IL, PARTIAL>;
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     MhaArgs args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
-        p.scale_softmax, p.scale_bmm2, p.status_word};
+        p.scale_softmax, p.scale_bmm2, p.status_word, 0, 1, nullptr, nullptr};
+    int64_t const rows = fixedLayout ? static_cast<int64_t>(p.S) * p.B : p.total;
+    if (PARTIAL)
+    {
+        args.chunkKeys = kChunkKeys;
+        args.numChunks = (p.S + kChunkKeys - 1) / kChunkKeys;
+        args.partO = static_cast<float*>(p.workspace);
+        args.partStats = reinterpret_cast<float2*>(args.partO + args.numChunks * rows * p.num_heads * kHeadSize);
+    }
     // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
-    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
+    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B * args.numChunks;
     int const grid = static_cast<int>(items < smCount() ? items : smCount());
     kernel<<<grid, kMhaThreads, smem, stream>>>(map, args);
-    return checkLaunch("mhaTcgen05Kernel");
+    int32_t const st = checkLaunch("mhaTcgen05Kernel");
+    if (!PARTIAL || st != BERT_B200_OK)
+        return st;
+    int64_t const work = rows * p.num_heads * (p.head_size / 8);
+    int64_t const want = (work + 255) / 256;
+    int const mergeGrid = static_cast<int>(want < smCount() * 8ll ? want : smCount() * 8ll);
+    mhaMergeKernel<<<mergeGrid, 256, 0, stream>>>(rows * p.num_heads, args.numChunks, p.head_size, args.partO, args.partStats,
+        static_cast<__half*>(p.out));
+    return checkLaunch("mhaMergeKernel");
 }
 
 } // namespace
@@ -925,6 +1041,12 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
     bool const lengthOk = p.S <= kMaxBlocks * kKeyBlock;
     // Outside the tensor-core kernel's shapes FP16 takes the SIMT kernel, like the reference's unfused runner
     // (qkvToContextPlugin.cpp:335-341, 522-531); INT8 has no such path there either (qkvToContextPlugin.cpp:530).
+    if (headOk && !lengthOk && p.type_id == BERT_B200_FP16 && p.workspace != nullptr && p.workspace_bytes >= partialBytes(p))
+    {
+        // longer than the score row that fits TMEM: chunks of the keys through the same kernel, then a merge
+        B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out) && aligned16(p.workspace), "mha: qkv, out and workspace must be 16-byte aligned");
+        return launchMha<__half, false, true>(p, s);
+    }
     if ((!headOk || !lengthOk) && p.type_id == BERT_B200_FP16)
         return mhaSimt(p, s);
     if (!headOk)
@@ -942,4 +1064,12 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
     if (p.type_id == BERT_B200_FP16)
         return launchMha<__half, false>(p, s);
     return launchMha<int8_t, false>(p, s);
+}
+
+extern "C" int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params)
+{
+    if (params == nullptr || params->type_id != BERT_B200_FP16 || params->interleaved || params->S <= kMaxBlocks * kKeyBlock
+        || params->head_size > kHeadSize || params->head_size % 16 != 0 || params->B < 0 || params->num_heads <= 0)
+        return 0;
+    return partialBytes(*params);
 }

@@ -151,7 +151,7 @@ def fc(a, wt, bias=None, activation=ACT_NONE, alpha=1.0, out_dtype=None, out_sca
 
 
 def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scale_bmm1=None, scale_softmax=1.0,
-        scale_bmm2=1.0, status=None, interleaved=False):
+        scale_bmm2=1.0, status=None, interleaved=False, workspace=None, use_workspace=True):
     """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None), packed [total, 3*N*d], or with
     interleaved=True the INT8 CHW32 form [3*N*d/32, total, 32] (output [N*d/32, total, 32])."""
     E = num_heads * head_size
@@ -168,5 +168,10 @@ def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scal
         scale_bmm1 = head_size ** -0.5
     p = _lib.MhaParams(_TYPE_ID[qkv.dtype], B, S, num_heads, head_size, total, _ptr(qkv), _ptr(out), _ptr(cu_seqlens),
                        _ptr(mask_idx), 1 if interleaved else 0, scale_bmm1, scale_softmax, scale_bmm2, _ptr(status))
+    if workspace is None and use_workspace:
+        need = int(lib.bert_b200_mha_workspace_size(C.byref(p)))
+        workspace = torch.empty(need, dtype=torch.uint8, device=qkv.device) if need > 0 else None
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = _ptr(workspace), workspace.numel() * workspace.element_size()
     check(lib.bert_b200_mha(C.byref(p), _stream()), "mha")
     return out

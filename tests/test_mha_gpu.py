@@ -225,11 +225,49 @@ def test_mha_fp16_outside_tensor_core_shapes(cuda, S, d):
     cu = O.cu_seqlens(lengths)
     qkv = rng.standard_normal((int(cu[-1]), 3 * N * d)).astype(np.float16)
     ref = O.mha(qkv, B, S, N, d, cu=cu)
-    out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda))
+    out = T.mha(_t(qkv, cuda), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda), use_workspace=False)
     ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
     assert ok, (worst, bad)
     with pytest.raises(RuntimeError, match="INT8 takes"):
         T.mha(torch.zeros_like(_t(qkv, cuda), dtype=torch.int8), B, S, N, head_size=d, cu_seqlens=_t(cu, cuda))
+
+
+@pytest.mark.parametrize("S,d", [(513, 64), (700, 64), (1100, 32), (1536, 64), (2000, 48)])
+@pytest.mark.parametrize("packed", [False, True])
+def test_mha_fp16_long_sequences_on_tensor_cores(cuda, S, d, packed):
+    """S > 512 with a workspace: chunks of 384 keys through the tensor-core kernel and a merge - one softmax over all
+    keys. Sequences shorter than a chunk boundary leave whole chunks without keys; one sequence has no key at all."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S + d + packed)
+    N = 3
+    lengths = np.array([S, 0, 385, S // 2, 1, 384], dtype=np.int32)
+    B = len(lengths)
+    st = _status(cuda)
+    if packed:
+        cu = O.cu_seqlens(lengths)
+        qkv = rng.standard_normal((int(cu[-1]), 3 * N * d)).astype(np.float16)
+        ref = O.mha(qkv, B, S, N, d, cu=cu)
+        kw = dict(cu_seqlens=_t(cu, cuda))
+    else:
+        qkv = rng.standard_normal((S, B, 3 * N * d)).astype(np.float16)
+        ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+        kw = dict(mask_idx=_t(lengths, cuda))
+    q = _t(qkv, cuda)
+    p = T._lib.MhaParams(1, B, S, N, d, int(lengths.sum()) if packed else 0, None, None, None, None, 0, 1.0, 1.0, 1.0, None, None, 0)
+    p.cu_seqlens = kw["cu_seqlens"].data_ptr() if packed else None
+    need = int(T._lib.lib.bert_b200_mha_workspace_size(T._lib.C.byref(p)))
+    rows = int(lengths.sum()) if packed else S * B
+    assert need == -(-S // 384) * rows * N * (64 * 4 + 8)
+    ws = torch.full((need,), 0xFF, dtype=torch.uint8, device=cuda)   # NaN patterns: nothing may leak from unwritten parts
+    out = T.mha(q, B, S, N, head_size=d, status=st, workspace=ws, **kw)
+    assert int(st[0]) == 0
+    assert out.shape == ref.shape
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+    # the same call without (or with too small a) workspace takes the SIMT kernel: same result within tolerance
+    slow = T.mha(q, B, S, N, head_size=d, workspace=ws[: need // 2], **kw)
+    assert O.close_abs_or_rel(slow.cpu().numpy(), ref, 1e-2, 1e-2)[0]
 
 
 @pytest.mark.parametrize("d", [32, 64])

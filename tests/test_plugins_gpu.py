@@ -80,6 +80,31 @@ def test_emb_v6_then_qkv_v4(cuda, S):
     qkv_p.close()
 
 
+def test_qkv_plugin_fp16_beyond_512_tokens(cuda):
+    """Version 4, FP16, S = 640: the plugin asks for the workspace of the chunked tensor-core path (the reference asks
+    for its unfused runner's score matrix there) and the result is one softmax over all 640 keys."""
+    from tensorrt_b200 import plugin_harness as H
+
+    rng = np.random.default_rng(12)
+    S, B, N, E = 640, 3, 2, 128
+    lengths = np.array([640, 200, 513], dtype=np.int32)
+    qkv_p = H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", E), ("num_heads", N), ("has_mask", 1)]).attach()
+    qkv = rng.standard_normal((S, B, 3 * E)).astype(np.float16)
+    ctx = torch.empty((S, B, E), dtype=torch.float16, device=cuda)
+    ind = [H.make_dyn((S, B, 3 * E, 1, 1), H.HALF), H.make_dyn((B,), H.INT32)]
+    outd = [H.make_dyn((S, B, E, 1, 1), H.HALF)]
+    assert qkv_p.configure(ind, outd) == 0
+    need = qkv_p.workspace_size(ind, outd)
+    assert need >= 2 * S * B * N * (64 * 4 + 8)   # two chunks of 384 keys
+    ws = torch.full((need,), 0xFF, dtype=torch.uint8, device=cuda)
+    assert qkv_p.on_shape_change([d.desc for d in ind], [d.desc for d in outd]) == 0
+    _run(qkv_p, H, [_t(qkv, cuda), _t(lengths, cuda)], [ctx], [d.desc for d in ind], [d.desc for d in outd], ws)
+    ref = O.mha(qkv, B, S, N, 64, lengths=lengths)
+    ok, worst, bad = O.close_abs_or_rel(ctx.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+    qkv_p.close()
+
+
 @pytest.mark.parametrize("ver", ["4", "5"])
 def test_emb_var_seqlen_plugin(cuda, ver):
     from tensorrt_b200 import plugin_harness as H
