@@ -27,6 +27,9 @@
 //               The passes loop over the key blocks (not unrolled): unrolled, the kernel was bound by instruction
 //               fetch (122 KB of text, 77 % instruction-cache hits).
 // The whole score row lives in TMEM, so the softmax uses the exact row maximum and never rescales O.
+// FP16 sequences beyond 512 keys (PARTIAL instantiation): the keys are cut into chunks of 384, every (sequence, head,
+// chunk) is a work item that leaves its unnormalised FP32 context rows and the row statistics in a workspace, and
+// mhaMergeKernel combines the chunks - numerically one softmax over all keys.
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
 #include "sm100.cuh"
 
