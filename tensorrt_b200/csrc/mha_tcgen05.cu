@@ -134,9 +134,17 @@ __device__ __forceinline__ uint32_t packProb4(float a, float b, float c, float d
     return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
 }
 
-__device__ __forceinline__ void softmaxBarrier()
+// The row reductions only join the four warps that own the columns of the same 32 query rows (one TMEM lane
+// quadrant). FP16: one named barrier per quadrant, so that the quadrants drift apart instead of waiting for the
+// slowest (+6 % at S = 384). INT8: all sixteen warps in step - its per-key-block hand-overs to the MMA threads need
+// every warp's arrival anyway, and drifting quadrants delay them (per-quadrant barriers: -4 %).
+template <bool kPerQuadrant>
+__device__ __forceinline__ void softmaxBarrier(int quad)
 {
-    asm volatile("bar.sync 1, 512;" ::: "memory");
+    if (kPerQuadrant)
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + quad) : "memory");
+    else
+        asm volatile("bar.sync 1, 512;" ::: "memory");
 }
 
 __device__ __forceinline__ void tmemStore32(uint32_t taddr, uint32_t const (&r)[32])
@@ -727,7 +735,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                     pending = false;
                 }
                 rowRed[sub * kQTile + r] = mx;
-                softmaxBarrier();
+                softmaxBarrier<!kInt8>(quad);
                 mx = fmaxf(fmaxf(rowRed[r], rowRed[kQTile + r]), fmaxf(rowRed[2 * kQTile + r], rowRed[3 * kQTile + r]));
                 float const mOff = mx * sl2;
                 float const mxMagic = kMagic + mx; // exact: both are integers below 2^24
@@ -802,7 +810,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 if (kInt8)
                     tmemStoreWait();
                 rowRed[4 * kQTile + sub * kQTile + r] = sum;
-                softmaxBarrier();
+                softmaxBarrier<!kInt8>(quad);
                 sum = (rowRed[4 * kQTile + r] + rowRed[5 * kQTile + r]) + (rowRed[6 * kQTile + r] + rowRed[7 * kQTile + r]);
                 float const inv = 1.f / sum;
 
