@@ -56,8 +56,43 @@ inline bool aligned16(void const* p)
 // Number of SMs of the current device (cached per device id).
 int32_t smCount();
 
+// Whether kernels are launched with programmatic stream serialisation (on unless BERT_B200_PDL=0): a kernel that
+// follows another one in its stream may then start - set up its barriers, allocate tensor memory, fetch descriptors -
+// while the earlier grid drains; it calls gridDependencyWait() before it touches global memory.
+bool dependentLaunchEnabled();
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launchDependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dependentLaunchEnabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 #ifdef __CUDACC__
 // ---- device helpers -----------------------------------------------------------------------
+
+// Programmatic dependent launch: let the next kernel of the stream start its set-up now ...
+__device__ __forceinline__ void gridDependencyLaunch()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// ... and wait until the grids this one depends on have completed and their writes are visible. Every thread calls it
+// before its first access to global memory; a no-op for a kernel launched without the attribute.
+__device__ __forceinline__ void gridDependencyWait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float warpSum(float v)
 {

@@ -583,6 +583,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFcThreads, 1)
     clusterSync(); // both CTAs' barriers are initialised before any remote arrival or TMA signal
     tcFenceAfter();
     uint32_t const tmemBase = *tmemSlot;
+    // set-up done: the next kernel of the stream may start its own; the operands of this one must be complete
+    gridDependencyLaunch();
+    gridDependencyWait();
 
     int64_t const mBlocks = (args.M + kPairM - 1) / kPairM;
     int64_t const nBlocks = (args.N + BLOCK_N - 1) / BLOCK_N;
@@ -831,7 +834,9 @@ int32_t launchFcPair(bert_b200_fc_params const& p, cudaStream_t stream)
     int const grid = static_cast<int>(2 * (tiles < pairs ? tiles : pairs));
     FcArgs args{p.m, p.n, p.k, p.c, p.ldc, p.bias, p.activation, p.alpha, p.out_scale, p.status_word,
         p.out_scale > 0.f ? -128.f / p.out_scale : 0.f, p.out_scale > 0.f ? 127.f / p.out_scale : 0.f};
-    kernel<<<grid, kFcThreads, L::kDynamic, stream>>>(mapA, mapB, mapC, args);
+    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kFcThreads), L::kDynamic, stream, mapA, mapB, mapC, args);
+    if (le != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "fcTcgen05PairKernel: %s", cudaGetErrorString(le));
     return checkLaunch("fcTcgen05PairKernel");
 }
 

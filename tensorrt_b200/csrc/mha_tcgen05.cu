@@ -288,6 +288,9 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     __syncthreads();
     tcFenceAfter();
     uint32_t const tmemBase = *tmemSlot;
+    // set-up done: the next kernel of the stream may start its own; the inputs of this one must be complete
+    gridDependencyLaunch();
+    gridDependencyWait();
 
     // Barriers that complete once per tile (qFull, qFree, oFull, oFree) are waited on with the parity of the CTA's
     // running tile count; those that complete once per use of key block j keep one parity bit per block.
@@ -1016,7 +1019,9 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
     int64_t const items = static_cast<int64_t>(p.num_heads) * p.B * args.numChunks;
     int const grid = static_cast<int>(items < smCount() ? items : smCount());
-    kernel<<<grid, kMhaThreads, smem, stream>>>(map, args);
+    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, map, args);
+    if (le != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "mhaTcgen05Kernel: %s", cudaGetErrorString(le));
     int32_t const st = checkLaunch("mhaTcgen05Kernel");
     if (!PARTIAL || st != BERT_B200_OK)
         return st;

@@ -1,6 +1,8 @@
 // Host-side runtime pieces shared by all kernels: error text, device properties, status word.
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <mutex>
 
 namespace b200
@@ -40,6 +42,15 @@ int32_t smCount()
         cache[dev] = n;
     }
     return cache[dev];
+}
+
+bool dependentLaunchEnabled()
+{
+    static int const on = [] {
+        char const* e = std::getenv("BERT_B200_PDL");
+        return (e != nullptr && e[0] == '0') ? 0 : 1;
+    }();
+    return on != 0;
 }
 
 } // namespace b200

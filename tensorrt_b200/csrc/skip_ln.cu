@@ -118,6 +118,8 @@ __global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64
     int const wInRow = warp % WPR;
     int const chunksPerRow = ld / E;
     float const rld = 1.f / static_cast<float>(ld);
+    gridDependencyLaunch();
+    gridDependencyWait(); // the rows come from the previous kernel of the stream
 
     int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
@@ -251,6 +253,8 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
     int const wInRow = warp % WPR;
     int const chunksPerRow = ld / E;
     float const rld = 1.f / static_cast<float>(ld);
+    gridDependencyLaunch();
+    gridDependencyWait(); // the rows come from the previous kernel of the stream
 
     int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
@@ -495,9 +499,11 @@ int32_t launchSkipLn(cudaStream_t stream, int32_t ld, int64_t rows, T const* in,
     int const rowsPerCta = kWarpsPerCta / WPR;
     int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 8);
     if (bias)
-        skipLnKernel<T, CPL, WPR, true><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+        launchDependent(skipLnKernel<T, CPL, WPR, true>, dim3(grid), dim3(kThreads), 0, stream, ld, rows, in, skip, beta, gamma, bias,
+            out, eps);
     else
-        skipLnKernel<T, CPL, WPR, false><<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, eps);
+        launchDependent(skipLnKernel<T, CPL, WPR, false>, dim3(grid), dim3(kThreads), 0, stream, ld, rows, in, skip, beta, gamma, bias,
+            out, eps);
     return checkLaunch("skipLnKernel");
 }
 
@@ -555,11 +561,11 @@ int32_t launchDqq(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* i
     int const rowsPerCta = kWarpsPerCta / WPR;
     int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 8);
     if (bias)
-        skipLnDqqKernel<CPL, WPR, true>
-            <<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+        launchDependent(skipLnDqqKernel<CPL, WPR, true>, dim3(grid), dim3(kThreads), 0, stream, ld, rows, in, skip, beta, gamma, bias,
+            out, dqIn, dqSkip, qScale, 0.f);
     else
-        skipLnDqqKernel<CPL, WPR, false>
-            <<<grid, kThreads, 0, stream>>>(ld, rows, in, skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+        launchDependent(skipLnDqqKernel<CPL, WPR, false>, dim3(grid), dim3(kThreads), 0, stream, ld, rows, in, skip, beta, gamma,
+            bias, out, dqIn, dqSkip, qScale, 0.f);
     return checkLaunch("skipLnDqqKernel");
 }
 
