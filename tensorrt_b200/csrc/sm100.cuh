@@ -90,11 +90,6 @@ __device__ __forceinline__ bool mbarTryWaitAddr(uint32_t barAddr, uint32_t parit
     return ok != 0;
 }
 
-__device__ __forceinline__ bool mbarTryWait(uint64_t* bar, uint32_t parity)
-{
-    return mbarTryWaitAddr(smemAddr(bar), parity);
-}
-
 // Every spin in these kernels is bounded: after kWaitLimitNs without progress the waiter records
 // `code` in *abortFlag (shared memory; every later wait in the CTA returns immediately) and
 // returns false. The kernel then drains, frees its TMEM and exits; the host sees the status word.
@@ -225,11 +220,6 @@ __device__ __forceinline__ void tcCommit(uint64_t* bar)
                  : "memory");
 }
 
-__device__ __forceinline__ void tcCommitAddr(uint32_t barAddr)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barAddr) : "memory");
-}
-
 // D[tmem] (+)= A[smem] * B[smem]; issued by a single thread.
 __device__ __forceinline__ void mmaF16(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
 {
@@ -314,11 +304,6 @@ __device__ __forceinline__ void tmemLoad16(uint32_t taddr, uint32_t (&r)[16])
         : "memory");
 }
 
-__device__ __forceinline__ void tmemLoadWait()
-{
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 // tcgen05.ld is asynchronous: its destination registers may only be read after tcgen05.wait::ld. Passing the
 // registers through the wait as read-write operands makes every later use depend on it, so the compiler cannot
 // schedule arithmetic on them ahead of the wait (needed when a load is left in flight across other work).
@@ -372,16 +357,6 @@ __device__ __forceinline__ void mbarArriveCluster(uint32_t clusterAddr)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
 }
 
-// Tile into this CTA's shared memory; the transaction bytes are counted on the mbarrier at `barClusterAddr`,
-// which may live in the peer CTA (the leader's "full" barrier collects both CTAs' loads).
-__device__ __forceinline__ void tmaLoad2dPair(void* dst, CUtensorMap const* map, uint32_t barClusterAddr, int32_t c0, int32_t c1)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smemAddr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(barClusterAddr), "r"(c0), "r"(c1)
-        : "memory");
-}
-
 // Executed by the same warp index in both CTAs of the pair.
 __device__ __forceinline__ void tmemAllocPair(uint32_t* dst, uint32_t columns)
 {
@@ -402,30 +377,6 @@ __device__ __forceinline__ void tcCommitPair(uint64_t* bar, uint16_t ctaMask)
     asm volatile(
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smemAddr(bar)),
         "h"(ctaMask)
-        : "memory");
-}
-
-__device__ __forceinline__ void mmaF16Pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-        "}" ::"r"(dTmem),
-        "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
-        : "memory");
-}
-
-__device__ __forceinline__ void mmaI8Pair(uint32_t dTmem, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, bool accumulate)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
-        "}" ::"r"(dTmem),
-        "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
         : "memory");
 }
 
@@ -471,6 +422,8 @@ __device__ __forceinline__ void tcCommitPairAddr(uint32_t barAddr, uint16_t ctaM
         : "memory");
 }
 
+// Tile into this CTA's shared memory (`dstAddr`, a shared::cta address); the transaction bytes are counted on the
+// mbarrier at `barClusterAddr`, which may live in the peer CTA (the leader's "full" barrier collects both CTAs' loads).
 __device__ __forceinline__ void tmaLoad2dPairAddr(uint32_t dstAddr, CUtensorMap const* map, uint32_t barClusterAddr, int32_t c0, int32_t c1)
 {
     asm volatile(
