@@ -266,6 +266,33 @@ typedef struct bert_b200_mha_params
 
 BERT_B200_API int32_t bert_b200_mha(bert_b200_mha_params const* params, void* stream);
 
+/*
+ * The same attention on separate Q, K, V tensors of shape [B][N][S][d] with the output [B][N][S][d] - the operand
+ * layout of TensorRT's IAttention layer, to which the reference's README tells users to migrate
+ * (plugin/bertQKVToContextPlugin/README.md:43-131). FP16 or INT8, head sizes 16 / 32 / 48 / 64, S <= 512;
+ * `kv_lengths` (may be NULL: all S) holds the valid keys per sequence like `mask_idx` above; the three scales as above.
+ * ref: none in the plugin library (the migration target is a TensorRT layer, not a plugin).
+ */
+typedef struct bert_b200_attention_bnsd_params
+{
+    int32_t type_id;
+    int32_t B;
+    int32_t S;
+    int32_t num_heads;
+    int32_t head_size;
+    void const* q;
+    void const* k;
+    void const* v;
+    void* out;
+    int32_t const* kv_lengths;
+    float scale_bmm1;
+    float scale_softmax;
+    float scale_bmm2;
+    uint32_t* status_word;
+} bert_b200_attention_bnsd_params;
+
+BERT_B200_API int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params const* params, void* stream);
+
 /* Bytes of `workspace` with which bert_b200_mha keeps this call on the tensor cores although S > 512; 0 when the
  * call does not need one (or would not use it). ref: UnfusedMHARunner::getWorkspaceSize (mhaRunner.cu:522). */
 BERT_B200_API int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params);

@@ -37,6 +37,12 @@ class MhaParams(C.Structure):
                 ("workspace_bytes", i64)]
 
 
+class AttentionBnsdParams(C.Structure):
+    _fields_ = [("type_id", i32), ("B", i32), ("S", i32), ("num_heads", i32), ("head_size", i32), ("q", vp), ("k", vp),
+                ("v", vp), ("out", vp), ("kv_lengths", vp), ("scale_bmm1", f32), ("scale_softmax", f32),
+                ("scale_bmm2", f32), ("status_word", vp)]
+
+
 class LayerWeights(C.Structure):
     _fields_ = [("wt_qkv", vp), ("b_qkv", vp), ("wt_out", vp), ("b_out", vp), ("ln1_gamma", vp), ("ln1_beta", vp),
                 ("wt_ffn1", vp), ("b_ffn1", vp), ("wt_ffn2", vp), ("b_ffn2", vp), ("ln2_gamma", vp), ("ln2_beta", vp),
@@ -67,6 +73,7 @@ SIGNATURES = {
     "bert_b200_packed_mask_to_lengths": (i32, [vp, i32, i32, u32, u32, u32, vp, vp]),
     "bert_b200_lengths_to_cu_seqlens": (i32, [vp, i32, vp, vp]),
     "bert_b200_fc": (i32, [C.POINTER(FcParams), vp]),
+    "bert_b200_attention_bnsd": (i32, [C.POINTER(AttentionBnsdParams), vp]),
     "bert_b200_mha_workspace_size": (i64, [C.POINTER(MhaParams)]),
     "bert_b200_mha": (i32, [C.POINTER(MhaParams), vp]),
     "bert_b200_encoder_workspace_size": (i64, [C.POINTER(EncoderConfig), i32, i32]),

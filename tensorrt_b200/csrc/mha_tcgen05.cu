@@ -167,10 +167,14 @@ __device__ __forceinline__ void tmemStoreWait()
 
 // IL (INT8 only): CHW32-interleaved tensors. Q, K and V tiles then arrive as two 32-channel sub-tiles of
 // [128 tokens][32 B] (32-byte swizzle); the head dimension is covered by one MMA per sub-tile.
-template <typename T, bool IL, bool PARTIAL>
+// BNSD: Q, K and V are three separate [B][N][S][d] tensors (mapQkv, mapK, mapV) and the output is [B][N][S][d];
+// otherwise mapQkv covers the fused tensor and the other two maps are not used.
+template <typename T, bool IL, bool PARTIAL, bool BNSD>
 __global__ void __launch_bounds__(kMhaThreads, 1)
-    mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, MhaArgs const args)
+    mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, const __grid_constant__ CUtensorMap mapK,
+        const __grid_constant__ CUtensorMap mapV, MhaArgs const args)
 {
+    static_assert(!BNSD || (!IL && !PARTIAL), "separate Q / K / V tensors: linear layout, S <= 512");
     using L = MhaSmem<T>;
     constexpr bool kInt8 = sizeof(T) == 1;
     static_assert(!IL || kInt8, "the interleaved layout is INT8 only");
@@ -281,6 +285,11 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
         *abortFlag = 0;
         fenceBarrierInit();
         prefetchTensorMap(&mapQkv);
+        if (BNSD)
+        {
+            prefetchTensorMap(&mapK);
+            prefetchTensorMap(&mapV);
+        }
     }
     if (warp == 1)
         tmemAlloc(tmemSlot, kTmemCols);
@@ -308,7 +317,9 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 int32_t const rowKv = rowK + it.keyBase; // first key of this item
                 // linear: (channel, which of [N][3], batch, row). interleaved: (channel, row, 32-channel group, which of [3][N])
                 auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
-                    if (IL)
+                    if (BNSD) // (channel, position, head, sequence) of the tensor `which` selects
+                        tmaLoad4d(dst, which == 0 ? &mapQkv : (which == 1 ? &mapK : &mapV), bar, 0, row, it.head, it.b);
+                    else if (IL)
                         tmaLoad4d(dst, &mapQkv, bar, 0, row, 0, which * args.N + it.head);
                     else
                         tmaLoad4d(dst, &mapQkv, bar, 0, it.head * 3 + which, args.fixedLayout ? it.b : 0, row);
@@ -648,6 +659,8 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             T* const outBase = static_cast<T*>(args.out) + static_cast<int64_t>(it.head) * args.d;
             // linear layouts: the d values of (token, head) are contiguous
             auto outRow = [&](int q) -> T* {
+                if (BNSD)
+                    return static_cast<T*>(args.out) + ((static_cast<int64_t>(it.b) * args.N + it.head) * args.S + q) * args.d;
                 int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + it.b : static_cast<int64_t>(it.rowBase) + q;
                 return outBase + rr * outRowStride;
             };
@@ -1002,7 +1015,7 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     }
     int const nbMax = ((PARTIAL ? kChunkKeys : p.S) + kKeyBlock - 1) / kKeyBlock;
     int const smem = L::dynamicBytes(nbMax);
-    auto kernel = mhaTcgen05Kernel<T, IL, PARTIAL>;
+    auto kernel = mhaTcgen05Kernel<T, IL, PARTIAL, false>;
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
@@ -1019,7 +1032,7 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
     int64_t const items = static_cast<int64_t>(p.num_heads) * p.B * args.numChunks;
     int const grid = static_cast<int>(items < smCount() ? items : smCount());
-    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, map, args);
+    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, map, map, map, args);
     if (le != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mhaTcgen05Kernel: %s", cudaGetErrorString(le));
     int32_t const st = checkLaunch("mhaTcgen05Kernel");
@@ -1033,10 +1046,67 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
     return checkLaunch("mhaMergeKernel");
 }
 
+// Separate Q, K, V tensors of shape [B][N][S][d] (the operand layout of TensorRT's attention layer), output
+// [B][N][S][d]: three tensor maps, the same kernel.
+template <typename T>
+int32_t launchMhaBnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t stream)
+{
+    using L = MhaSmem<T>;
+    uint64_t const d = static_cast<uint64_t>(p.head_size), S = static_cast<uint64_t>(p.S), N = static_cast<uint64_t>(p.num_heads);
+    CUtensorMap maps[3];
+    void const* const base[3] = {p.q, p.k, p.v};
+    for (int i = 0; i < 3; ++i)
+    {
+        // dim0: channel (box 64 wide, zero-filled beyond d); dim1: position; dim2: head; dim3: sequence
+        uint64_t const dims[4] = {d, S, N, static_cast<uint64_t>(p.B)};
+        uint64_t const strides[3] = {d * sizeof(T), S * d * sizeof(T), N * S * d * sizeof(T)};
+        uint32_t const box[4] = {kHeadSize, kKeyBlock, 1, 1};
+        int32_t const st = makeTensorMap(&maps[i], sizeof(T) == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+            base[i], dims, strides, box, sizeof(T) == 1 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
+    int const smem = L::dynamicBytes(nbMax);
+    auto kernel = mhaTcgen05Kernel<T, false, false, true>;
+    cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "attention_bnsd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    MhaArgs args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.scale_softmax,
+        p.scale_bmm2, p.status_word, 0, 1, nullptr, nullptr};
+    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
+    int const grid = static_cast<int>(items < smCount() ? items : smCount());
+    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, maps[0], maps[1], maps[2], args);
+    if (le != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "mhaTcgen05Kernel: %s", cudaGetErrorString(le));
+    return checkLaunch("mhaTcgen05Kernel");
+}
+
 } // namespace
 } // namespace b200
 
 using namespace b200;
+
+extern "C" int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params const* params, void* stream)
+{
+    B200_REQUIRE(params != nullptr, "attention_bnsd: null params");
+    bert_b200_attention_bnsd_params const& p = *params;
+    B200_REQUIRE(p.B >= 0 && p.S > 0 && p.num_heads > 0 && p.head_size > 0, "attention_bnsd: bad sizes B=%d S=%d N=%d d=%d", p.B,
+        p.S, p.num_heads, p.head_size);
+    B200_REQUIRE(p.q && p.k && p.v && p.out, "attention_bnsd: null pointer");
+    if (p.B == 0)
+        return BERT_B200_OK;
+    B200_REQUIRE(p.B <= 65535 && p.num_heads <= 65535, "attention_bnsd: B and num_heads are limited to 65535");
+    B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "attention_bnsd: type_id %d", p.type_id);
+    if (p.head_size > kHeadSize || p.head_size % 16 != 0)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: head sizes 16, 32, 48 and 64, got %d", p.head_size);
+    if (p.S > kMaxBlocks * kKeyBlock)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
+    B200_REQUIRE(aligned16(p.q) && aligned16(p.k) && aligned16(p.v) && aligned16(p.out),
+        "attention_bnsd: q, k, v and out must be 16-byte aligned");
+    auto s = static_cast<cudaStream_t>(stream);
+    return p.type_id == BERT_B200_FP16 ? launchMhaBnsd<__half>(p, s) : launchMhaBnsd<int8_t>(p, s);
+}
 
 extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* stream)
 {

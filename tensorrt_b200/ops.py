@@ -150,6 +150,18 @@ def fc(a, wt, bias=None, activation=ACT_NONE, alpha=1.0, out_dtype=None, out_sca
     return out
 
 
+def attention_bnsd(q, k, v, kv_lengths=None, scale_bmm1=None, scale_softmax=1.0, scale_bmm2=1.0, status=None):
+    """Fused attention on separate q, k, v of shape [B, N, S, d]; returns [B, N, S, d]."""
+    B, N, S, d = q.shape
+    out = torch.empty_like(q)
+    if scale_bmm1 is None:
+        scale_bmm1 = d ** -0.5
+    p = _lib.AttentionBnsdParams(_TYPE_ID[q.dtype], B, S, N, d, _ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(kv_lengths),
+                                 scale_bmm1, scale_softmax, scale_bmm2, _ptr(status))
+    check(lib.bert_b200_attention_bnsd(C.byref(p), _stream()), "attention_bnsd")
+    return out
+
+
 def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scale_bmm1=None, scale_softmax=1.0,
         scale_bmm2=1.0, status=None, interleaved=False, workspace=None, use_workspace=True):
     """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None), packed [total, 3*N*d], or with

@@ -270,6 +270,57 @@ def test_mha_fp16_long_sequences_on_tensor_cores(cuda, S, d, packed):
     assert O.close_abs_or_rel(slow.cpu().numpy(), ref, 1e-2, 1e-2)[0]
 
 
+def _split_bnsd(qkv, S, B, N, d):
+    """fixed-layout [S, B, N, 3, d] -> three contiguous [B, N, S, d] arrays"""
+    t = qkv.reshape(S, B, N, 3, d).transpose(3, 1, 2, 0, 4)
+    return (np.ascontiguousarray(t[i]) for i in range(3))
+
+
+@pytest.mark.parametrize("S,d", [(200, 64), (384, 32), (512, 64), (40, 16)])
+def test_attention_bnsd_fp16(cuda, S, d):
+    """Separate Q, K, V of shape [B, N, S, d] (the operand layout of TensorRT's attention layer) through the same
+    kernel: must equal the fused-tensor path's oracle, output [B, N, S, d]."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S + d)
+    B, N = 3, 4
+    qkv = rng.standard_normal((S, B, 3 * N * d)).astype(np.float16)
+    lengths = np.array([S, max(1, S // 3), 0], dtype=np.int32)
+    ref = O.mha(qkv, B, S, N, d, lengths=lengths).reshape(S, B, N, d).transpose(1, 2, 0, 3)
+    q, k, v = _split_bnsd(qkv, S, B, N, d)
+    st = _status(cuda)
+    out = T.attention_bnsd(_t(q, cuda), _t(k, cuda), _t(v, cuda), kv_lengths=_t(lengths, cuda), status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (worst, bad)
+    full = T.attention_bnsd(_t(q, cuda), _t(k, cuda), _t(v, cuda))   # no lengths: every key valid
+    ref_full = O.mha(qkv, B, S, N, d, lengths=np.full(B, S, np.int32)).reshape(S, B, N, d).transpose(1, 2, 0, 3)
+    assert O.close_abs_or_rel(full.cpu().numpy(), ref_full, 1e-2, 1e-2)[0]
+
+
+def test_attention_bnsd_int8(cuda):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(21)
+    S, B, N, d = 260, 2, 3, 64
+    q8, s_qkv = _int8_case(rng, S * B, N, d)
+    q8 = q8.reshape(S, B, -1)
+    lengths = np.array([260, 77], dtype=np.int32)
+    dq_probs = 1.0 / 127.0
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    s2 = dq_probs * s_qkv / (s_qkv * 0.5)
+    ref = O.mha_int8(q8, B, S, N, d, s1, 1.0 / dq_probs, s2, lengths=lengths).reshape(S, B, N, d).transpose(1, 2, 0, 3)
+    q, k, v = _split_bnsd(q8, S, B, N, d)
+    st = _status(cuda)
+    out = T.attention_bnsd(_t(q, cuda), _t(k, cuda), _t(v, cuda), kv_lengths=_t(lengths, cuda), scale_bmm1=s1,
+                           scale_softmax=1.0 / dq_probs, scale_bmm2=s2, status=st)
+    assert int(st[0]) == 0
+    _assert_int8_attention(out.cpu().numpy(), ref)
+    with pytest.raises(RuntimeError, match="S <= 512"):
+        big = torch.zeros((1, 1, 600, 64), dtype=torch.int8, device=cuda)
+        T.attention_bnsd(big, big, big)
+
+
 @pytest.mark.parametrize("d", [32, 64])
 def test_mha_fp32(cuda, d):
     import tensorrt_b200 as T
