@@ -114,3 +114,38 @@ def test_forward_host_async_matches_forward_host(cuda):
     for i in range(steps):
         assert torch.equal(got[i], want[i]), i
     enc.close()
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_forward_is_graph_capturable(cuda, int8):
+    """TensorRT replays engines as CUDA graphs: a forward captured into a graph (kernels launched with programmatic
+    stream serialisation included) must replay to the same bits as the eager call."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(31)
+    p = _small(rng)
+    lengths = np.array([200, 64, 384, 3], dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, S = int(cu[-1]), int(lengths.max())
+    ids = _t(rng.integers(0, 1000, size=total).astype(np.int32), cuda)
+    seg = _t(rng.integers(0, 2, size=total).astype(np.int32), cuda)
+    cu_d = _t(cu, cuda)
+    if int8:
+        O.calibrate_int8(p, ids.cpu().numpy(), seg.cpu().numpy(), cu, S)
+    enc = T.BertEncoder(p, T.INT8 if int8 else T.FP16, cuda)
+    out = torch.empty((total, 128), dtype=torch.float16, device=cuda)
+    eager = enc.forward(ids, seg, cu_d, S, out=out).clone()
+    stream = torch.cuda.Stream(device=cuda)
+    with torch.cuda.stream(stream):
+        enc.forward(ids, seg, cu_d, S, out=out)       # warm-up on the capturing stream
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            enc.forward(ids, seg, cu_d, S, out=out)
+    out.zero_()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    assert enc.status_word() == 0
+    enc.close()
