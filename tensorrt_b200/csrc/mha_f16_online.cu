@@ -1,0 +1,769 @@
+// FP16 fused multi-head attention on the sm_100a tensor cores with a key-block-wise online softmax
+// (head sizes 16, 32, 48, 64; any sequence length), fixed [S,B,N,3,d], packed [total,N,3,d] and separate
+// [B,N,S,d] layouts.
+//
+// Replaces, for FP16, the precompiled fused attention kernels the reference launches through
+// FusedMHARunnerFP16[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265) and its unfused
+// cuBLAS + softmax path (mhaRunner.cu:533-601) for the sequence lengths those kernels do not cover.
+//
+// One persistent CTA per SM keeps TWO 128-query tiles in flight (streams 0 and 1). The tiles of the CTA's work
+// list are dealt alternately to the two streams, across the boundaries of (sequence, head) items, so an odd number
+// of tiles per item (S = 384) leaves no stream idle. 11 warps:
+//   warps 0-3 / 4-7 : softmax of stream 0 / 1, ONE THREAD PER QUERY ROW (the 32x32b TMEM load hands lane = row):
+//                     no cross-thread reduction, no barrier among softmax threads. Per key block: load the 128
+//                     scores, block maximum, lazy rescale (below), p = exp2(x*scale*log2e - m), row sum,
+//                     P as FP16 back into the TMEM columns of the scores.
+//   warp 8          : one lane loads the Q tiles (two slots, one per stream).
+//   warp 9          : one lane loads K / V blocks (128 keys x 64 channels, 16 KB) into a ring of 12 stages. The
+//                     blocks of an item stay resident for all its query tiles when they fit (S <= 768); longer
+//                     sequences stream their blocks once per pair of query tiles.
+//   warp 10         : one lane issues every MMA, serving whichever stream has its next P block ready:
+//                       S = Q K_j^T           (128 x 128, FP32, TMEM columns 128*stream ..)
+//                       O (+)= P_j V_j        (128 x 64, A operand = P straight from TMEM, columns 256 + 64*stream ..)
+//                     S_{j+1} is issued right behind P_j V_j, so that the softmax threads of one stream work while
+//                     the tensor pipe serves the other.
+// Online softmax: the running maximum m only moves when the block maximum exceeds it by more than 8 in the log2
+// domain (P then stays below 2^8, far inside FP16); when it moves, the softmax threads scale the row sum and the
+// context accumulator in TMEM themselves (after the previous P V product has completed). The final context is
+// O / rowsum. Compared with a softmax over the exact row maximum this changes nothing but the rounding of P.
+// Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM and reports through the status word.
+#include "sm100.cuh"
+
+namespace b200
+{
+
+namespace
+{
+
+constexpr int kTile = 128;       // query rows per tile = keys per block
+constexpr int kHeadSize = 64;    // channels per tile row (smaller heads are zero-filled by the TMA unit)
+constexpr int kStages = 12;      // K / V ring
+constexpr int kStageBytes = kTile * kHeadSize * 2; // 16 KB: one Q tile, one K block, one V block
+constexpr int kThreads = 352;    // 8 softmax warps, Q loader, K/V loader, MMA issuer
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kOColumn = 256; // context accumulators: 64 columns per stream
+constexpr float kRescaleLog2 = 8.f;
+
+struct OnlineArgs
+{
+    int32_t B, S, N, total;
+    int32_t d;
+    int32_t fixedLayout;
+    void* out;
+    int32_t const* cu;
+    int32_t const* maskIdx;
+    float scaleBmm1;
+    uint32_t* statusWord;
+    int32_t tilesPerUnit, chunks; // a work unit = (sequence, head, chunk of tilesPerUnit query tiles)
+};
+
+// [ Q slot 0 ][ Q slot 1 ][ 12 K/V stages ][ barriers ]
+constexpr int kSmemQ = 0;
+constexpr int kSmemKv = 2 * kStageBytes;
+constexpr int kSmemBars = kSmemKv + kStages * kStageBytes;
+// full[12] empty[12] qFull[2] qFree[2] sFull[2] pReady[2] pvDone[2], tmem slot, abort flag
+constexpr int kNumBars = 2 * kStages + 10;
+constexpr int kSmemBytes = kSmemBars + kNumBars * 8 + 16 + 1024;
+
+__device__ __forceinline__ float ex2Approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c)
+{
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (P, FP16, two keys per 32-bit column, lane = query row) is read from
+// tensor memory. The 64-bit B descriptor is assembled from its halves inside the asm block.
+__device__ __forceinline__ void mmaF16TmemA(uint32_t dTmem, uint32_t aTmem, uint32_t bLo, uint32_t bHi, uint32_t iDesc, bool accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .b64 db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t"
+        "}" ::"r"(dTmem),
+        "r"(aTmem), "r"(bLo), "r"(bHi), "r"(iDesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmemStore16(uint32_t taddr, uint32_t const (&r)[16])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmemStoreWait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t packHalf2(float lo, float hi)
+{
+    __half2 const h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t const*>(&h);
+}
+
+// Geometry of one work unit; identical in every role (derived from the arguments and two words of global memory).
+struct Unit
+{
+    int32_t b, head, rowBase, rows, len, nb, tBegin, tEnd;
+};
+
+// The CTA's list of query tiles in processing order. Tile number n (counted per CTA) belongs to stream n & 1.
+// A "sub-item" is the run of tiles that shares one load of the K / V blocks: all tiles of a unit when its blocks fit
+// the ring, otherwise pairs of tiles (one per stream). `loadBase` is the number of K / V blocks loaded before it:
+// block j of the sub-item is load number loadBase + 2j (K) and loadBase + 2j + 1 (V); a load number L lives in ring
+// stage L % kStages and is the (L / kStages)-th fill of that stage.
+struct Walker
+{
+    OnlineArgs const& a;
+    int32_t numUnits;
+    int32_t unit;
+    Unit g;
+    int32_t t;        // query tile inside the (sequence, head)
+    int32_t subEnd;   // one past the last tile of the sub-item
+    int32_t subTiles; // tiles in the sub-item = uses of each of its stages
+    uint32_t loadBase;
+    uint32_t n;
+
+    __device__ __forceinline__ Walker(OnlineArgs const& args)
+        : a(args)
+        , numUnits(args.B * args.N * args.chunks)
+    {
+    }
+
+    // returns whether the unit has work for the tensor pipeline (a query row and a valid key)
+    __device__ __forceinline__ bool getUnit(int32_t u, Unit& o) const
+    {
+        int32_t const chunk = u % a.chunks;
+        int32_t const i = u / a.chunks;
+        o.b = i / a.N;
+        o.head = i - o.b * a.N;
+        if (a.fixedLayout)
+        {
+            o.rowBase = 0;
+            o.rows = a.S;
+            o.len = a.maskIdx ? min(max(__ldg(a.maskIdx + o.b), 0), a.S) : a.S;
+        }
+        else
+        {
+            o.rowBase = __ldg(a.cu + o.b);
+            o.len = min(max(__ldg(a.cu + o.b + 1) - o.rowBase, 0), a.S);
+            o.rows = o.len;
+        }
+        o.nb = (o.len + kTile - 1) / kTile;
+        int32_t const nq = (o.rows + kTile - 1) / kTile;
+        o.tBegin = chunk * a.tilesPerUnit;
+        o.tEnd = min(nq, o.tBegin + a.tilesPerUnit);
+        return o.len > 0 && o.tBegin < o.tEnd;
+    }
+
+    __device__ __forceinline__ bool seek(int32_t u)
+    {
+        while (u < numUnits && !getUnit(u, g))
+            u += gridDim.x;
+        unit = u;
+        if (u >= numUnits)
+            return false;
+        t = g.tBegin;
+        setSub();
+        return true;
+    }
+
+    __device__ __forceinline__ bool resident() const
+    {
+        return 2 * g.nb <= kStages;
+    }
+
+    __device__ __forceinline__ void setSub()
+    {
+        subTiles = resident() ? g.tEnd - t : min(2, g.tEnd - t);
+        subEnd = t + subTiles;
+    }
+
+    __device__ __forceinline__ bool begin()
+    {
+        n = 0;
+        loadBase = 0;
+        return seek(blockIdx.x);
+    }
+
+    __device__ __forceinline__ bool next()
+    {
+        ++t;
+        ++n;
+        if (t == subEnd)
+        {
+            loadBase += 2u * static_cast<uint32_t>(g.nb);
+            if (t == g.tEnd)
+                return seek(unit + gridDim.x);
+            setSub();
+        }
+        return true;
+    }
+
+    __device__ __forceinline__ bool firstOfSub() const
+    {
+        return t == subEnd - subTiles;
+    }
+};
+
+template <bool BNSD>
+__global__ void __maxnreg__(168)
+    mhaOnlineF16Kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+        const __grid_constant__ CUtensorMap mapV, OnlineArgs const args)
+{
+    constexpr uint32_t kIdescQk = makeInstrDesc(1u, 0u, 0u, 0u, 128u, 128u);
+    constexpr uint32_t kIdescPv = makeInstrDesc(1u, 0u, 0u, 1u, 128u, 64u);
+
+    int const warp = threadIdx.x >> 5;
+    int const lane = threadIdx.x & 31;
+
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sQ = smem + kSmemQ;
+    uint8_t* sKv = smem + kSmemKv;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kSmemBars);
+    uint64_t* full = bars;                    // [12] K / V block landed
+    uint64_t* empty = bars + kStages;         // [12] every MMA that reads the stage has completed
+    uint64_t* qFull = bars + 2 * kStages;     // [2]  Q tile of the stream landed
+    uint64_t* qFree = qFull + 2;              // [2]  all score MMAs of the stream's tile have completed
+    uint64_t* sFull = qFree + 2;              // [2]  scores of a key block complete         (once per block)
+    uint64_t* pReady = sFull + 2;             // [2]  P block written, 128 arrivals           (once per block)
+    uint64_t* pvDone = pReady + 2;            // [2]  context product of a block complete     (once per block)
+    uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(pvDone + 2);
+    volatile uint32_t* abortFlag = tmemSlot + 1;
+
+    if (threadIdx.x == 0)
+    {
+        for (int i = 0; i < kStages; ++i)
+        {
+            mbarInit(&full[i], 1);
+            mbarInit(&empty[i], 1);
+        }
+        for (int i = 0; i < 2; ++i)
+        {
+            mbarInit(&qFull[i], 1);
+            mbarInit(&qFree[i], 1);
+            mbarInit(&sFull[i], 1);
+            mbarInit(&pReady[i], kTile);
+            mbarInit(&pvDone[i], 1);
+        }
+        *abortFlag = 0;
+        fenceBarrierInit();
+        prefetchTensorMap(&mapQ);
+        if (BNSD)
+        {
+            prefetchTensorMap(&mapK);
+            prefetchTensorMap(&mapV);
+        }
+    }
+    if (warp == 8)
+        tmemAlloc(tmemSlot, kTmemCols);
+    tcFenceBefore();
+    __syncthreads();
+    tcFenceAfter();
+    uint32_t const tmemBase = *tmemSlot;
+    gridDependencyLaunch();
+    gridDependencyWait();
+
+    // which: 0 = Q, 1 = K, 2 = V; row = first token of the box inside the (packed or per-sequence) tensor
+    auto load = [&](uint8_t* dst, uint64_t* bar, int which, Unit const& g, int32_t row) {
+        if (BNSD) // (channel, position, head, sequence)
+            tmaLoad4d(dst, which == 0 ? &mapQ : (which == 1 ? &mapK : &mapV), bar, 0, row, g.head, g.b);
+        else // (channel, which of [N][3], batch, row)
+            tmaLoad4d(dst, &mapQ, bar, 0, g.head * 3 + which, args.fixedLayout ? g.b : 0, row);
+    };
+
+    if (warp == 8)
+    {
+        // ---- Q tiles: slot n & 1, refilled when the score MMAs of the stream's previous tile have completed ----
+        if (lane == 0)
+        {
+            Walker w(args);
+            bool ok = true;
+            for (bool more = w.begin(); more && ok; more = w.next())
+            {
+                uint32_t const slot = w.n & 1u;
+                if (w.n >= 2)
+                    ok = mbarWait(&qFree[slot], ((w.n >> 1) - 1) & 1u, abortFlag, kWaitStageFree);
+                if (!ok)
+                    break;
+                mbarArriveExpectTx(&qFull[slot], kStageBytes);
+                load(sQ + slot * kStageBytes, &qFull[slot], 0, w.g, (args.fixedLayout ? 0 : w.g.rowBase) + w.t * kTile);
+            }
+        }
+    }
+    else if (warp == 9)
+    {
+        // ---- K / V blocks of every sub-item, in the order the MMA thread consumes them ----
+        if (lane == 0)
+        {
+            Walker w(args);
+            bool ok = true;
+            for (bool more = w.begin(); more && ok; more = w.next())
+            {
+                if (!w.firstOfSub())
+                    continue;
+                int32_t const rowK = args.fixedLayout ? 0 : w.g.rowBase;
+                for (int j = 0; j < w.g.nb && ok; ++j)
+                {
+                    for (int kv = 0; kv < 2 && ok; ++kv)
+                    {
+                        uint32_t const L = w.loadBase + 2u * j + kv;
+                        uint32_t const s = L % kStages;
+                        uint32_t const fill = L / kStages;
+                        if (fill > 0)
+                            ok = mbarWait(&empty[s], (fill - 1) & 1u, abortFlag, kWaitStageFree);
+                        if (!ok)
+                            break;
+                        mbarArriveExpectTx(&full[s], kStageBytes);
+                        load(sKv + s * kStageBytes, &full[s], 1 + kv, w.g, rowK + j * kTile);
+                    }
+                }
+            }
+        }
+    }
+    else if (warp == 10)
+    {
+        // ---- MMA issue for both streams ----
+        if (lane == 0)
+        {
+            // K-major Q / K tiles (128-byte rows, 128-byte swizzle): SBO = 8 rows = 1024 B. V is MN-major (the head
+            // dimension contiguous): one MMA consumes 16 key rows = 2048 B.
+            uint64_t const dQk = makeSmemDesc(0, 16, 1024, kSwizzle128B);
+            uint64_t const dV = makeSmemDesc(0, 1024, 1024, kSwizzle128B);
+            uint32_t const hiQk = static_cast<uint32_t>(dQk >> 32), hiV = static_cast<uint32_t>(dV >> 32);
+            uint32_t const qLo = static_cast<uint32_t>(dQk) + (smemAddr(sQ) >> 4);
+            uint32_t const kLo = static_cast<uint32_t>(dQk) + (smemAddr(sKv) >> 4);
+            uint32_t const vLo = static_cast<uint32_t>(dV) + (smemAddr(sKv) >> 4);
+            constexpr uint32_t kStage16 = kStageBytes >> 4;
+
+            bool ok = true;
+            uint64_t used = 0; // per ring stage (4 bits each): uses of its current contents so far
+
+            // the MMAs that read stage `s` have been issued once more; after the last use of the sub-item the stage
+            // goes back to the loader as soon as they complete
+            auto useStage = [&](uint32_t s, int32_t uses) {
+                uint32_t const cnt = static_cast<uint32_t>((used >> (4 * s)) & 15u) + 1u;
+                if (static_cast<int32_t>(cnt) >= uses)
+                {
+                    tcCommit(&empty[s]);
+                    used &= ~(15ull << (4 * s));
+                }
+                else
+                    used += 1ull << (4 * s);
+            };
+
+            // Nothing below blocks: a stream whose next MMA lacks an operand is simply skipped in this round of the
+            // polling loop. (A blocking wait for one stream could wait for a Q tile or a K / V stage that the loaders
+            // only deliver after the OTHER stream has been served.)
+            enum : int32_t
+            {
+                kOpStart = 0, // first scores of a tile: needs its Q tile and K_0
+                kOpPv = 1,    // context product of block j: needs P_j and V_j
+                kOpQk = 2     // scores of block j (j >= 1): needs K_j
+            };
+            struct Stream
+            {
+                bool active;
+                int32_t op;
+                int32_t j;        // key block of the pending operation
+                uint32_t blocks;  // context products issued so far (parity of pReady)
+            };
+            Walker w0(args), w1(args);
+            Stream st0{false, kOpStart, 0, 0}, st1{false, kOpStart, 0, 0};
+
+            auto landed = [&](uint32_t L) { return mbarTryWaitAddr(smemAddr(&full[L % kStages]), (L / kStages) & 1u); };
+            auto issueQk = [&](Walker const& w, uint32_t s, int32_t j) {
+                uint32_t const stage = (w.loadBase + 2u * j) % kStages;
+                tcFenceAfter();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) // head size 64 = 4 x 16
+                    mmaLoHi<false>(tmemBase + s * kTile, qLo + s * kStage16 + 2 * k, hiQk, kLo + stage * kStage16 + 2 * k, hiQk,
+                        kIdescQk, k != 0);
+                useStage(stage, w.subTiles);
+                tcCommit(&sFull[s]);
+                if (j == w.g.nb - 1)
+                    tcCommit(&qFree[s]);
+            };
+            auto issuePv = [&](Walker const& w, uint32_t s, int32_t j) {
+                uint32_t const stage = (w.loadBase + 2u * j + 1u) % kStages;
+                tcFenceAfter();
+#pragma unroll
+                for (int k = 0; k < 8; ++k) // 128 keys = 8 x 16; P: 8 TMEM columns per 16 keys
+                    mmaF16TmemA(tmemBase + kOColumn + s * kHeadSize, tmemBase + s * kTile + 8 * k, vLo + stage * kStage16 + k * 128u,
+                        hiV, kIdescPv, (j | k) != 0);
+                useStage(stage, w.subTiles);
+                tcCommit(&pvDone[s]);
+            };
+            // issues as many of the stream's pending operations as have their operands; returns whether any was issued
+            auto advance = [&](Walker& w, Stream& st, uint32_t s) -> bool {
+                bool progressed = false;
+                while (st.active)
+                {
+                    if (st.op == kOpStart)
+                    {
+                        if (!mbarTryWaitAddr(smemAddr(&qFull[s]), (w.n >> 1) & 1u) || !landed(w.loadBase))
+                            break;
+                        issueQk(w, s, 0);
+                        st.j = 0;
+                        st.op = kOpPv;
+                    }
+                    else if (st.op == kOpPv)
+                    {
+                        if (!mbarTryWaitAddr(smemAddr(&pReady[s]), st.blocks & 1u) || !landed(w.loadBase + 2u * st.j + 1u))
+                            break;
+                        ++st.blocks;
+                        issuePv(w, s, st.j);
+                        ++st.j;
+                        if (st.j < w.g.nb)
+                            st.op = kOpQk;
+                        else
+                        {
+                            st.op = kOpStart;
+                            st.active = w.next() && w.next();
+                        }
+                    }
+                    else
+                    {
+                        if (!landed(w.loadBase + 2u * st.j))
+                            break;
+                        issueQk(w, s, st.j);
+                        st.op = kOpPv;
+                    }
+                    progressed = true;
+                }
+                return progressed;
+            };
+
+            st0.active = w0.begin();
+            st1.active = w1.begin() && w1.next();
+            uint32_t idle = 0;
+            uint64_t tIdle = 0;
+            while ((st0.active || st1.active) && ok)
+            {
+                bool progressed = advance(w0, st0, 0);
+                progressed = advance(w1, st1, 1) || progressed;
+                if (progressed)
+                    idle = 0;
+                else if ((++idle & 1023u) == 0)
+                {
+                    if (*abortFlag != 0)
+                        ok = false;
+                    uint64_t const now = globalTimerNs();
+                    if (idle == 1024u)
+                        tIdle = now;
+                    else if (now - tIdle > kWaitLimitNs)
+                    {
+                        *abortFlag = kWaitSoftmax;
+                        ok = false;
+                    }
+                }
+            }
+        }
+    }
+    else
+    {
+        // ---- softmax: stream = warp / 4, query row = TMEM lane ----
+        uint32_t const s = static_cast<uint32_t>(warp >> 2);
+        int const r = (warp & 3) * 32 + lane;
+        uint32_t const tRow = tmemBase + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+        uint32_t const tS = tRow + s * kTile;
+        uint32_t const tO = tRow + kOColumn + s * kHeadSize;
+        float const sl2 = args.scaleBmm1 * 1.4426950408889634f;
+        float const thrRaw = kRescaleLog2 / sl2; // the same threshold on the unscaled scores
+        bool ok = true;
+
+        if (s == 0 && args.fixedLayout)
+        {
+            // sequences without a valid key: every probability is zero and so is the context row
+            Walker z(args);
+            Unit g;
+            int const chunks16 = args.d / 8;
+            for (int u = blockIdx.x; u < z.numUnits; u += gridDim.x)
+            {
+                z.getUnit(u, g);
+                if (g.len > 0 || g.tBegin >= g.tEnd)
+                    continue;
+                int const q0 = g.tBegin * kTile, q1 = min(g.rows, g.tEnd * kTile);
+                for (int i = threadIdx.x; i < (q1 - q0) * chunks16; i += kTile)
+                {
+                    int const q = q0 + i / chunks16, c = i % chunks16;
+                    __half* row = BNSD
+                        ? static_cast<__half*>(args.out) + ((static_cast<int64_t>(g.b) * args.N + g.head) * args.S + q) * args.d
+                        : static_cast<__half*>(args.out) + (static_cast<int64_t>(q) * args.B + g.b) * args.N * args.d + g.head * args.d;
+                    reinterpret_cast<uint4*>(row)[c] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+
+        Walker w(args);
+        bool active = w.begin() && (s == 0 || w.next());
+        uint32_t blocks = 0; // key blocks this stream has completed: parity of sFull / pvDone
+        while (active)
+        {
+            Unit const g = w.g;
+            float mRun = -INFINITY, l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+#pragma unroll 1
+            for (int j = 0; j < g.nb; ++j)
+            {
+                ok = ok && mbarWait(&sFull[s], blocks & 1u, abortFlag, kWaitSoftmax);
+                tcFenceAfter();
+                uint32_t x0[32], x1[32], x2[32], x3[32];
+                tmemLoad32(tS, x0);
+                tmemLoad32(tS + 32, x1);
+                tmemLoad32(tS + 64, x2);
+                tmemLoad32(tS + 96, x3);
+                tmemLoadWait32(x0);
+                tmemLoadWait32(x1);
+                tmemLoadWait32(x2);
+                tmemLoadWait32(x3);
+                int const limit = g.len - j * kTile;
+                if (limit < kTile) // the last block of the sequence: keys beyond its length take no part
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                    {
+                        if (i >= limit)
+                            x0[i] = 0xff800000u;
+                        if (i + 32 >= limit)
+                            x1[i] = 0xff800000u;
+                        if (i + 64 >= limit)
+                            x2[i] = 0xff800000u;
+                        if (i + 96 >= limit)
+                            x3[i] = 0xff800000u;
+                    }
+                }
+                float mA = __uint_as_float(x0[0]), mB = __uint_as_float(x1[0]), mC = __uint_as_float(x2[0]), mD = __uint_as_float(x3[0]);
+#pragma unroll
+                for (int i = 1; i < 31; i += 2)
+                {
+                    mA = fmax3(mA, __uint_as_float(x0[i]), __uint_as_float(x0[i + 1]));
+                    mB = fmax3(mB, __uint_as_float(x1[i]), __uint_as_float(x1[i + 1]));
+                    mC = fmax3(mC, __uint_as_float(x2[i]), __uint_as_float(x2[i + 1]));
+                    mD = fmax3(mD, __uint_as_float(x3[i]), __uint_as_float(x3[i + 1]));
+                }
+                mA = fmax3(mA, __uint_as_float(x0[31]), __uint_as_float(x1[31]));
+                mC = fmax3(mC, __uint_as_float(x2[31]), __uint_as_float(x3[31]));
+                float const mBlk = fmaxf(fmaxf(mA, mB), fmaxf(mC, mD));
+
+                if (j == 0)
+                    mRun = mBlk;
+                else
+                {
+                    // The running maximum moves only when this block exceeds it by more than 2^8 after scaling.
+                    bool const move = mBlk > mRun + thrRaw;
+                    if (__any_sync(0xffffffffu, move))
+                    {
+                        float const f = move ? ex2Approx((mRun - mBlk) * sl2) : 1.f;
+                        if (move)
+                            mRun = mBlk;
+                        l0 *= f;
+                        l1 *= f;
+                        l2 *= f;
+                        l3 *= f;
+                        // the context so far, once the previous block's product has completed
+                        ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
+                        tcFenceAfter();
+#pragma unroll 1
+                        for (int c = 0; c < kHeadSize; c += 16) // 16 columns at a time: the scores stay in registers
+                        {
+                            uint32_t o[16];
+                            tmemLoad16(tO + c, o);
+                            tmemLoadWait16(o);
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                            tmemStore16(tO + c, o);
+                        }
+                    }
+                }
+                float const negM = -mRun * sl2;
+
+                // p = exp2(x * scale * log2e - m); P as FP16 pairs over the first 64 columns of the scores
+                auto expBlock = [&](uint32_t(&x)[32], uint32_t col) {
+                    uint32_t p[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                    {
+                        float const e0 = ex2Approx(fmaf(__uint_as_float(x[i]), sl2, negM));
+                        float const e1 = ex2Approx(fmaf(__uint_as_float(x[i + 1]), sl2, negM));
+                        float const e2 = ex2Approx(fmaf(__uint_as_float(x[i + 2]), sl2, negM));
+                        float const e3 = ex2Approx(fmaf(__uint_as_float(x[i + 3]), sl2, negM));
+                        l0 += e0;
+                        l1 += e1;
+                        l2 += e2;
+                        l3 += e3;
+                        p[i / 2] = packHalf2(e0, e1);
+                        p[i / 2 + 1] = packHalf2(e2, e3);
+                    }
+                    tmemStore16(tS + col, p); // 32 keys -> 16 columns
+                };
+                expBlock(x0, 0);
+                expBlock(x1, 16);
+                expBlock(x2, 32);
+                expBlock(x3, 48);
+                tmemStoreWait();
+                tcFenceBefore();
+                mbarArrive(&pReady[s]);
+                ++blocks;
+            }
+
+            // ---- epilogue: context / row sum -> FP16 ----
+            ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
+            tcFenceAfter();
+            uint32_t o0[32], o1[32];
+            tmemLoad32(tO, o0);
+            tmemLoad32(tO + 32, o1);
+            tmemLoadWait32(o0);
+            tmemLoadWait32(o1);
+            tcFenceBefore();
+            int const q = w.t * kTile + r;
+            if (q < g.rows && ok)
+            {
+                float const inv = 1.f / ((l0 + l1) + (l2 + l3));
+                __half* dst;
+                if (BNSD)
+                    dst = static_cast<__half*>(args.out) + ((static_cast<int64_t>(g.b) * args.N + g.head) * args.S + q) * args.d;
+                else
+                {
+                    int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + g.b : static_cast<int64_t>(g.rowBase) + q;
+                    dst = static_cast<__half*>(args.out) + rr * args.N * args.d + g.head * args.d;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                {
+                    if (c * 8 < args.d)
+                    {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            f[i] = __uint_as_float(c < 4 ? o0[c * 8 + i] : o1[(c - 4) * 8 + i]) * inv;
+                        reinterpret_cast<uint4*>(dst)[c] = packHalf8(f);
+                    }
+                }
+            }
+            active = w.next() && w.next();
+        }
+        tcFenceBefore();
+    }
+
+    __syncthreads();
+    uint32_t const aborted = *abortFlag;
+    if (aborted != 0)
+    {
+        uint64_t const t0 = globalTimerNs();
+        while (globalTimerNs() - t0 < 1000000ull)
+            __nanosleep(1000);
+        if (threadIdx.x == 0 && args.statusWord)
+            atomicMax(args.statusWord, aborted);
+        __syncthreads();
+    }
+    if (warp == 8)
+    {
+        __syncwarp();
+        tcFenceAfter();
+        tmemFree(tmemBase, kTmemCols);
+    }
+}
+
+// Query tiles per work unit: all tiles of a (sequence, head) share one load of K / V, so whole items are the
+// cheapest units; they are cut into smaller ones only when that shortens the longest CTA's list.
+int32_t chooseTilesPerUnit(int64_t items, int32_t nqMax, int32_t sms)
+{
+    int32_t best = nqMax;
+    int64_t bestCost = ((items + sms - 1) / sms) * nqMax;
+    for (int32_t tpu = nqMax - 1; tpu >= 1; --tpu)
+    {
+        int64_t const chunks = (nqMax + tpu - 1) / tpu;
+        int64_t const cost = ((items * chunks + sms - 1) / sms) * tpu;
+        if (cost < bestCost)
+        {
+            bestCost = cost;
+            best = tpu;
+        }
+    }
+    return best;
+}
+
+template <bool BNSD>
+int32_t launchOnline(CUtensorMap const (&maps)[3], OnlineArgs args, cudaStream_t stream)
+{
+    auto kernel = mhaOnlineF16Kernel<BNSD>;
+    cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    int32_t const nqMax = (args.S + kTile - 1) / kTile;
+    int64_t const items = static_cast<int64_t>(args.B) * args.N;
+    args.tilesPerUnit = chooseTilesPerUnit(items, nqMax, smCount());
+    args.chunks = (nqMax + args.tilesPerUnit - 1) / args.tilesPerUnit;
+    int64_t const units = items * args.chunks;
+    if (units > INT32_MAX)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: too many work units (%lld)", static_cast<long long>(units));
+    int const grid = static_cast<int>(units < smCount() ? units : smCount());
+    cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, maps[0], maps[1], maps[2], args);
+    if (le != cudaSuccess)
+        B200_FAIL(BERT_B200_CUDA_ERROR, "mhaOnlineF16Kernel: %s", cudaGetErrorString(le));
+    return checkLaunch("mhaOnlineF16Kernel");
+}
+
+} // namespace
+
+// FP16, head sizes 16 / 32 / 48 / 64, fused [N][3][d] tensor in the fixed or the packed layout.
+int32_t mhaOnlineF16(bert_b200_mha_params const& p, cudaStream_t stream)
+{
+    bool const fixedLayout = p.cu_seqlens == nullptr;
+    uint64_t const d = static_cast<uint64_t>(p.head_size);
+    uint64_t const rowElems = 3ull * static_cast<uint64_t>(p.num_heads) * d;
+    // dim0: the d channels of one of Q, K, V of a head (the box is 64 wide: channels beyond d arrive as zeros);
+    // dim1: which of [N][3]; dim2: batch (fixed layout only); dim3: sequence position / packed row
+    uint64_t const dims[4] = {d, 3ull * static_cast<uint64_t>(p.num_heads), fixedLayout ? static_cast<uint64_t>(p.B) : 1ull,
+        fixedLayout ? static_cast<uint64_t>(p.S) : static_cast<uint64_t>(p.total)};
+    uint64_t const strides[3] = {d * 2, rowElems * 2, (fixedLayout ? static_cast<uint64_t>(p.B) : 1ull) * rowElems * 2};
+    uint32_t const box[4] = {kHeadSize, 1, 1, kTile};
+    CUtensorMap maps[3];
+    int32_t const st = makeTensorMap(&maps[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, p.qkv, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != BERT_B200_OK)
+        return st;
+    maps[1] = maps[0];
+    maps[2] = maps[0];
+    OnlineArgs const args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx,
+        p.scale_bmm1, p.status_word, 1, 1};
+    return launchOnline<false>(maps, args, stream);
+}
+
+// Separate Q, K, V tensors of shape [B][N][S][d] (the operand layout of TensorRT's attention layer), output
+// [B][N][S][d]: three tensor maps, the same kernel.
+int32_t mhaOnlineF16Bnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t stream)
+{
+    uint64_t const d = static_cast<uint64_t>(p.head_size), S = static_cast<uint64_t>(p.S), N = static_cast<uint64_t>(p.num_heads);
+    CUtensorMap maps[3];
+    void const* const base[3] = {p.q, p.k, p.v};
+    for (int i = 0; i < 3; ++i)
+    {
+        uint64_t const dims[4] = {d, S, N, static_cast<uint64_t>(p.B)};
+        uint64_t const strides[3] = {d * 2, S * d * 2, N * S * d * 2};
+        uint32_t const box[4] = {kHeadSize, kTile, 1, 1};
+        int32_t const st = makeTensorMap(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, base[i], dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (st != BERT_B200_OK)
+            return st;
+    }
+    OnlineArgs const args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.status_word, 1, 1};
+    return launchOnline<true>(maps, args, stream);
+}
+
+} // namespace b200

@@ -33,12 +33,16 @@
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
 #include "sm100.cuh"
 
+#include <cstdlib>
 #include <type_traits>
 
 namespace b200
 {
 
 int32_t mhaSimt(bert_b200_mha_params const& p, cudaStream_t stream);
+int32_t mhaOnlineF16(bert_b200_mha_params const& p, cudaStream_t stream);
+int32_t mhaOnlineF16Bnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t stream);
+bool legacyF16Attention();
 
 namespace
 {
@@ -1083,6 +1087,16 @@ int32_t launchMhaBnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t str
 }
 
 } // namespace
+
+// Development switch: BERT_B200_MHA_F16=legacy keeps FP16 on the whole-row kernel of this file.
+bool legacyF16Attention()
+{
+    static int const on = [] {
+        char const* e = std::getenv("BERT_B200_MHA_F16");
+        return (e != nullptr && e[0] == 'l') ? 1 : 0;
+    }();
+    return on != 0;
+}
 } // namespace b200
 
 using namespace b200;
@@ -1100,11 +1114,16 @@ extern "C" int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params cons
     B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "attention_bnsd: type_id %d", p.type_id);
     if (p.head_size > kHeadSize || p.head_size % 16 != 0)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: head sizes 16, 32, 48 and 64, got %d", p.head_size);
-    if (p.S > kMaxBlocks * kKeyBlock)
-        B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
+    if (p.S > kMaxBlocks * kKeyBlock && (p.type_id == BERT_B200_INT8 || legacyF16Attention()))
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: INT8 takes S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
     B200_REQUIRE(aligned16(p.q) && aligned16(p.k) && aligned16(p.v) && aligned16(p.out),
         "attention_bnsd: q, k, v and out must be 16-byte aligned");
     auto s = static_cast<cudaStream_t>(stream);
+    if (p.type_id == BERT_B200_FP16 && !legacyF16Attention())
+    {
+        B200_REQUIRE(p.scale_bmm1 > 0.f, "attention_bnsd: scale_bmm1 must be positive");
+        return mhaOnlineF16Bnsd(p, s);
+    }
     return p.type_id == BERT_B200_FP16 ? launchMhaBnsd<__half>(p, s) : launchMhaBnsd<int8_t>(p, s);
 }
 
@@ -1125,6 +1144,11 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
     B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "mha: type_id %d", p.type_id);
     bool const headOk = p.head_size <= kHeadSize && p.head_size % 16 == 0 && (!p.interleaved || p.head_size % 32 == 0);
     bool const lengthOk = p.S <= kMaxBlocks * kKeyBlock;
+    if (headOk && p.type_id == BERT_B200_FP16 && !p.interleaved && p.scale_bmm1 > 0.f && !legacyF16Attention())
+    {
+        B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
+        return mhaOnlineF16(p, s);
+    }
     // Outside the tensor-core kernel's shapes FP16 takes the SIMT kernel, like the reference's unfused runner
     // (qkvToContextPlugin.cpp:335-341, 522-531); INT8 has no such path there either (qkvToContextPlugin.cpp:530).
     if (headOk && !lengthOk && p.type_id == BERT_B200_FP16 && p.workspace != nullptr && p.workspace_bytes >= partialBytes(p))

@@ -5,6 +5,7 @@ config 1: one BERT-base post-LN encoder layer (batch 8, seq 128, hidden 768, 12 
           path a TensorRT engine would take: FC -> QKVToContext(v4, mask from EmbLayerNorm-style mask index) -> FC ->
           SkipLayerNorm(v5, bias) -> FC(+bias+GELU) -> FC -> SkipLayerNorm(v5, bias).
 config 2: BERT-base front end: EmbLayerNorm v6 on B=32, S=128 with lengths in [64, 128] + two layers of the encoder.
+config 3: BERT-large, 24 layers, S = 384, 64 sequences, explicit INT8 (the benchmark's headline configuration).
 config 4: BERT-large packed variable-length path, lengths uniform in [32, 384] (seed 1), sharded by token count.
 """
 import numpy as np
@@ -141,4 +142,53 @@ def test_config4_packed_var_len_sharded(cuda):
     # same three sequences alone give bit-identical rows
     alone = enc.forward(_t(ids[:cu[k]], cuda), _t(seg[:cu[k]], cuda), _t(cu[:k + 1], cuda), 384).cpu().numpy()
     assert np.array_equal(alone, out[:cu[k]])
+    enc.close()
+
+
+def test_config3_bert_large_int8_24_layers(cuda):
+    """Config 3 at full size: 24 layers, hidden 1024, 16 heads, FFN 4096, S = 384, a batch of 64 sequences, explicit
+    INT8 with per-tensor amax / 127 scales from a seeded calibration batch (the oracle's calibration on two sequences),
+    dq_probs = 1 / 127. The oracle runs two sequences of the batch - one at the front and one that a persistent CTA
+    meets late in its work list. Layer 1 is held to the operator tolerance (+-1 LSB, a rounding tie of an attention
+    probability may cost 2); after 24 layers the INT8 rounding differences have compounded and the check is the
+    statistical one of the whole-encoder tests."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(3)
+    B, S = 64, 384
+    p = O.make_bert_params(rng, 24, 1024, 16, 4096)
+    ids2, seg2, _, cu2 = O.make_inputs(rng, 2, S)
+    O.calibrate_int8(p, ids2, seg2, cu2, S)
+    ref, ref_i8, _ = O.encoder_int8(p, ids2, seg2, cu2, S, return_all=True)
+    # the same two sequences at positions 0 and 41 of a batch of 64
+    ids, seg, _, cu = O.make_inputs(rng, B, S)
+    where = (0, 41)
+    for k, b in enumerate(where):
+        ids[b * S:(b + 1) * S] = ids2[k * S:(k + 1) * S]
+        seg[b * S:(b + 1) * S] = seg2[k * S:(k + 1) * S]
+    rows = np.concatenate([np.arange(b * S, (b + 1) * S) for b in where])
+
+    # layer 1 alone: operator-level tolerance
+    p1 = O.BertParams(p.hidden, p.heads, p.ffn, p.word_emb, p.pos_emb, p.tok_emb, p.emb_gamma, p.emb_beta, p.layers[:1], p.dq_probs)
+    _, ref1_i8, _ = O.encoder_int8(p1, ids2, seg2, cu2, S, return_all=True)
+    enc1 = T.BertEncoder(p1, T.INT8, cuda)
+    out1 = enc1.forward(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), S).cpu().numpy().astype(np.float64)[rows]
+    assert enc1.status_word() == 0
+    got1 = np.rint(out1 / p.layers[0].scales["s_out"]).astype(np.int32)
+    d1 = np.abs(got1 - ref1_i8.astype(np.int32))
+    assert d1.max() <= 2 and (d1 > 1).mean() < 1e-3 and (d1 == 0).mean() > 0.9, (int(d1.max()), float((d1 > 1).mean()), float((d1 == 0).mean()))
+    enc1.close()
+
+    enc = T.BertEncoder(p, T.INT8, cuda)
+    out = enc.forward(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), S).cpu().numpy().astype(np.float64)
+    assert enc.status_word() == 0
+    assert enc.launches_per_forward == 2 + 7 * 24
+    got = out[rows]
+    cos = float((got * ref).sum() / np.sqrt((got * got).sum() * (ref * ref).sum()))
+    assert cos > 0.999, cos
+    lsb = np.abs(np.rint(got / p.layers[-1].scales["s_out"]) - ref_i8.astype(np.float64))
+    assert (lsb <= 2).mean() > 0.99, float((lsb <= 2).mean())
+    # a sequence's output does not depend on its place in the batch
+    alone = enc.forward(_t(ids2, cuda), _t(seg2, cuda), _t(cu2, cuda), S).cpu().numpy()
+    assert np.array_equal(alone, out[rows].astype(np.float16))
     enc.close()

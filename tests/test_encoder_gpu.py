@@ -149,3 +149,44 @@ def test_forward_is_graph_capturable(cuda, int8):
     assert torch.equal(out, eager)
     assert enc.status_word() == 0
     enc.close()
+
+
+def test_calibration_maxima_match_oracle(cuda):
+    """bert_b200_encoder_calibrate: the |tensor| maxima taken on the device during an FP16 forward equal the oracle's
+    (float64 forward with FP16-rounded tensors) up to FP16 rounding of the tensors they are taken from, and the
+    scales derived from them equal amax / 127."""
+    import tensorrt_b200 as T
+    from tensorrt_b200 import synthetic
+
+    rng = np.random.default_rng(41)
+    p = _small(rng, layers=3)
+    lengths = np.array([384, 17, 200, 1, 128], dtype=np.int32)
+    cu = O.cu_seqlens(lengths)
+    total, S = int(cu[-1]), int(lengths.max())
+    ids = rng.integers(0, 1000, size=total).astype(np.int32)
+    seg = rng.integers(0, 2, size=total).astype(np.int32)
+    enc = T.BertEncoder(p, T.FP16, cuda)
+    amax = enc.calibrate(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), S)
+    enc.close()
+    # oracle: the same forward with every stored tensor rounded to FP16, maxima in the device's slot order
+    x, _ = O.emb_layer_norm_var_seqlen(ids, seg, cu, p.word_emb, p.pos_emb, p.tok_emb, p.emb_gamma, p.emb_beta)
+    x = x.astype(np.float16).astype(np.float64)
+    want = np.zeros_like(amax)
+    for li, lp in enumerate(p.layers):
+        want[li, 0] = np.abs(x).max()
+        x, t = O.encoder_layer_fp(x, lp, len(lengths), S, p.heads, cu, round_fp16=True)
+        want[li, 1:7] = [np.abs(t[k]).max() for k in ("qkv", "ctx", "ao", "h1", "f1", "f2")]
+        want[li, 7] = np.abs(x).max()
+    # the maxima are FP16 values; kernels and oracle may round an extreme element to neighbouring FP16 numbers, and
+    # through three layers inputs differ by a few FP16 ulps
+    assert np.all(np.abs(amax - want) <= 1e-2 * want + 1e-3), (amax, want)
+    # the scales the INT8 encoder is given are exactly amax / 127 (weights: amax of the matrix / 127)
+    import types
+    layers = [types.SimpleNamespace(scales={}, **{n: torch.from_numpy(getattr(lp, n).astype(np.float32)) for n in
+                                                 ("w_qkv", "w_out", "w_ffn1", "w_ffn2")}) for lp in p.layers]
+    synthetic.assign_int8_scales(types.SimpleNamespace(layers=layers), amax)
+    for li, lp in enumerate(p.layers):
+        assert layers[li].scales["s_qkv"] == pytest.approx(float(amax[li, 1]) / 127.0, rel=1e-6)
+        assert layers[li].scales["s_w_qkv"] == pytest.approx(O.amax_scale(lp.w_qkv.astype(np.float32)), rel=1e-6)
+        if li > 0:
+            assert layers[li].scales["s_in"] == layers[li - 1].scales["s_out"]

@@ -119,3 +119,62 @@ def test_fc_linearity_full_size(cuda):
     lhs = T.fc((a1.float() + a2.float()).half(), wt).float()
     rhs = T.fc(a1, wt).float() + T.fc(a2, wt).float()
     assert (lhs - rhs).abs().max().item() < 2e-2
+
+
+def _sampled_rows(m, rng):
+    """Rows spread over the whole range: two of every 256-row block (the unit a pair of CTAs owns), the last 32 rows
+    and some at random - so that every tile a persistent cluster takes, not only its first, is compared."""
+    rows = [blk * 256 + int(o) for blk in range(m // 256) for o in rng.integers(0, 256, size=2)]
+    rows += list(range(m - 32, m)) + list(rng.integers(0, m, size=128))
+    return np.unique(np.array(rows, dtype=np.int64))
+
+
+# the four projections of a BERT-large layer at the benchmark's row count (64 sequences x 384 tokens)
+LARGE = [(24576, 1024, 3072, "bias"), (24576, 1024, 1024, "none"), (24576, 1024, 4096, "bias_gelu"), (24576, 4096, 1024, "none")]
+
+
+@pytest.mark.parametrize("m,k,n,epi", LARGE)
+def test_fc_fp16_benchmark_shapes(cuda, m, k, n, epi):
+    """Element-wise against the oracle at the benchmarked size: 312-1248 tiles on 74 CTA pairs, i.e. the second and
+    later tiles of every persistent cluster (accumulator double-buffering, stage parities) are checked too."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(m + k + n)
+    gen = torch.Generator(device=cuda).manual_seed(k + n)
+    a = torch.randn((m, k), device=cuda, generator=gen).half()
+    wt = (0.02 * torch.randn((n, k), device=cuda, generator=gen)).half()
+    bias = (0.02 * torch.randn((n,), device=cuda, generator=gen)).float() if epi != "none" else None
+    st = _status(cuda)
+    out = T.fc(a, wt, bias, T.ACT_GELU_ERF if epi == "bias_gelu" else T.ACT_NONE, status=st)
+    assert int(st[0]) == 0
+    rows = _sampled_rows(m, rng)
+    idx = torch.from_numpy(rows).to(cuda)
+    ref = O.fc(a[idx].cpu().numpy(), wt.cpu().numpy().T, None if bias is None else bias.cpu().numpy(),
+               "gelu" if epi == "bias_gelu" else None)
+    ok, worst, bad = O.close_abs_or_rel(out[idx].cpu().numpy(), ref, 2e-3, 2e-3)
+    assert ok, (worst, bad)
+
+
+@pytest.mark.parametrize("m,k,n,epi", LARGE)
+def test_fc_int8_benchmark_shapes(cuda, m, k, n, epi):
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(m + k + n + 1)
+    gen = torch.Generator(device=cuda).manual_seed(k + n + 1)
+    a = torch.randint(-127, 128, (m, k), device=cuda, generator=gen, dtype=torch.int32).to(torch.int8)
+    wt = torch.randint(-127, 128, (n, k), device=cuda, generator=gen, dtype=torch.int32).to(torch.int8)
+    bias = (0.5 * torch.randn((n,), device=cuda, generator=gen)).float() if epi != "none" else None
+    alpha = 2.0 / (127 * 127 * np.sqrt(k))
+    inv = 1.0 / 0.02
+    st = _status(cuda)
+    out = T.fc(a, wt, bias, T.ACT_GELU_ERF if epi == "bias_gelu" else T.ACT_NONE, alpha=alpha, out_dtype=torch.int8,
+               out_scale=inv, status=st)
+    assert int(st[0]) == 0
+    rows = _sampled_rows(m, rng)
+    idx = torch.from_numpy(rows).to(cuda)
+    ref = O.fc_int8(a[idx].cpu().numpy(), wt.cpu().numpy().T, alpha, None if bias is None else bias.cpu().numpy(),
+                    "gelu" if epi == "bias_gelu" else None, inv)
+    got = out[idx].cpu().numpy()
+    ok, worst, bad = O.int8_within_lsb(got, ref)
+    assert ok, (worst, bad)
+    assert (got == ref).mean() > (0.93 if epi == "bias_gelu" else 0.99)

@@ -355,3 +355,60 @@ def test_mha_full_size_properties(cuda):
     o1 = T.mha(qkv2.reshape(S, -1), 1, S, N, cu_seqlens=cu1).float()
     o2 = T.mha(shuffled.reshape(S, -1), 1, S, N, cu_seqlens=cu1).float()
     assert (o1 - o2).abs().max().item() < 5e-3
+
+
+# Sequences of a 64-sequence batch whose 16 (sequence, head) work items sit at every position (first ... seventh) of
+# a persistent CTA's work list when 1024 items are dealt round-robin to 148 CTAs.
+_QUEUE_SAMPLE = [0, 10, 19, 28, 37, 47, 56, 63]
+
+
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("int8", [False, True])
+def test_mha_benchmark_size_against_oracle(cuda, packed, int8):
+    """BERT-large S = 384, 64 sequences, 16 heads (1024 work items on 148 persistent CTAs), ragged lengths: whole
+    sequences compared element-wise with the oracle, chosen so that every position of a CTA's work list is covered
+    (a stale Q / K / V tile or a wrong barrier phase on a CTA's later items would show here)."""
+    import tensorrt_b200 as T
+
+    S, B, N, d = 384, 64, 16, 64
+    rng = np.random.default_rng(384 + packed + 2 * int8)
+    lengths = rng.integers(1, S + 1, size=B).astype(np.int32)
+    lengths[[0, 19, 63]] = S
+    lengths[28] = 129
+    lengths[5] = 0
+    cu = O.cu_seqlens(lengths)
+    rows = int(cu[-1]) if packed else S * B
+    x = rng.standard_normal((rows, 3 * N * d)).astype(np.float32)
+    st = _status(cuda)
+    if int8:
+        s_qkv = O.amax_scale(x)
+        data = O.quantize(x, 1.0 / s_qkv)
+        s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+        s2 = (1.0 / 127.0) * s_qkv / (0.5 * s_qkv)
+        kw = dict(scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=s2)
+    else:
+        data = x.astype(np.float16)
+        kw = {}
+    if packed:
+        out = T.mha(_t(data, cuda), B, S, N, cu_seqlens=_t(cu, cuda), status=st, **kw).cpu().numpy()
+    else:
+        out = T.mha(_t(data.reshape(S, B, -1), cuda), B, S, N, mask_idx=_t(lengths, cuda), status=st, **kw).cpu().numpy()
+    assert int(st[0]) == 0
+    for b in _QUEUE_SAMPLE + [5]:
+        if packed:
+            seq = data[int(cu[b]):int(cu[b + 1])]
+            got = out[int(cu[b]):int(cu[b + 1])]
+            one = dict(cu=np.array([0, seq.shape[0]], dtype=np.int32))
+        else:
+            seq = data.reshape(S, B, -1)[:, b:b + 1]
+            got = out[:, b:b + 1]
+            one = dict(lengths=lengths[b:b + 1])
+        if seq.shape[0] == 0:
+            continue
+        if int8:
+            ref = O.mha_int8(seq, 1, S, N, d, s1, 127.0, s2, **one)
+            _assert_int8_attention(got, ref)
+        else:
+            ref = O.mha(seq, 1, S, N, d, **one)
+            ok, worst, bad = O.close_abs_or_rel(got, ref, 1e-2, 1e-2)
+            assert ok, (b, worst, bad)

@@ -149,3 +149,44 @@ def test_attention_int8_three_way(cuda, ref, S, lengths, interleaved):
     assert close(y_ref, y_orc), "reference kernels vs oracle"
     assert close(y_new, y_orc), "product vs oracle"
     assert close(y_new, y_ref), "product vs reference kernels"
+
+
+@pytest.mark.parametrize("int8", [False, True])
+def test_attention_benchmark_size_three_way(cuda, ref, int8):
+    """BERT-large S = 384, 64 sequences x 16 heads, ragged packed lengths: the product against the reference's own
+    sm100 kernel over the WHOLE output (every work item of every persistent CTA), and both against the oracle on a
+    sample of sequences."""
+    import tensorrt_b200 as T
+
+    S, B, N, d = 384, 64, 16, 64
+    rng = np.random.default_rng(7 + int8)
+    lengths = rng.integers(1, S + 1, size=B).astype(np.int32)
+    lengths[[0, 31, 63]] = S
+    cu = O.cu_seqlens(lengths)
+    total = int(cu[-1])
+    x = rng.standard_normal((total, 3 * N * d)).astype(np.float32)
+    if int8:
+        s_qkv = O.amax_scale(x)
+        data = O.quantize(x, 1.0 / s_qkv)
+        s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+        s2 = float((1.0 / 127.0) * s_qkv / (0.5 * s_qkv))
+        y_ref = ref.fmha_v2(_t(data, cuda), _t(cu, cuda), B, S, N, d, scales=(s1, 127.0, s2)).cpu().numpy()
+        y_new = T.mha(_t(data, cuda), B, S, N, cu_seqlens=_t(cu, cuda), scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=s2).cpu().numpy()
+        dd = np.abs(y_new.astype(np.int32) - y_ref.astype(np.int32))
+        assert dd.max() <= 2 and (dd > 1).sum() <= max(1, int(1e-5 * dd.size)) and (dd == 0).mean() > 0.98
+    else:
+        data = x.astype(np.float16)
+        y_ref = ref.fmha_v2(_t(data, cuda), _t(cu, cuda), B, S, N, d).cpu().numpy()
+        y_new = T.mha(_t(data, cuda), B, S, N, cu_seqlens=_t(cu, cuda)).cpu().numpy()
+        assert O.close_abs_or_rel(y_new, y_ref, 1e-2, 1e-2)[0]
+    for b in (0, 20, 41, 63):
+        seq = data[int(cu[b]):int(cu[b + 1])]
+        one = np.array([0, seq.shape[0]], dtype=np.int32)
+        for y in (y_ref, y_new):
+            got = y[int(cu[b]):int(cu[b + 1])]
+            if int8:
+                orc = O.mha_int8(seq, 1, S, N, d, s1, 127.0, s2, cu=one)
+                dd = np.abs(got.astype(np.int32) - orc.astype(np.int32))
+                assert dd.max() <= 2 and (dd > 1).sum() <= max(1, int(1e-5 * dd.size))
+            else:
+                assert O.close_abs_or_rel(got, O.mha(seq, 1, S, N, d, cu=one), 1e-2, 1e-2)[0]
