@@ -8,20 +8,25 @@
 //
 // One persistent CTA per SM keeps TWO 128-query tiles in flight (streams 0 and 1). The tiles of the CTA's work
 // list are dealt alternately to the two streams, across the boundaries of (sequence, head) items, so an odd number
-// of tiles per item (S = 384) leaves no stream idle. 11 warps:
+// of tiles per item (S = 384) leaves no stream idle. 12 warps:
 //   warps 0-3 / 4-7 : softmax of stream 0 / 1, ONE THREAD PER QUERY ROW (the 32x32b TMEM load hands lane = row):
 //                     no cross-thread reduction, no barrier among softmax threads. Per key block: load the 128
-//                     scores, block maximum, lazy rescale (below), p = exp2(x*scale*log2e - m), row sum,
-//                     P as FP16 back into the TMEM columns of the scores.
+//                     scores into registers (their TMEM columns are then free for the next block's scores), block
+//                     maximum, lazy rescale (below), p = exp2(x*scale*log2e - m), row sum, P as FP16 pairs into 64
+//                     TMEM columns of its own. The normalising epilogue of a tile is deferred into the first block of
+//                     the stream's next tile, so its wait for the last context product costs nothing.
 //   warp 8          : one lane loads the Q tiles (two slots, one per stream).
 //   warp 9          : one lane loads K / V blocks (128 keys x 64 channels, 16 KB) into a ring of 12 stages. The
 //                     blocks of an item stay resident for all its query tiles when they fit (S <= 768); longer
 //                     sequences stream their blocks once per pair of query tiles.
-//   warp 10         : one lane issues every MMA, serving whichever stream has its next P block ready:
-//                       S = Q K_j^T           (128 x 128, FP32, TMEM columns 128*stream ..)
-//                       O (+)= P_j V_j        (128 x 64, A operand = P straight from TMEM, columns 256 + 64*stream ..)
-//                     S_{j+1} is issued right behind P_j V_j, so that the softmax threads of one stream work while
-//                     the tensor pipe serves the other.
+//   warp 10         : one lane issues the scores of both streams,  S = Q K_j^T  (128 x 128, FP32, TMEM columns
+//                     128*stream ..), as soon as the softmax threads hold the previous block in registers.
+//   warp 11         : one lane issues the context products of both streams,  O (+)= P_j V_j  (128 x 64, A operand = P
+//                     straight from TMEM columns 256 + 64*stream .., accumulator in columns 384 + 64*stream ..).
+//                     (Every tcgen05.mma / commit keeps its issuing thread busy for 50-120 cycles; one thread for all
+//                     twelve MMAs and four commits of a block would be the slowest link.)
+//                     Neither issuer ever blocks on one stream: an operand that a loader delivers only after the other
+//                     stream has been served must not stall that other stream.
 // Online softmax: the running maximum m only moves when the block maximum exceeds it by more than 8 in the log2
 // domain (P then stays below 2^8, far inside FP16); when it moves, the softmax threads scale the row sum and the
 // context accumulator in TMEM themselves (after the previous P V product has completed). The final context is
@@ -29,19 +34,31 @@
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM and reports through the status word.
 #include "sm100.cuh"
 
+#include <cstdlib>
+
 namespace b200
 {
 
 namespace
 {
 
+#ifdef MHA_TRACE
+// timeline of CTA 0: (role, event code, cycle) triples, 512 events per role, roles 0/1 softmax, 2/3 MMA threads
+#define TR_DECL(role) uint32_t trN = 0; uint32_t* const trBuf = (blockIdx.x == 0 && args.statusWord) ? args.statusWord + 16 + (role) * 1024 : nullptr
+#define TR_EVT(code) do { if (trBuf && trN < 512) { trBuf[2 * trN] = (code); trBuf[2 * trN + 1] = static_cast<uint32_t>(clock64()); ++trN; } } while (0)
+#else
+#define TR_DECL(role)
+#define TR_EVT(code)
+#endif
+
 constexpr int kTile = 128;       // query rows per tile = keys per block
 constexpr int kHeadSize = 64;    // channels per tile row (smaller heads are zero-filled by the TMA unit)
 constexpr int kStages = 12;      // K / V ring
 constexpr int kStageBytes = kTile * kHeadSize * 2; // 16 KB: one Q tile, one K block, one V block
-constexpr int kThreads = 352;    // 8 softmax warps, Q loader, K/V loader, MMA issuer
+constexpr int kThreads = 384;    // 8 softmax warps, Q loader, K/V loader, two MMA issuers
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kOColumn = 256; // context accumulators: 64 columns per stream
+constexpr uint32_t kPColumn = 256; // P blocks (FP16 pairs): 64 columns per stream
+constexpr uint32_t kOColumn = 384; // context accumulators: 64 columns per stream
 constexpr float kRescaleLog2 = 8.f;
 
 struct OnlineArgs
@@ -55,15 +72,18 @@ struct OnlineArgs
     float scaleBmm1;
     uint32_t* statusWord;
     int32_t tilesPerUnit, chunks; // a work unit = (sequence, head, chunk of tilesPerUnit query tiles)
+    uint32_t staggerNs;           // start delay of stream 1
 };
 
 // [ Q slot 0 ][ Q slot 1 ][ 12 K/V stages ][ barriers ]
 constexpr int kSmemQ = 0;
 constexpr int kSmemKv = 2 * kStageBytes;
 constexpr int kSmemBars = kSmemKv + kStages * kStageBytes;
-// full[12] empty[12] qFull[2] qFree[2] sFull[2] pReady[2] pvDone[2], tmem slot, abort flag
-constexpr int kNumBars = 2 * kStages + 10;
-constexpr int kSmemBytes = kSmemBars + kNumBars * 8 + 16 + 1024;
+// full[12] empty[12] qFull[2] qFree[2] sFull[2] sFree[2] pReady[2] pvDone[2], tmem slot, abort flag
+constexpr int kNumBars = 2 * kStages + 12;
+constexpr int kGeoEntries = 128; // geometry words of the CTA's first work units, read once from global memory
+constexpr int kSmemGeo = kSmemBars + kNumBars * 8 + 16;
+constexpr int kSmemBytes = kSmemGeo + kGeoEntries * 8 + 1024;
 
 __device__ __forceinline__ float ex2Approx(float x)
 {
@@ -129,7 +149,7 @@ struct Unit
 // stage L % kStages and is the (L / kStages)-th fill of that stage.
 struct Walker
 {
-    OnlineArgs const& a;
+    OnlineArgs const* ap;
     int32_t numUnits;
     int32_t unit;
     Unit g;
@@ -138,36 +158,68 @@ struct Walker
     int32_t subTiles; // tiles in the sub-item = uses of each of its stages
     uint32_t loadBase;
     uint32_t n;
+    // (row base, end) or mask length of the CTA's k-th unit for k < kGeoEntries, staged in shared memory by the kernel's
+    // prologue: a load from global memory at every change of unit (under streaming traffic often a DRAM access) would
+    // sit on the critical path of every role
+    int2 const* geo;
 
-    __device__ __forceinline__ Walker(OnlineArgs const& args)
-        : a(args)
+    __device__ __forceinline__ Walker(OnlineArgs const& args, int2 const* geoTable)
+        : ap(&args)
         , numUnits(args.B * args.N * args.chunks)
+        , geo(geoTable)
     {
+    }
+
+    __device__ __forceinline__ static void fetch(OnlineArgs const& a, int32_t u, int32_t& wa, int32_t& wb)
+    {
+        int32_t const b = (u / a.chunks) / a.N;
+        wa = 0;
+        wb = 0;
+        if (a.fixedLayout)
+        {
+            if (a.maskIdx)
+                wb = __ldg(a.maskIdx + b);
+        }
+        else
+        {
+            wa = __ldg(a.cu + b);
+            wb = __ldg(a.cu + b + 1);
+        }
     }
 
     // returns whether the unit has work for the tensor pipeline (a query row and a valid key)
     __device__ __forceinline__ bool getUnit(int32_t u, Unit& o) const
     {
-        int32_t const chunk = u % a.chunks;
-        int32_t const i = u / a.chunks;
-        o.b = i / a.N;
-        o.head = i - o.b * a.N;
-        if (a.fixedLayout)
+        int32_t wa, wb;
+        int32_t const k = (u - static_cast<int32_t>(blockIdx.x)) / static_cast<int32_t>(gridDim.x);
+        if (k < kGeoEntries)
+        {
+            int2 const e = geo[k];
+            wa = e.x;
+            wb = e.y;
+        }
+        else
+            fetch(*ap, u, wa, wb);
+        int32_t const chunk = u % ap->chunks;
+        int32_t const i = u / ap->chunks;
+        o.b = i / ap->N;
+        o.head = i - o.b * ap->N;
+        if (ap->fixedLayout)
         {
             o.rowBase = 0;
-            o.rows = a.S;
-            o.len = a.maskIdx ? min(max(__ldg(a.maskIdx + o.b), 0), a.S) : a.S;
+            o.rows = ap->S;
+            o.len = ap->maskIdx ? min(max(wb, 0), ap->S) : ap->S;
         }
         else
         {
-            o.rowBase = __ldg(a.cu + o.b);
-            o.len = min(max(__ldg(a.cu + o.b + 1) - o.rowBase, 0), a.S);
+            o.rowBase = wa;
+            o.len = min(max(wb - wa, 0), ap->S);
             o.rows = o.len;
         }
         o.nb = (o.len + kTile - 1) / kTile;
         int32_t const nq = (o.rows + kTile - 1) / kTile;
-        o.tBegin = chunk * a.tilesPerUnit;
-        o.tEnd = min(nq, o.tBegin + a.tilesPerUnit);
+        o.tBegin = chunk * ap->tilesPerUnit;
+        o.tEnd = min(nq, o.tBegin + ap->tilesPerUnit);
         return o.len > 0 && o.tBegin < o.tEnd;
     }
 
@@ -241,25 +293,28 @@ __global__ void __maxnreg__(168)
     uint64_t* empty = bars + kStages;         // [12] every MMA that reads the stage has completed
     uint64_t* qFull = bars + 2 * kStages;     // [2]  Q tile of the stream landed
     uint64_t* qFree = qFull + 2;              // [2]  all score MMAs of the stream's tile have completed
-    uint64_t* sFull = qFree + 2;              // [2]  scores of a key block complete         (once per block)
-    uint64_t* pReady = sFull + 2;             // [2]  P block written, 128 arrivals           (once per block)
-    uint64_t* pvDone = pReady + 2;            // [2]  context product of a block complete     (once per block)
+    uint64_t* sFull = qFree + 2;              // [2]  scores of a key block complete               (once per block)
+    uint64_t* sFree = sFull + 2;              // [2]  scores are in registers, 4 arrivals           (once per block)
+    uint64_t* pReady = sFree + 2;             // [2]  P block written, 4 arrivals                   (once per block)
+    uint64_t* pvDone = pReady + 2;            // [2]  context product of a block complete           (once per block)
     uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(pvDone + 2);
     volatile uint32_t* abortFlag = tmemSlot + 1;
+    int2* geoTable = reinterpret_cast<int2*>(smem + kSmemGeo);
 
     if (threadIdx.x == 0)
     {
         for (int i = 0; i < kStages; ++i)
         {
             mbarInit(&full[i], 1);
-            mbarInit(&empty[i], 1);
+            mbarInit(&empty[i], 2); // one arrival per stream (see the MMA threads)
         }
         for (int i = 0; i < 2; ++i)
         {
             mbarInit(&qFull[i], 1);
             mbarInit(&qFree[i], 1);
             mbarInit(&sFull[i], 1);
-            mbarInit(&pReady[i], kTile);
+            mbarInit(&sFree[i], 4); // one arrival per softmax warp of the stream
+            mbarInit(&pReady[i], 4);
             mbarInit(&pvDone[i], 1);
         }
         *abortFlag = 0;
@@ -279,6 +334,17 @@ __global__ void __maxnreg__(168)
     uint32_t const tmemBase = *tmemSlot;
     gridDependencyLaunch();
     gridDependencyWait();
+    {
+        int32_t const numUnits = args.B * args.N * args.chunks;
+        int32_t const u = static_cast<int32_t>(blockIdx.x) + static_cast<int32_t>(threadIdx.x) * static_cast<int32_t>(gridDim.x);
+        if (threadIdx.x < kGeoEntries && u < numUnits)
+        {
+            int32_t wa, wb;
+            Walker::fetch(args, u, wa, wb);
+            geoTable[threadIdx.x] = make_int2(wa, wb);
+        }
+        __syncthreads();
+    }
 
     // which: 0 = Q, 1 = K, 2 = V; row = first token of the box inside the (packed or per-sequence) tensor
     auto load = [&](uint8_t* dst, uint64_t* bar, int which, Unit const& g, int32_t row) {
@@ -293,7 +359,7 @@ __global__ void __maxnreg__(168)
         // ---- Q tiles: slot n & 1, refilled when the score MMAs of the stream's previous tile have completed ----
         if (lane == 0)
         {
-            Walker w(args);
+            Walker w(args, geoTable);
             bool ok = true;
             for (bool more = w.begin(); more && ok; more = w.next())
             {
@@ -309,10 +375,10 @@ __global__ void __maxnreg__(168)
     }
     else if (warp == 9)
     {
-        // ---- K / V blocks of every sub-item, in the order the MMA thread consumes them ----
+        // ---- K / V blocks of every sub-item, in the order the MMA threads consume them ----
         if (lane == 0)
         {
-            Walker w(args);
+            Walker w(args, geoTable);
             bool ok = true;
             for (bool more = w.begin(); more && ok; more = w.next())
             {
@@ -337,142 +403,121 @@ __global__ void __maxnreg__(168)
             }
         }
     }
-    else if (warp == 10)
+    else if (warp == 10 || warp == 11)
     {
-        // ---- MMA issue for both streams ----
+        // ---- MMA issue: warp 10 owns stream 0, warp 11 stream 1 ----
+        // The events of one stream come in a fixed order - scores of block j in registers (sFree), P_j written
+        // (pReady), scores of block j+1 in registers, ... - so its thread simply waits for them in turn: after sFree it
+        // issues the next scores (of this tile or of the stream's next one), after pReady the context product.
         if (lane == 0)
         {
+            uint32_t const s = static_cast<uint32_t>(warp - 10);
             // K-major Q / K tiles (128-byte rows, 128-byte swizzle): SBO = 8 rows = 1024 B. V is MN-major (the head
             // dimension contiguous): one MMA consumes 16 key rows = 2048 B.
             uint64_t const dQk = makeSmemDesc(0, 16, 1024, kSwizzle128B);
             uint64_t const dV = makeSmemDesc(0, 1024, 1024, kSwizzle128B);
             uint32_t const hiQk = static_cast<uint32_t>(dQk >> 32), hiV = static_cast<uint32_t>(dV >> 32);
-            uint32_t const qLo = static_cast<uint32_t>(dQk) + (smemAddr(sQ) >> 4);
+            uint32_t const qLo = static_cast<uint32_t>(dQk) + (smemAddr(sQ) >> 4) + s * (kStageBytes >> 4);
             uint32_t const kLo = static_cast<uint32_t>(dQk) + (smemAddr(sKv) >> 4);
             uint32_t const vLo = static_cast<uint32_t>(dV) + (smemAddr(sKv) >> 4);
             constexpr uint32_t kStage16 = kStageBytes >> 4;
-
+            uint32_t const fullAddr = smemAddr(full), emptyAddr = smemAddr(empty);
+            uint32_t const sFullAddr = smemAddr(&sFull[s]), sFreeAddr = smemAddr(&sFree[s]), pReadyAddr = smemAddr(&pReady[s]);
+            uint32_t const pvDoneAddr = smemAddr(&pvDone[s]), qFullAddr = smemAddr(&qFull[s]), qFreeAddr = smemAddr(&qFree[s]);
+            uint32_t const tS = tmemBase + s * kTile, tP = tmemBase + kPColumn + s * kHeadSize, tO = tmemBase + kOColumn + s * kHeadSize;
             bool ok = true;
-            uint64_t used = 0; // per ring stage (4 bits each): uses of its current contents so far
-
-            // the MMAs that read stage `s` have been issued once more; after the last use of the sub-item the stage
-            // goes back to the loader as soon as they complete
-            auto useStage = [&](uint32_t s, int32_t uses) {
-                uint32_t const cnt = static_cast<uint32_t>((used >> (4 * s)) & 15u) + 1u;
-                if (static_cast<int32_t>(cnt) >= uses)
+            auto commitAddr = [](uint32_t barAddr) {
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barAddr) : "memory");
+            };
+            // A ring stage goes back to the loader when the MMAs of BOTH streams that read it have completed: each stream
+            // commits once, with its last tile of the sub-item; a sub-item of a single tile has no second stream, and its
+            // thread adds the missing arrival itself.
+            auto release = [&](uint32_t stage, Walker const& w) {
+                if (w.t >= w.subEnd - 2)
                 {
-                    tcCommit(&empty[s]);
-                    used &= ~(15ull << (4 * s));
+                    commitAddr(emptyAddr + 8 * stage);
+                    if (w.subTiles == 1)
+                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(emptyAddr + 8 * stage) : "memory");
                 }
-                else
-                    used += 1ull << (4 * s);
             };
-
-            // Nothing below blocks: a stream whose next MMA lacks an operand is simply skipped in this round of the
-            // polling loop. (A blocking wait for one stream could wait for a Q tile or a K / V stage that the loaders
-            // only deliver after the OTHER stream has been served.)
-            enum : int32_t
-            {
-                kOpStart = 0, // first scores of a tile: needs its Q tile and K_0
-                kOpPv = 1,    // context product of block j: needs P_j and V_j
-                kOpQk = 2     // scores of block j (j >= 1): needs K_j
-            };
-            struct Stream
-            {
-                bool active;
-                int32_t op;
-                int32_t j;        // key block of the pending operation
-                uint32_t blocks;  // context products issued so far (parity of pReady)
-            };
-            Walker w0(args), w1(args);
-            Stream st0{false, kOpStart, 0, 0}, st1{false, kOpStart, 0, 0};
-
-            auto landed = [&](uint32_t L) { return mbarTryWaitAddr(smemAddr(&full[L % kStages]), (L / kStages) & 1u); };
-            auto issueQk = [&](Walker const& w, uint32_t s, int32_t j) {
-                uint32_t const stage = (w.loadBase + 2u * j) % kStages;
+            // scores of key block j of the tile `w` stands on
+            auto issueQk = [&](Walker const& w, int32_t j) {
+                uint32_t const L = w.loadBase + 2u * j;
+                uint32_t const stage = L % kStages;
+                ok = ok && mbarWaitAddr(fullAddr + 8 * stage, (L / kStages) & 1u, abortFlag, kWaitTmaFull);
+                if (!ok)
+                    return;
                 tcFenceAfter();
+                uint32_t const b = kLo + stage * kStage16;
 #pragma unroll
                 for (int k = 0; k < 4; ++k) // head size 64 = 4 x 16
-                    mmaLoHi<false>(tmemBase + s * kTile, qLo + s * kStage16 + 2 * k, hiQk, kLo + stage * kStage16 + 2 * k, hiQk,
-                        kIdescQk, k != 0);
-                useStage(stage, w.subTiles);
-                tcCommit(&sFull[s]);
+                    mmaLoHi<false>(tS, qLo + 2 * k, hiQk, b + 2 * k, hiQk, kIdescQk, k != 0);
+                commitAddr(sFullAddr);
+                release(stage, w);
                 if (j == w.g.nb - 1)
-                    tcCommit(&qFree[s]);
+                    commitAddr(qFreeAddr);
             };
-            auto issuePv = [&](Walker const& w, uint32_t s, int32_t j) {
-                uint32_t const stage = (w.loadBase + 2u * j + 1u) % kStages;
+            auto issuePv = [&](Walker const& w, int32_t j) {
+                uint32_t const L = w.loadBase + 2u * j + 1u;
+                uint32_t const stage = L % kStages;
+                ok = ok && mbarWaitAddr(fullAddr + 8 * stage, (L / kStages) & 1u, abortFlag, kWaitTmaFull);
+                if (!ok)
+                    return;
                 tcFenceAfter();
+                uint32_t const b = vLo + stage * kStage16;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) // 128 keys = 8 x 16; P: 8 TMEM columns per 16 keys
-                    mmaF16TmemA(tmemBase + kOColumn + s * kHeadSize, tmemBase + s * kTile + 8 * k, vLo + stage * kStage16 + k * 128u,
-                        hiV, kIdescPv, (j | k) != 0);
-                useStage(stage, w.subTiles);
-                tcCommit(&pvDone[s]);
-            };
-            // issues as many of the stream's pending operations as have their operands; returns whether any was issued
-            auto advance = [&](Walker& w, Stream& st, uint32_t s) -> bool {
-                bool progressed = false;
-                while (st.active)
-                {
-                    if (st.op == kOpStart)
-                    {
-                        if (!mbarTryWaitAddr(smemAddr(&qFull[s]), (w.n >> 1) & 1u) || !landed(w.loadBase))
-                            break;
-                        issueQk(w, s, 0);
-                        st.j = 0;
-                        st.op = kOpPv;
-                    }
-                    else if (st.op == kOpPv)
-                    {
-                        if (!mbarTryWaitAddr(smemAddr(&pReady[s]), st.blocks & 1u) || !landed(w.loadBase + 2u * st.j + 1u))
-                            break;
-                        ++st.blocks;
-                        issuePv(w, s, st.j);
-                        ++st.j;
-                        if (st.j < w.g.nb)
-                            st.op = kOpQk;
-                        else
-                        {
-                            st.op = kOpStart;
-                            st.active = w.next() && w.next();
-                        }
-                    }
-                    else
-                    {
-                        if (!landed(w.loadBase + 2u * st.j))
-                            break;
-                        issueQk(w, s, st.j);
-                        st.op = kOpPv;
-                    }
-                    progressed = true;
-                }
-                return progressed;
+                    mmaF16TmemA(tO, tP + 8 * k, b + k * 128u, hiV, kIdescPv, (j | k) != 0);
+                commitAddr(pvDoneAddr);
+                release(stage, w);
             };
 
-            st0.active = w0.begin();
-            st1.active = w1.begin() && w1.next();
-            uint32_t idle = 0;
-            uint64_t tIdle = 0;
-            while ((st0.active || st1.active) && ok)
+            TR_DECL(2 + s);
+            Walker cur(args, geoTable);
+            bool active = cur.begin() && (s == 0 || cur.next());
+            uint32_t qk = 0, pv = 0; // groups of score / context MMAs issued so far
+            if (active)
             {
-                bool progressed = advance(w0, st0, 0);
-                progressed = advance(w1, st1, 1) || progressed;
-                if (progressed)
-                    idle = 0;
-                else if ((++idle & 1023u) == 0)
+                ok = mbarWaitAddr(qFullAddr, (cur.n >> 1) & 1u, abortFlag, kWaitTmaFull);
+                if (ok)
+                    issueQk(cur, 0);
+                qk = 1;
+            }
+            while (active && ok)
+            {
+                Walker nxt = cur;
+                bool const hasNext = nxt.next() && nxt.next();
+                for (int j = 0; j < cur.g.nb && ok; ++j)
                 {
-                    if (*abortFlag != 0)
-                        ok = false;
-                    uint64_t const now = globalTimerNs();
-                    if (idle == 1024u)
-                        tIdle = now;
-                    else if (now - tIdle > kWaitLimitNs)
+                    // the scores that follow block j: block j + 1, or the first block of the stream's next tile
+                    if (j + 1 < cur.g.nb)
                     {
-                        *abortFlag = kWaitSoftmax;
-                        ok = false;
+                        ok = mbarWaitAddr(sFreeAddr, (qk - 1) & 1u, abortFlag, kWaitAccFree);
+                        TR_EVT(1);
+                        if (ok)
+                            issueQk(cur, j + 1);
+                        TR_EVT(2);
+                        ++qk;
                     }
+                    else if (hasNext)
+                    {
+                        ok = mbarWaitAddr(sFreeAddr, (qk - 1) & 1u, abortFlag, kWaitAccFree)
+                            && mbarWaitAddr(qFullAddr, (nxt.n >> 1) & 1u, abortFlag, kWaitTmaFull);
+                        TR_EVT(1);
+                        if (ok)
+                            issueQk(nxt, 0);
+                        TR_EVT(2);
+                        ++qk;
+                    }
+                    ok = ok && mbarWaitAddr(pReadyAddr, pv & 1u, abortFlag, kWaitSoftmax);
+                    TR_EVT(3);
+                    if (ok)
+                        issuePv(cur, j);
+                    TR_EVT(4);
+                    ++pv;
                 }
+                cur = nxt;
+                active = hasNext;
             }
         }
     }
@@ -483,6 +528,7 @@ __global__ void __maxnreg__(168)
         int const r = (warp & 3) * 32 + lane;
         uint32_t const tRow = tmemBase + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         uint32_t const tS = tRow + s * kTile;
+        uint32_t const tP = tRow + kPColumn + s * kHeadSize;
         uint32_t const tO = tRow + kOColumn + s * kHeadSize;
         float const sl2 = args.scaleBmm1 * 1.4426950408889634f;
         float const thrRaw = kRescaleLog2 / sl2; // the same threshold on the unscaled scores
@@ -491,7 +537,7 @@ __global__ void __maxnreg__(168)
         if (s == 0 && args.fixedLayout)
         {
             // sequences without a valid key: every probability is zero and so is the context row
-            Walker z(args);
+            Walker z(args, geoTable);
             Unit g;
             int const chunks16 = args.d / 8;
             for (int u = blockIdx.x; u < z.numUnits; u += gridDim.x)
@@ -511,9 +557,55 @@ __global__ void __maxnreg__(168)
             }
         }
 
-        Walker w(args);
+        TR_DECL(lane == 0 && (warp & 3) == 0 ? s : 7);
+        // The two streams share the exponential unit. Started together they stay in step - both in their exponentials
+        // (at half rate each), then both in the phases that do not use the unit; half a block apart, one stream's
+        // exponentials run under the other's loads, maxima and waits.
+        if (s == 1)
+            __nanosleep(args.staggerNs);
+        Walker w(args, geoTable);
         bool active = w.begin() && (s == 0 || w.next());
         uint32_t blocks = 0; // key blocks this stream has completed: parity of sFull / pvDone
+        // the tile whose context still has to be normalised and stored (null: none, or a row beyond the sequence)
+        bool pending = false;
+        __half* pendDst = nullptr;
+        float pendInv = 0.f;
+        // context of the stream's previous tile: wait for its last product, O / rowsum -> FP16
+        auto epilogue = [&]() {
+            ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
+            tcFenceAfter();
+#pragma unroll 1
+            for (int c = 0; c < kHeadSize; c += 16) // 16 columns at a time: the block's scores stay in registers
+            {
+                uint32_t o[16];
+                tmemLoad16(tO + c, o);
+                tmemLoadWait16(o);
+                if (pendDst != nullptr && ok && c < args.d)
+                {
+                    float f[8];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            f[i] = __uint_as_float(o[8 * h + i]) * pendInv;
+                        reinterpret_cast<uint4*>(pendDst + c)[h] = packHalf8(f);
+                    }
+                }
+            }
+            tcFenceBefore();
+            pending = false;
+        };
+        // Keys at or beyond `limit` (counted from the chunk's first column) take no part: -inf scores, zero probabilities.
+        auto maskChunk = [](uint32_t(&x)[32], int limit) {
+            if (limit < 32)
+            {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (i >= limit)
+                        x[i] = 0xff800000u;
+            }
+        };
         while (active)
         {
             Unit const g = w.g;
@@ -521,8 +613,13 @@ __global__ void __maxnreg__(168)
 #pragma unroll 1
             for (int j = 0; j < g.nb; ++j)
             {
+                TR_EVT(10);
                 ok = ok && mbarWait(&sFull[s], blocks & 1u, abortFlag, kWaitSoftmax);
                 tcFenceAfter();
+                TR_EVT(11);
+                int const limit = g.len - j * kTile;
+                // All 128 scores of the row go to registers at once; their TMEM columns are free for the next block's
+                // scores from here on, so the tensor pipe works on S_{j+1} during this block's exponentials.
                 uint32_t x0[32], x1[32], x2[32], x3[32];
                 tmemLoad32(tS, x0);
                 tmemLoad32(tS + 32, x1);
@@ -532,35 +629,34 @@ __global__ void __maxnreg__(168)
                 tmemLoadWait32(x1);
                 tmemLoadWait32(x2);
                 tmemLoadWait32(x3);
-                int const limit = g.len - j * kTile;
-                if (limit < kTile) // the last block of the sequence: keys beyond its length take no part
-                {
+                tcFenceBefore();
+                __syncwarp();
+                if (lane == 0)
+                    mbarArrive(&sFree[s]);
+                TR_EVT(12);
+                // eight independent chains: the block maximum costs the latency of eight dependent maxima, not thirty-two
+                float mA = -INFINITY, mB = -INFINITY, mC = -INFINITY, mD = -INFINITY;
+                float mE = -INFINITY, mF = -INFINITY, mG = -INFINITY, mH = -INFINITY;
+                maskChunk(x0, limit);
+                maskChunk(x1, limit - 32);
+                maskChunk(x2, limit - 64);
+                maskChunk(x3, limit - 96);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                    {
-                        if (i >= limit)
-                            x0[i] = 0xff800000u;
-                        if (i + 32 >= limit)
-                            x1[i] = 0xff800000u;
-                        if (i + 64 >= limit)
-                            x2[i] = 0xff800000u;
-                        if (i + 96 >= limit)
-                            x3[i] = 0xff800000u;
-                    }
-                }
-                float mA = __uint_as_float(x0[0]), mB = __uint_as_float(x1[0]), mC = __uint_as_float(x2[0]), mD = __uint_as_float(x3[0]);
-#pragma unroll
-                for (int i = 1; i < 31; i += 2)
+                for (int i = 0; i < 32; i += 4)
                 {
                     mA = fmax3(mA, __uint_as_float(x0[i]), __uint_as_float(x0[i + 1]));
-                    mB = fmax3(mB, __uint_as_float(x1[i]), __uint_as_float(x1[i + 1]));
-                    mC = fmax3(mC, __uint_as_float(x2[i]), __uint_as_float(x2[i + 1]));
-                    mD = fmax3(mD, __uint_as_float(x3[i]), __uint_as_float(x3[i + 1]));
+                    mB = fmax3(mB, __uint_as_float(x0[i + 2]), __uint_as_float(x0[i + 3]));
+                    mC = fmax3(mC, __uint_as_float(x1[i]), __uint_as_float(x1[i + 1]));
+                    mD = fmax3(mD, __uint_as_float(x1[i + 2]), __uint_as_float(x1[i + 3]));
+                    mE = fmax3(mE, __uint_as_float(x2[i]), __uint_as_float(x2[i + 1]));
+                    mF = fmax3(mF, __uint_as_float(x2[i + 2]), __uint_as_float(x2[i + 3]));
+                    mG = fmax3(mG, __uint_as_float(x3[i]), __uint_as_float(x3[i + 1]));
+                    mH = fmax3(mH, __uint_as_float(x3[i + 2]), __uint_as_float(x3[i + 3]));
                 }
-                mA = fmax3(mA, __uint_as_float(x0[31]), __uint_as_float(x1[31]));
-                mC = fmax3(mC, __uint_as_float(x2[31]), __uint_as_float(x3[31]));
-                float const mBlk = fmaxf(fmaxf(mA, mB), fmaxf(mC, mD));
-
+                mA = fmax3(mA, mB, mC);
+                mD = fmax3(mD, mE, mF);
+                mG = fmaxf(mG, mH);
+                float const mBlk = fmax3(mA, mD, mG);
                 if (j == 0)
                     mRun = mBlk;
                 else
@@ -580,7 +676,7 @@ __global__ void __maxnreg__(168)
                         ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
                         tcFenceAfter();
 #pragma unroll 1
-                        for (int c = 0; c < kHeadSize; c += 16) // 16 columns at a time: the scores stay in registers
+                        for (int c = 0; c < kHeadSize; c += 16)
                         {
                             uint32_t o[16];
                             tmemLoad16(tO + c, o);
@@ -594,9 +690,8 @@ __global__ void __maxnreg__(168)
                 }
                 float const negM = -mRun * sl2;
 
-                // p = exp2(x * scale * log2e - m); P as FP16 pairs over the first 64 columns of the scores
-                auto expBlock = [&](uint32_t(&x)[32], uint32_t col) {
-                    uint32_t p[16];
+                // p = exp2(x * scale * log2e - m), row sum, P as FP16 pairs (32 keys -> 16 columns)
+                auto expChunk = [&](uint32_t(&x)[32], uint32_t(&p)[16]) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4)
                     {
@@ -611,54 +706,54 @@ __global__ void __maxnreg__(168)
                         p[i / 2] = packHalf2(e0, e1);
                         p[i / 2 + 1] = packHalf2(e2, e3);
                     }
-                    tmemStore16(tS + col, p); // 32 keys -> 16 columns
                 };
-                expBlock(x0, 0);
-                expBlock(x1, 16);
-                expBlock(x2, 32);
-                expBlock(x3, 48);
+                {
+                    uint32_t pa[16], pb[16];
+                    TR_EVT(13);
+                    expChunk(x0, pa);
+                    expChunk(x1, pb);
+                    TR_EVT(14);
+                    // The P columns are read by the previous block's product and the context accumulator by the previous
+                    // tile's epilogue: half a block of exponentials later both are long done.
+                    if (pending)
+                        epilogue();
+                    else if (blocks > 0)
+                        ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
+                    TR_EVT(15);
+                    tmemStore16(tP, pa);
+                    tmemStore16(tP + 16, pb);
+                    expChunk(x2, pa);
+                    tmemStore16(tP + 32, pa);
+                    expChunk(x3, pb);
+                    tmemStore16(tP + 48, pb);
+                    TR_EVT(16);
+                }
                 tmemStoreWait();
                 tcFenceBefore();
-                mbarArrive(&pReady[s]);
+                __syncwarp();
+                if (lane == 0)
+                    mbarArrive(&pReady[s]);
+                TR_EVT(17);
                 ++blocks;
             }
-
-            // ---- epilogue: context / row sum -> FP16 ----
-            ok = ok && mbarWait(&pvDone[s], (blocks - 1) & 1u, abortFlag, kWaitAccFull);
-            tcFenceAfter();
-            uint32_t o0[32], o1[32];
-            tmemLoad32(tO, o0);
-            tmemLoad32(tO + 32, o1);
-            tmemLoadWait32(o0);
-            tmemLoadWait32(o1);
-            tcFenceBefore();
             int const q = w.t * kTile + r;
-            if (q < g.rows && ok)
+            pending = true;
+            pendInv = 1.f / ((l0 + l1) + (l2 + l3));
+            pendDst = nullptr;
+            if (q < g.rows)
             {
-                float const inv = 1.f / ((l0 + l1) + (l2 + l3));
-                __half* dst;
                 if (BNSD)
-                    dst = static_cast<__half*>(args.out) + ((static_cast<int64_t>(g.b) * args.N + g.head) * args.S + q) * args.d;
+                    pendDst = static_cast<__half*>(args.out) + ((static_cast<int64_t>(g.b) * args.N + g.head) * args.S + q) * args.d;
                 else
                 {
                     int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + g.b : static_cast<int64_t>(g.rowBase) + q;
-                    dst = static_cast<__half*>(args.out) + rr * args.N * args.d + g.head * args.d;
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                {
-                    if (c * 8 < args.d)
-                    {
-                        float f[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            f[i] = __uint_as_float(c < 4 ? o0[c * 8 + i] : o1[(c - 4) * 8 + i]) * inv;
-                        reinterpret_cast<uint4*>(dst)[c] = packHalf8(f);
-                    }
+                    pendDst = static_cast<__half*>(args.out) + rr * args.N * args.d + g.head * args.d;
                 }
             }
             active = w.next() && w.next();
         }
+        if (pending)
+            epilogue();
         tcFenceBefore();
     }
 
@@ -711,6 +806,10 @@ int32_t launchOnline(CUtensorMap const (&maps)[3], OnlineArgs args, cudaStream_t
     int64_t const items = static_cast<int64_t>(args.B) * args.N;
     args.tilesPerUnit = chooseTilesPerUnit(items, nqMax, smCount());
     args.chunks = (nqMax + args.tilesPerUnit - 1) / args.tilesPerUnit;
+    {
+        char const* e = std::getenv("BERT_B200_MHA_STAGGER");
+        args.staggerNs = e ? static_cast<uint32_t>(std::atoi(e)) : 800u;
+    }
     int64_t const units = items * args.chunks;
     if (units > INT32_MAX)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: too many work units (%lld)", static_cast<long long>(units));
@@ -742,7 +841,7 @@ int32_t mhaOnlineF16(bert_b200_mha_params const& p, cudaStream_t stream)
     maps[1] = maps[0];
     maps[2] = maps[0];
     OnlineArgs const args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx,
-        p.scale_bmm1, p.status_word, 1, 1};
+        p.scale_bmm1, p.status_word, 1, 1, 0};
     return launchOnline<false>(maps, args, stream);
 }
 
@@ -762,7 +861,7 @@ int32_t mhaOnlineF16Bnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t 
         if (st != BERT_B200_OK)
             return st;
     }
-    OnlineArgs const args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.status_word, 1, 1};
+    OnlineArgs const args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.status_word, 1, 1, 0};
     return launchOnline<true>(maps, args, stream);
 }
 

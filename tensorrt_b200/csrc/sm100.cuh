@@ -90,6 +90,24 @@ __device__ __forceinline__ bool mbarTryWaitAddr(uint32_t barAddr, uint32_t parit
     return ok != 0;
 }
 
+// Non-blocking form: mbarrier.try_wait may suspend the thread for a system-dependent time before it reports an
+// incomplete phase; a thread that polls several barriers in turn (and must not sleep on one while another completes)
+// uses test_wait, which returns at once.
+__device__ __forceinline__ bool mbarTestWaitAddr(uint32_t barAddr, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(barAddr), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Every spin in these kernels is bounded: after kWaitLimitNs without progress the waiter records
 // `code` in *abortFlag (shared memory; every later wait in the CTA returns immediately) and
 // returns false. The kernel then drains, frees its TMEM and exits; the host sees the status word.
