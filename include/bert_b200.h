@@ -216,16 +216,15 @@ BERT_B200_API int32_t bert_b200_fc(bert_b200_fc_params const* params, void* stre
 
 /*
  * O = softmax(Q K^T * scale, keys < len_b) V per (sequence b, head n).
- * Tensor-core kernel (FP16, INT8): head sizes 16, 32, 48, 64 (32, 64 when interleaved), S <= 512; smaller heads
- * ride the 64-wide tiles with the missing channels zero-filled by the TMA unit, which replaces the reference's
- * pad / unpad copies (plugin/bertQKVToContextPlugin/zeroPadding2d.cu:190-204). FP32 always, and FP16 outside
- * those shapes, run a SIMT kernel (the reference's unfused runner, mhaRunner.cu:533-601); INT8 outside them is
- * BERT_B200_NOT_SUPPORTED as in the reference (qkvToContextPlugin.cpp:530).
- * FP16 with S > 512 and a head size of the tensor-core kernel stays on the tensor cores when `workspace` holds
- * bert_b200_mha_workspace_size() bytes (16-byte aligned, contents irrelevant): the keys are processed in chunks of
- * 384 by the same kernel, which leaves unnormalised FP32 context rows and the row statistics per chunk there, and a
- * second kernel merges the chunks (the result of one softmax over all keys). The reference's unfused runner gets its
- * score matrix from the plugin workspace the same way (qkvToContextPlugin.cpp:430-438).
+ * Tensor-core kernels (FP16, INT8): head sizes 16, 32, 48, 64 (32, 64 when interleaved); smaller heads ride the
+ * 64-wide tiles with the missing channels zero-filled by the TMA unit, which replaces the reference's pad / unpad
+ * copies (plugin/bertQKVToContextPlugin/zeroPadding2d.cu:190-204). FP16 takes any sequence length (key blocks are
+ * streamed with an online softmax; scale_bmm1 must be positive) and ignores scale_softmax / scale_bmm2; INT8 takes
+ * S <= 512 (its quantised probabilities need the whole score row in tensor memory) and is BERT_B200_NOT_SUPPORTED
+ * beyond, as in the reference (qkvToContextPlugin.cpp:530). FP32 always, and FP16 with other head sizes, run a SIMT
+ * kernel (the reference's unfused runner, mhaRunner.cu:533-601).
+ * No attention kernel needs scratch memory: `workspace` is ignored and bert_b200_mha_workspace_size() returns 0 (the
+ * reference's unfused runner takes its score matrix from the plugin workspace, qkvToContextPlugin.cpp:430-438).
  *
  * Layouts (ref: plugin/bertQKVToContextPlugin/README.md:26-30, mhaRunner.cu:550-552, 1006, 1171):
  *  - fixed  (cu_seqlens == NULL): qkv [S][B][N][3][d], out [S][B][N][d]; valid keys of sequence b
@@ -260,7 +259,7 @@ typedef struct bert_b200_mha_params
     float scale_softmax;
     float scale_bmm2;
     uint32_t* status_word;
-    void* workspace;         /* optional, see bert_b200_mha_workspace_size */
+    void* workspace;         /* not used (see bert_b200_mha_workspace_size) */
     int64_t workspace_bytes;
 } bert_b200_mha_params;
 
@@ -293,8 +292,8 @@ typedef struct bert_b200_attention_bnsd_params
 
 BERT_B200_API int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params const* params, void* stream);
 
-/* Bytes of `workspace` with which bert_b200_mha keeps this call on the tensor cores although S > 512; 0 when the
- * call does not need one (or would not use it). ref: UnfusedMHARunner::getWorkspaceSize (mhaRunner.cu:522). */
+/* Bytes of scratch memory bert_b200_mha wants in `workspace`: always 0. Kept so that callers written against the
+ * reference's runner interface have something to ask. ref: UnfusedMHARunner::getWorkspaceSize (mhaRunner.cu:522). */
 BERT_B200_API int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params);
 
 /* ------------------------------------------------------------------------------------------

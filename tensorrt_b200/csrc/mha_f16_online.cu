@@ -34,8 +34,6 @@
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM and reports through the status word.
 #include "sm100.cuh"
 
-#include <cstdlib>
-
 namespace b200
 {
 
@@ -72,7 +70,7 @@ struct OnlineArgs
     float scaleBmm1;
     uint32_t* statusWord;
     int32_t tilesPerUnit, chunks; // a work unit = (sequence, head, chunk of tilesPerUnit query tiles)
-    uint32_t staggerNs;           // start delay of stream 1
+    int32_t stepChunk, stepHead, stepB; // gridDim.x = stepChunk + chunks * (stepHead + N * stepB)
 };
 
 // [ Q slot 0 ][ Q slot 1 ][ 12 K/V stages ][ barriers ]
@@ -187,11 +185,43 @@ struct Walker
         }
     }
 
-    // returns whether the unit has work for the tensor pipeline (a query row and a valid key)
-    __device__ __forceinline__ bool getUnit(int32_t u, Unit& o) const
+    // The CTA's k-th unit is unit number blockIdx.x + k * gridDim.x = (sequence cb, head ch, chunk cc). Going to the
+    // next one adds the launch's precomputed decomposition of gridDim.x (no division on the way).
+    int32_t k, cb, ch, cc;
+
+    __device__ __forceinline__ void firstUnit()
+    {
+        unit = static_cast<int32_t>(blockIdx.x);
+        k = 0;
+        cc = unit % ap->chunks;
+        int32_t const i = unit / ap->chunks;
+        cb = i / ap->N;
+        ch = i - cb * ap->N;
+    }
+
+    __device__ __forceinline__ void stepUnit()
+    {
+        unit += static_cast<int32_t>(gridDim.x);
+        ++k;
+        cc += ap->stepChunk;
+        if (cc >= ap->chunks)
+        {
+            cc -= ap->chunks;
+            ++ch;
+        }
+        ch += ap->stepHead;
+        if (ch >= ap->N)
+        {
+            ch -= ap->N;
+            ++cb;
+        }
+        cb += ap->stepB;
+    }
+
+    // geometry of the current unit; returns whether it has work for the tensor pipeline (a query row and a valid key)
+    __device__ __forceinline__ bool geometry(Unit& o) const
     {
         int32_t wa, wb;
-        int32_t const k = (u - static_cast<int32_t>(blockIdx.x)) / static_cast<int32_t>(gridDim.x);
         if (k < kGeoEntries)
         {
             int2 const e = geo[k];
@@ -199,11 +229,9 @@ struct Walker
             wb = e.y;
         }
         else
-            fetch(*ap, u, wa, wb);
-        int32_t const chunk = u % ap->chunks;
-        int32_t const i = u / ap->chunks;
-        o.b = i / ap->N;
-        o.head = i - o.b * ap->N;
+            fetch(*ap, unit, wa, wb);
+        o.b = cb;
+        o.head = ch;
         if (ap->fixedLayout)
         {
             o.rowBase = 0;
@@ -218,17 +246,17 @@ struct Walker
         }
         o.nb = (o.len + kTile - 1) / kTile;
         int32_t const nq = (o.rows + kTile - 1) / kTile;
-        o.tBegin = chunk * ap->tilesPerUnit;
+        o.tBegin = cc * ap->tilesPerUnit;
         o.tEnd = min(nq, o.tBegin + ap->tilesPerUnit);
         return o.len > 0 && o.tBegin < o.tEnd;
     }
 
-    __device__ __forceinline__ bool seek(int32_t u)
+    // settles on the current unit or the first one after it that has work
+    __device__ __forceinline__ bool seek()
     {
-        while (u < numUnits && !getUnit(u, g))
-            u += gridDim.x;
-        unit = u;
-        if (u >= numUnits)
+        while (unit < numUnits && !geometry(g))
+            stepUnit();
+        if (unit >= numUnits)
             return false;
         t = g.tBegin;
         setSub();
@@ -250,7 +278,8 @@ struct Walker
     {
         n = 0;
         loadBase = 0;
-        return seek(blockIdx.x);
+        firstUnit();
+        return seek();
     }
 
     __device__ __forceinline__ bool next()
@@ -261,7 +290,10 @@ struct Walker
         {
             loadBase += 2u * static_cast<uint32_t>(g.nb);
             if (t == g.tEnd)
-                return seek(unit + gridDim.x);
+            {
+                stepUnit();
+                return seek();
+            }
             setSub();
         }
         return true;
@@ -540,9 +572,9 @@ __global__ void __maxnreg__(168)
             Walker z(args, geoTable);
             Unit g;
             int const chunks16 = args.d / 8;
-            for (int u = blockIdx.x; u < z.numUnits; u += gridDim.x)
+            for (z.firstUnit(); z.unit < z.numUnits; z.stepUnit())
             {
-                z.getUnit(u, g);
+                z.geometry(g);
                 if (g.len > 0 || g.tBegin >= g.tEnd)
                     continue;
                 int const q0 = g.tBegin * kTile, q1 = min(g.rows, g.tEnd * kTile);
@@ -558,11 +590,6 @@ __global__ void __maxnreg__(168)
         }
 
         TR_DECL(lane == 0 && (warp & 3) == 0 ? s : 7);
-        // The two streams share the exponential unit. Started together they stay in step - both in their exponentials
-        // (at half rate each), then both in the phases that do not use the unit; half a block apart, one stream's
-        // exponentials run under the other's loads, maxima and waits.
-        if (s == 1)
-            __nanosleep(args.staggerNs);
         Walker w(args, geoTable);
         bool active = w.begin() && (s == 0 || w.next());
         uint32_t blocks = 0; // key blocks this stream has completed: parity of sFull / pvDone
@@ -738,7 +765,7 @@ __global__ void __maxnreg__(168)
             }
             int const q = w.t * kTile + r;
             pending = true;
-            pendInv = 1.f / ((l0 + l1) + (l2 + l3));
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(pendInv) : "f"((l0 + l1) + (l2 + l3)));
             pendDst = nullptr;
             if (q < g.rows)
             {
@@ -806,14 +833,13 @@ int32_t launchOnline(CUtensorMap const (&maps)[3], OnlineArgs args, cudaStream_t
     int64_t const items = static_cast<int64_t>(args.B) * args.N;
     args.tilesPerUnit = chooseTilesPerUnit(items, nqMax, smCount());
     args.chunks = (nqMax + args.tilesPerUnit - 1) / args.tilesPerUnit;
-    {
-        char const* e = std::getenv("BERT_B200_MHA_STAGGER");
-        args.staggerNs = e ? static_cast<uint32_t>(std::atoi(e)) : 800u;
-    }
     int64_t const units = items * args.chunks;
     if (units > INT32_MAX)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: too many work units (%lld)", static_cast<long long>(units));
     int const grid = static_cast<int>(units < smCount() ? units : smCount());
+    args.stepChunk = grid % args.chunks;
+    args.stepHead = (grid / args.chunks) % args.N;
+    args.stepB = (grid / args.chunks) / args.N;
     cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, maps[0], maps[1], maps[2], args);
     if (le != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mhaOnlineF16Kernel: %s", cudaGetErrorString(le));
@@ -841,7 +867,7 @@ int32_t mhaOnlineF16(bert_b200_mha_params const& p, cudaStream_t stream)
     maps[1] = maps[0];
     maps[2] = maps[0];
     OnlineArgs const args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx,
-        p.scale_bmm1, p.status_word, 1, 1, 0};
+        p.scale_bmm1, p.status_word, 1, 1, 0, 0, 0};
     return launchOnline<false>(maps, args, stream);
 }
 
@@ -861,7 +887,7 @@ int32_t mhaOnlineF16Bnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t 
         if (st != BERT_B200_OK)
             return st;
     }
-    OnlineArgs const args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.status_word, 1, 1, 0};
+    OnlineArgs const args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.status_word, 1, 1, 0, 0, 0};
     return launchOnline<true>(maps, args, stream);
 }
 

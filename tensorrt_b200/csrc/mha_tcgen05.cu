@@ -1,10 +1,14 @@
-// Fused multi-head attention on the sm_100a tensor cores (head sizes 16, 32, 48, 64; sequence length <= 512),
-// FP16 and INT8, fixed [S,B,N,3,d], packed [total,N,3,d] and INT8 CHW32-interleaved layouts.
+// INT8 fused multi-head attention on the sm_100a tensor cores (head sizes 16, 32, 48, 64; sequence length <= 512),
+// fixed [S,B,N,3,d], packed [total,N,3,d] and INT8 CHW32-interleaved layouts, and the C entry points of both
+// attention kernels (FP16 runs the online-softmax kernel of mha_f16_online.cu).
 //
-// Replaces the precompiled fused attention kernels the reference launches through
-// FusedMHARunnerFP16/Int8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265), the head-size
-// padding copies (zeroPadding2d.cu:190-204: here the TMA unit zero-fills the channels beyond the head size) and, for
-// these shapes, the unfused cuBLAS + softmax path (mhaRunner.cu:533-601).
+// Replaces the precompiled fused INT8 attention kernels the reference launches through
+// FusedMHARunnerInt8[v2]::run (plugin/bertQKVToContextPlugin/mhaRunner.cu:835-860, 1127-1265) and the head-size
+// padding copies (zeroPadding2d.cu:190-204: here the TMA unit zero-fills the channels beyond the head size).
+//
+// The quantised probabilities P_q = rni(p / rowsum * scale_softmax) need the exact row maximum and the complete row
+// sum before the first of them can be formed, so the whole score row lives in TMEM (<= 512 keys) and the softmax makes
+// three sweeps over it; that is what keeps the result bit-identical with the reference's INT8 kernels.
 //
 // Persistent CTAs (one per SM) take (sequence, head) work items round-robin. Per item a CTA loops over the 128-query
 // tiles of the sequence, so that K and V are loaded once and the tensor pipe works on the next tile (of this item or
@@ -19,17 +23,15 @@
 //                 S_j = Q K_j^T           (128 x 128 per key block, accumulators in TMEM columns 128j..)
 //               (with a single key block per sequence warp 1 issues both and this warp idles).
 //   warps 2-17: softmax, four threads per query row (each owns 32 of every 128 key columns):
-//                 pass A  row maximum over all key blocks straight from TMEM,
-//                 pass B  p = exp2(x*scale*log2e - max) -> FP16 P_j into swizzled shared memory for the PV product
-//                         (INT8: exp values go back to TMEM, pass C quantises p/sum*scale_softmax to INT8 P_j),
-//                 epilogue O / rowsum (INT8: O * scale_bmm2, round, saturate) -> 128-bit global stores, deferred
-//                         until after pass A of the next tile.
+//                 pass A  row maximum over all key blocks straight from TMEM (integer maximum, no conversions),
+//                 pass B  p = exp2((x - max) * scale * log2e), row sum; the exponentials go back to TMEM,
+//                 pass C  P_q = rni(p / sum * scale_softmax) -> INT8 P_j into swizzled shared memory for the PV product,
+//                 epilogue O * scale_bmm2, round, saturate -> 128-bit global stores, deferred until after pass A of
+//                         the next tile.
 //               The passes loop over the key blocks (not unrolled): unrolled, the kernel was bound by instruction
 //               fetch (122 KB of text, 77 % instruction-cache hits).
-// The whole score row lives in TMEM, so the softmax uses the exact row maximum and never rescales O.
-// FP16 sequences beyond 512 keys (PARTIAL instantiation): the keys are cut into chunks of 384, every (sequence, head,
-// chunk) is a work item that leaves its unnormalised FP32 context rows and the row statistics in a workspace, and
-// mhaMergeKernel combines the chunks - numerically one softmax over all keys.
+// The kernel template also takes FP16 tensors (exact-maximum two-sweep form, P in shared memory); that instantiation
+// is not built.
 // Every wait is bounded (sm100.cuh); on expiry the CTA drains, frees TMEM, reports through the status word.
 #include "sm100.cuh"
 
@@ -42,7 +44,6 @@ namespace b200
 int32_t mhaSimt(bert_b200_mha_params const& p, cudaStream_t stream);
 int32_t mhaOnlineF16(bert_b200_mha_params const& p, cudaStream_t stream);
 int32_t mhaOnlineF16Bnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t stream);
-bool legacyF16Attention();
 
 namespace
 {
@@ -66,12 +67,6 @@ struct MhaArgs
     int32_t const* maskIdx;
     float scaleBmm1, scaleSoftmax, scaleBmm2;
     uint32_t* statusWord;
-    // Sequences longer than the score row that fits TMEM (PARTIAL kernels): the keys are cut into chunks of chunkKeys,
-    // every (sequence, head, chunk) is a work item that leaves its unnormalised context rows (FP32) and the row
-    // statistics (maximum in the log2 domain, sum of exponentials) here; mhaMergeKernel combines the chunks.
-    int32_t chunkKeys, numChunks;
-    float* partO;       // [chunk][row][head][64]
-    float2* partStats;  // [chunk][row][head]
 };
 
 template <typename T>
@@ -173,12 +168,12 @@ __device__ __forceinline__ void tmemStoreWait()
 // [128 tokens][32 B] (32-byte swizzle); the head dimension is covered by one MMA per sub-tile.
 // BNSD: Q, K and V are three separate [B][N][S][d] tensors (mapQkv, mapK, mapV) and the output is [B][N][S][d];
 // otherwise mapQkv covers the fused tensor and the other two maps are not used.
-template <typename T, bool IL, bool PARTIAL, bool BNSD>
+template <typename T, bool IL, bool BNSD>
 __global__ void __launch_bounds__(kMhaThreads, 1)
     mhaTcgen05Kernel(const __grid_constant__ CUtensorMap mapQkv, const __grid_constant__ CUtensorMap mapK,
         const __grid_constant__ CUtensorMap mapV, MhaArgs const args)
 {
-    static_assert(!BNSD || (!IL && !PARTIAL), "separate Q / K / V tensors: linear layout, S <= 512");
+    static_assert(!BNSD || !IL, "separate Q / K / V tensors: linear layout");
     using L = MhaSmem<T>;
     constexpr bool kInt8 = sizeof(T) == 1;
     static_assert(!IL || kInt8, "the interleaved layout is INT8 only");
@@ -198,19 +193,11 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     struct Item
     {
         int32_t b, head, rowBase, rows, len, nb, nq;
-        int32_t chunk, keyBase; // PARTIAL: which chunk of the keys, and its first key
     };
-    int const numItems = args.B * args.N * (PARTIAL ? args.numChunks : 1);
+    int const numItems = args.B * args.N;
     // Geometry of item i (uniform over the CTA; every role derives the same values). Returns whether the item has
     // work for the tensor pipeline (at least one query row and one valid key).
     auto getItem = [&](int i, Item& it) -> bool {
-        it.chunk = 0;
-        if (PARTIAL)
-        {
-            it.chunk = i % args.numChunks;
-            i /= args.numChunks;
-        }
-        it.keyBase = it.chunk * args.chunkKeys;
         it.b = i / args.N;
         it.head = i - it.b * args.N;
         if (args.fixedLayout)
@@ -225,8 +212,6 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             it.len = min(max(__ldg(args.cu + it.b + 1) - it.rowBase, 0), args.S);
             it.rows = it.len;
         }
-        if (PARTIAL)
-            it.len = min(max(it.len - it.keyBase, 0), args.chunkKeys); // this chunk's valid keys
         it.nb = (it.len + kKeyBlock - 1) / kKeyBlock; // key blocks
         it.nq = (it.rows + kQTile - 1) / kQTile;      // query tiles
         return it.rows > 0 && it.len > 0;
@@ -239,7 +224,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     };
 
     // The layout of shared memory and TMEM follows the longest sequence the launch admits.
-    int const nbMax = ((PARTIAL ? args.chunkKeys : args.S) + kKeyBlock - 1) / kKeyBlock;
+    int const nbMax = (args.S + kKeyBlock - 1) / kKeyBlock;
     // S > 384: the context accumulator has to share TMEM columns with the scores of key block 0
     bool const oAliasesScores = nbMax > 3;
     uint32_t const oCol = oAliasesScores ? 0u : kOColumn;
@@ -318,7 +303,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             for (int item = nextWork(blockIdx.x, it); item < numItems && ok; item = nextWork(item + gridDim.x, it))
             {
                 int32_t const rowK = args.fixedLayout ? 0 : it.rowBase;
-                int32_t const rowKv = rowK + it.keyBase; // first key of this item
+                int32_t const rowKv = rowK; // first key of this item
                 // linear: (channel, which of [N][3], batch, row). interleaved: (channel, row, 32-channel group, which of [3][N])
                 auto load = [&](uint8_t* dst, uint64_t* bar, int which, int32_t row) {
                     if (BNSD) // (channel, position, head, sequence) of the tensor `which` selects
@@ -610,16 +595,6 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
             mbarArrive(oFree);
             if (dst == nullptr)
                 return;
-            if (PARTIAL)
-            {
-                // unnormalised FP32 context of this chunk of the keys (dst points into args.partO)
-                float4* const d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    d4[g] = make_float4(__uint_as_float(x[4 * g]), __uint_as_float(x[4 * g + 1]), __uint_as_float(x[4 * g + 2]),
-                        __uint_as_float(x[4 * g + 3]));
-                return;
-            }
             if (kInt8)
             {
                 float const s2 = args.scaleBmm2;
@@ -673,19 +648,6 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 return static_cast<T*>(args.out)
                     + ((static_cast<int64_t>(it.head) * (args.d / 32) + grp) * args.total + it.rowBase + q) * 32;
             };
-            // PARTIAL: row `q` of this item in the [chunk][row][head] arrays of the partial results
-            int64_t const partRows = args.fixedLayout ? static_cast<int64_t>(args.S) * args.B : args.total;
-            auto partIndex = [&](int q) -> int64_t {
-                int64_t const rr = args.fixedLayout ? static_cast<int64_t>(q) * args.B + it.b : static_cast<int64_t>(it.rowBase) + q;
-                return (it.chunk * partRows + rr) * args.N + it.head;
-            };
-            if (PARTIAL && !work)
-            {
-                // no valid key in this chunk: it takes no part in the merge (sum 0)
-                for (int q = threadIdx.x - 64; q < it.rows; q += kSoftmaxThreads)
-                    args.partStats[partIndex(q)] = make_float2(-INFINITY, 0.f);
-                continue;
-            }
             if (!work)
             {
                 // no valid key: every probability is zero and so is the context row
@@ -883,13 +845,10 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
                 }
                 sBits ^= (1u << nb) - 1u; // every block of this tile used its sFull / pReady phase
                 int const q = t * kQTile + r;
-                if (PARTIAL && sub == 0 && q < it.rows)
-                    args.partStats[partIndex(q)] = make_float2(mOff, sum);
                 // this thread's 16 of the 64 context columns; columns >= d are the zero padding
                 T* const dst = q >= it.rows || sub * 16 >= args.d
                     ? nullptr
-                    : (PARTIAL ? reinterpret_cast<T*>(args.partO + partIndex(q) * kHeadSize + sub * 16)
-                               : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16));
+                    : (IL ? outPtrIl(q, sub >> 1) + (sub & 1) * 16 : outRow(q) + sub * 16);
                 ++tiles;
                 if (deferEpilogue)
                 {
@@ -925,64 +884,7 @@ __global__ void __launch_bounds__(kMhaThreads, 1)
     }
 }
 
-constexpr int kChunkKeys = 3 * kKeyBlock; // PARTIAL kernels: keys per chunk (the score columns that leave room for O)
-
-// Bytes of [chunks][rows][heads] x (64 FP32 context values + float2 statistics).
-inline int64_t partialBytes(bert_b200_mha_params const& p)
-{
-    int64_t const chunks = (p.S + kChunkKeys - 1) / kChunkKeys;
-    int64_t const rows = p.cu_seqlens ? p.total : static_cast<int64_t>(p.S) * p.B;
-    return chunks * rows * p.num_heads * (kHeadSize * 4 + 8);
-}
-
-// out[row][head][:d] = sum_c w_c O_c / sum_c w_c l_c with w_c = 2^(m_c - max_c m_c): the chunks of the keys combined
-// exactly as one softmax over all keys. One thread per (row, head, 8 channels).
-__global__ void __launch_bounds__(256) mhaMergeKernel(int64_t const rowsHeads, int32_t const numChunks, int32_t const d,
-    float const* __restrict__ partO, float2 const* __restrict__ partStats, __half* __restrict__ out)
-{
-    int const groups = d / 8;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < rowsHeads * groups;
-         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-    {
-        int64_t const rh = i / groups;
-        int const g = static_cast<int>(i - rh * groups);
-        float m = -INFINITY;
-        for (int c = 0; c < numChunks; ++c)
-        {
-            float2 const st = partStats[c * rowsHeads + rh];
-            if (st.y > 0.f)
-                m = fmaxf(m, st.x);
-        }
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        float l = 0.f;
-        for (int c = 0; c < numChunks; ++c)
-        {
-            float2 const st = partStats[c * rowsHeads + rh];
-            if (st.y > 0.f) // a chunk without valid keys has written no context
-            {
-                float const w = exp2f(st.x - m);
-                l = fmaf(w, st.y, l);
-                float4 const* o = reinterpret_cast<float4 const*>(partO + (c * rowsHeads + rh) * kHeadSize + g * 8);
-                float4 const a = o[0], b = o[1];
-                acc[0] = fmaf(w, a.x, acc[0]);
-                acc[1] = fmaf(w, a.y, acc[1]);
-                acc[2] = fmaf(w, a.z, acc[2]);
-                acc[3] = fmaf(w, a.w, acc[3]);
-                acc[4] = fmaf(w, b.x, acc[4]);
-                acc[5] = fmaf(w, b.y, acc[5]);
-                acc[6] = fmaf(w, b.z, acc[6]);
-                acc[7] = fmaf(w, b.w, acc[7]);
-            }
-        }
-        float const inv = l > 0.f ? 1.f / l : 0.f; // no valid key at all: zero row
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            acc[j] *= inv;
-        *reinterpret_cast<uint4*>(out + rh * d + g * 8) = packHalf8(acc);
-    }
-}
-
-template <typename T, bool IL, bool PARTIAL = false>
+template <typename T, bool IL>
 int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
 {
     using L = MhaSmem<T>;
@@ -1017,37 +919,21 @@ int32_t launchMha(bert_b200_mha_params const& p, cudaStream_t stream)
         if (st != BERT_B200_OK)
             return st;
     }
-    int const nbMax = ((PARTIAL ? kChunkKeys : p.S) + kKeyBlock - 1) / kKeyBlock;
+    int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
     int const smem = L::dynamicBytes(nbMax);
-    auto kernel = mhaTcgen05Kernel<T, IL, PARTIAL, false>;
+    auto kernel = mhaTcgen05Kernel<T, IL, false>;
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mha: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     MhaArgs args{p.B, p.S, p.num_heads, p.total, p.head_size, fixedLayout ? 1 : 0, p.out, p.cu_seqlens, p.mask_idx, p.scale_bmm1,
-        p.scale_softmax, p.scale_bmm2, p.status_word, 0, 1, nullptr, nullptr};
-    int64_t const rows = fixedLayout ? static_cast<int64_t>(p.S) * p.B : p.total;
-    if (PARTIAL)
-    {
-        args.chunkKeys = kChunkKeys;
-        args.numChunks = (p.S + kChunkKeys - 1) / kChunkKeys;
-        args.partO = static_cast<float*>(p.workspace);
-        args.partStats = reinterpret_cast<float2*>(args.partO + args.numChunks * rows * p.num_heads * kHeadSize);
-    }
+        p.scale_softmax, p.scale_bmm2, p.status_word};
     // one persistent CTA per SM (512 TMEM columns and most of the shared memory each), items dealt round-robin
-    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B * args.numChunks;
+    int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
     int const grid = static_cast<int>(items < smCount() ? items : smCount());
     cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, map, map, map, args);
     if (le != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "mhaTcgen05Kernel: %s", cudaGetErrorString(le));
-    int32_t const st = checkLaunch("mhaTcgen05Kernel");
-    if (!PARTIAL || st != BERT_B200_OK)
-        return st;
-    int64_t const work = rows * p.num_heads * (p.head_size / 8);
-    int64_t const want = (work + 255) / 256;
-    int const mergeGrid = static_cast<int>(want < smCount() * 8ll ? want : smCount() * 8ll);
-    mhaMergeKernel<<<mergeGrid, 256, 0, stream>>>(rows * p.num_heads, args.numChunks, p.head_size, args.partO, args.partStats,
-        static_cast<__half*>(p.out));
-    return checkLaunch("mhaMergeKernel");
+    return checkLaunch("mhaTcgen05Kernel");
 }
 
 // Separate Q, K, V tensors of shape [B][N][S][d] (the operand layout of TensorRT's attention layer), output
@@ -1072,12 +958,12 @@ int32_t launchMhaBnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t str
     }
     int const nbMax = (p.S + kKeyBlock - 1) / kKeyBlock;
     int const smem = L::dynamicBytes(nbMax);
-    auto kernel = mhaTcgen05Kernel<T, false, false, true>;
+    auto kernel = mhaTcgen05Kernel<T, false, true>;
     cudaError_t const e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "attention_bnsd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     MhaArgs args{p.B, p.S, p.num_heads, 0, p.head_size, 1, p.out, nullptr, p.kv_lengths, p.scale_bmm1, p.scale_softmax,
-        p.scale_bmm2, p.status_word, 0, 1, nullptr, nullptr};
+        p.scale_bmm2, p.status_word};
     int64_t const items = static_cast<int64_t>(p.num_heads) * p.B;
     int const grid = static_cast<int>(items < smCount() ? items : smCount());
     cudaError_t const le = launchDependent(kernel, dim3(grid), dim3(kMhaThreads), smem, stream, maps[0], maps[1], maps[2], args);
@@ -1088,15 +974,6 @@ int32_t launchMhaBnsd(bert_b200_attention_bnsd_params const& p, cudaStream_t str
 
 } // namespace
 
-// Development switch: BERT_B200_MHA_F16=legacy keeps FP16 on the whole-row kernel of this file.
-bool legacyF16Attention()
-{
-    static int const on = [] {
-        char const* e = std::getenv("BERT_B200_MHA_F16");
-        return (e != nullptr && e[0] == 'l') ? 1 : 0;
-    }();
-    return on != 0;
-}
 } // namespace b200
 
 using namespace b200;
@@ -1114,17 +991,17 @@ extern "C" int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params cons
     B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "attention_bnsd: type_id %d", p.type_id);
     if (p.head_size > kHeadSize || p.head_size % 16 != 0)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: head sizes 16, 32, 48 and 64, got %d", p.head_size);
-    if (p.S > kMaxBlocks * kKeyBlock && (p.type_id == BERT_B200_INT8 || legacyF16Attention()))
+    if (p.S > kMaxBlocks * kKeyBlock && p.type_id == BERT_B200_INT8)
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "attention_bnsd: INT8 takes S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
     B200_REQUIRE(aligned16(p.q) && aligned16(p.k) && aligned16(p.v) && aligned16(p.out),
         "attention_bnsd: q, k, v and out must be 16-byte aligned");
     auto s = static_cast<cudaStream_t>(stream);
-    if (p.type_id == BERT_B200_FP16 && !legacyF16Attention())
+    if (p.type_id == BERT_B200_FP16)
     {
         B200_REQUIRE(p.scale_bmm1 > 0.f, "attention_bnsd: scale_bmm1 must be positive");
         return mhaOnlineF16Bnsd(p, s);
     }
-    return p.type_id == BERT_B200_FP16 ? launchMhaBnsd<__half>(p, s) : launchMhaBnsd<int8_t>(p, s);
+    return launchMhaBnsd<int8_t>(p, s);
 }
 
 extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* stream)
@@ -1142,22 +1019,18 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
     if (p.type_id == BERT_B200_FP32)
         return mhaSimt(p, s);
     B200_REQUIRE(p.type_id == BERT_B200_FP16 || p.type_id == BERT_B200_INT8, "mha: type_id %d", p.type_id);
+    B200_REQUIRE(!p.interleaved || (p.type_id == BERT_B200_INT8 && p.cu_seqlens != nullptr),
+        "mha: the interleaved (CHW32) layout needs INT8 and the packed (cu_seqlens) form");
     bool const headOk = p.head_size <= kHeadSize && p.head_size % 16 == 0 && (!p.interleaved || p.head_size % 32 == 0);
     bool const lengthOk = p.S <= kMaxBlocks * kKeyBlock;
-    if (headOk && p.type_id == BERT_B200_FP16 && !p.interleaved && p.scale_bmm1 > 0.f && !legacyF16Attention())
+    if (headOk && p.type_id == BERT_B200_FP16 && !p.interleaved && p.scale_bmm1 > 0.f)
     {
         B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
         return mhaOnlineF16(p, s);
     }
     // Outside the tensor-core kernel's shapes FP16 takes the SIMT kernel, like the reference's unfused runner
     // (qkvToContextPlugin.cpp:335-341, 522-531); INT8 has no such path there either (qkvToContextPlugin.cpp:530).
-    if (headOk && !lengthOk && p.type_id == BERT_B200_FP16 && p.workspace != nullptr && p.workspace_bytes >= partialBytes(p))
-    {
-        // longer than the score row that fits TMEM: chunks of the keys through the same kernel, then a merge
-        B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out) && aligned16(p.workspace), "mha: qkv, out and workspace must be 16-byte aligned");
-        return launchMha<__half, false, true>(p, s);
-    }
-    if ((!headOk || !lengthOk) && p.type_id == BERT_B200_FP16)
+    if (p.type_id == BERT_B200_FP16) // heads wider than 64 or not a multiple of 16 (or a non-positive scale)
         return mhaSimt(p, s);
     if (!headOk)
         B200_FAIL(BERT_B200_NOT_SUPPORTED,
@@ -1166,20 +1039,12 @@ extern "C" int32_t bert_b200_mha(bert_b200_mha_params const* params, void* strea
         B200_FAIL(BERT_B200_NOT_SUPPORTED, "mha: INT8 takes S <= %d, got %d", kMaxBlocks * kKeyBlock, p.S);
     B200_REQUIRE(aligned16(p.qkv) && aligned16(p.out), "mha: qkv and out must be 16-byte aligned");
     if (p.interleaved)
-    {
-        B200_REQUIRE(p.type_id == BERT_B200_INT8 && p.cu_seqlens != nullptr,
-            "mha: the interleaved (CHW32) layout needs INT8 and the packed (cu_seqlens) form");
         return launchMha<int8_t, true>(p, s);
-    }
-    if (p.type_id == BERT_B200_FP16)
-        return launchMha<__half, false>(p, s);
     return launchMha<int8_t, false>(p, s);
 }
 
 extern "C" int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params)
 {
-    if (params == nullptr || params->type_id != BERT_B200_FP16 || params->interleaved || params->S <= kMaxBlocks * kKeyBlock
-        || params->head_size > kHeadSize || params->head_size % 16 != 0 || params->B < 0 || params->num_heads <= 0)
-        return 0;
-    return partialBytes(*params);
+    (void) params; // no attention kernel of this library needs scratch memory
+    return 0;
 }

@@ -770,30 +770,18 @@ public:
         }
         return STATUS_SUCCESS;
     }
-    // Workspace of the fixed-length versions: the lengths recovered from a packed mask, then - FP16 beyond 512 tokens -
-    // the per-chunk partial results of the attention kernel (the reference's unfused runner keeps its score matrix
-    // there, qkvToContextPlugin.cpp:430-438).
+    // Workspace of the fixed-length versions: the lengths recovered from a packed mask. (The reference's unfused runner
+    // also keeps its score matrix there, qkvToContextPlugin.cpp:430-438; these kernels need no scratch memory.)
     static int64_t maskBytes(int64_t b)
     {
         return (b * 4 + 255) / 256 * 256;
-    }
-    int64_t partialBytes(int64_t s, int64_t b) const
-    {
-        bert_b200_mha_params q{};
-        q.type_id = type;
-        q.B = static_cast<int32_t>(b);
-        q.S = static_cast<int32_t>(s);
-        q.num_heads = numHeads;
-        q.head_size = headSize;
-        return bert_b200_mha_workspace_size(&q);
     }
     size_t getWorkspaceSize(DynamicPluginTensorDesc const* in, int32_t nbInputs, DynamicPluginTensorDesc const*, int32_t) const noexcept override
     {
         if (kind != QkvKind::kFixed || !in || nbInputs < 1)
             return 0;
         int64_t const b = in[0].max.d[BDIM] > 0 ? in[0].max.d[BDIM] : 1;
-        int64_t const s = in[0].max.d[SDIM] > 0 ? in[0].max.d[SDIM] : 1;
-        return static_cast<size_t>((hasMask ? maskBytes(b) : 0) + partialBytes(s, b));
+        return static_cast<size_t>(hasMask ? maskBytes(b) : 0);
     }
     int32_t enqueue(PluginTensorDesc const* inDesc, PluginTensorDesc const* outDesc, void const* const* inputs,
         void* const* outputs, void* workspace, cudaStream_t stream) noexcept override
@@ -869,12 +857,6 @@ public:
                         p.mask_idx = static_cast<int32_t const*>(inputs[1]);
                     }
                 }
-            }
-            if (kind == QkvKind::kFixed && workspace != nullptr)
-            {
-                // what getWorkspaceSize asked for beyond the lengths (for the maximum shape, so it holds this one)
-                p.workspace = static_cast<uint8_t*>(workspace) + (hasMask ? maskBytes(p.B) : 0);
-                p.workspace_bytes = partialBytes(p.S, p.B);
             }
             return abiStatus(bert_b200_mha(&p, stream), "mha");
         }

@@ -58,14 +58,10 @@ def test_attention_workspace_and_separate_tensor_entry_validation():
 
     m = _lib.MhaParams()
     m.type_id, m.B, m.S, m.num_heads, m.head_size = 1, 4, 1024, 16, 64
-    # fixed layout: 3 chunks of 384 keys x (S * B) rows x heads x (64 FP32 + two FP32 statistics)
-    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 3 * 1024 * 4 * 16 * (64 * 4 + 8)
-    m.S = 512
-    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 0       # fits the tensor memory: no workspace
+    # no attention kernel needs scratch memory: FP16 streams the key blocks of long sequences through tensor memory
+    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 0
     m.S, m.type_id = 1024, 2
-    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 0       # INT8 has no long-sequence path
-    m.type_id, m.head_size = 1, 80
-    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 0       # SIMT path: no workspace
+    assert _lib.lib.bert_b200_mha_workspace_size(C.byref(m)) == 0
     assert _lib.lib.bert_b200_mha_workspace_size(None) == 0
 
     a = _lib.AttentionBnsdParams()
@@ -73,8 +69,10 @@ def test_attention_workspace_and_separate_tensor_entry_validation():
     a.type_id, a.B, a.S, a.num_heads, a.head_size = 1, 1, 128, 2, 64
     assert _lib.lib.bert_b200_attention_bnsd(C.byref(a), None) == 2 and b"null" in _lib.lib.bert_b200_last_error()
     a.q = a.k = a.v = a.out = C.c_void_p(0x1000)
-    a.S = 600
-    assert _lib.lib.bert_b200_attention_bnsd(C.byref(a), None) == 3      # BERT_B200_NOT_SUPPORTED
+    a.S, a.type_id = 600, 2
+    assert _lib.lib.bert_b200_attention_bnsd(C.byref(a), None) == 3      # BERT_B200_NOT_SUPPORTED: INT8 beyond 512 keys
+    a.type_id = 1
+    assert _lib.lib.bert_b200_attention_bnsd(C.byref(a), None) == 2 and b"scale_bmm1" in _lib.lib.bert_b200_last_error()
     a.S, a.head_size = 128, 40
     assert _lib.lib.bert_b200_attention_bnsd(C.byref(a), None) == 3
     a.head_size, a.type_id = 64, 0

@@ -213,10 +213,10 @@ def test_mha_int8_small_heads(cuda, d, interleaved):
     _assert_int8_attention(out, ref)
 
 
-@pytest.mark.parametrize("S,d", [(40, 80), (64, 24), (700, 64), (1100, 128)])
+@pytest.mark.parametrize("S,d", [(40, 80), (64, 24), (700, 72), (1100, 128)])
 def test_mha_fp16_outside_tensor_core_shapes(cuda, S, d):
-    """Heads wider than 64 or not a multiple of 16, sequences beyond 512: FP16 I/O through the SIMT kernel (the
-    shapes the reference gives to its unfused runner); INT8 is refused there, as in the reference."""
+    """Heads wider than 64 or not a multiple of 16: FP16 I/O through the SIMT kernel (shapes the reference gives to
+    its unfused runner); INT8 is refused there, as in the reference."""
     import tensorrt_b200 as T
 
     rng = np.random.default_rng(S + d)
@@ -235,8 +235,9 @@ def test_mha_fp16_outside_tensor_core_shapes(cuda, S, d):
 @pytest.mark.parametrize("S,d", [(513, 64), (700, 64), (1100, 32), (1536, 64), (2000, 48)])
 @pytest.mark.parametrize("packed", [False, True])
 def test_mha_fp16_long_sequences_on_tensor_cores(cuda, S, d, packed):
-    """S > 512 with a workspace: chunks of 384 keys through the tensor-core kernel and a merge - one softmax over all
-    keys. Sequences shorter than a chunk boundary leave whole chunks without keys; one sequence has no key at all."""
+    """S > 512: up to six key blocks (S <= 768) stay resident for all query tiles of a sequence, longer sequences
+    stream their key blocks once per pair of query tiles - either way one softmax over all keys, no workspace.
+    Sequences shorter than the longest leave key blocks unused; one sequence has no key at all."""
     import tensorrt_b200 as T
 
     rng = np.random.default_rng(S + d + packed)
@@ -255,19 +256,35 @@ def test_mha_fp16_long_sequences_on_tensor_cores(cuda, S, d, packed):
         kw = dict(mask_idx=_t(lengths, cuda))
     q = _t(qkv, cuda)
     p = T._lib.MhaParams(1, B, S, N, d, int(lengths.sum()) if packed else 0, None, None, None, None, 0, 1.0, 1.0, 1.0, None, None, 0)
-    p.cu_seqlens = kw["cu_seqlens"].data_ptr() if packed else None
-    need = int(T._lib.lib.bert_b200_mha_workspace_size(T._lib.C.byref(p)))
-    rows = int(lengths.sum()) if packed else S * B
-    assert need == -(-S // 384) * rows * N * (64 * 4 + 8)
-    ws = torch.full((need,), 0xFF, dtype=torch.uint8, device=cuda)   # NaN patterns: nothing may leak from unwritten parts
-    out = T.mha(q, B, S, N, head_size=d, status=st, workspace=ws, **kw)
+    assert int(T._lib.lib.bert_b200_mha_workspace_size(T._lib.C.byref(p))) == 0
+    out = T.mha(q, B, S, N, head_size=d, status=st, **kw)
     assert int(st[0]) == 0
     assert out.shape == ref.shape
     ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
     assert ok, (worst, bad)
-    # the same call without (or with too small a) workspace takes the SIMT kernel: same result within tolerance
-    slow = T.mha(q, B, S, N, head_size=d, workspace=ws[: need // 2], **kw)
-    assert O.close_abs_or_rel(slow.cpu().numpy(), ref, 1e-2, 1e-2)[0]
+
+
+def test_mha_fp16_rescales_when_a_later_block_dominates(cuda):
+    """The online softmax keeps one running maximum per row and rescales the accumulated context when a later key
+    block exceeds it by more than the lazy threshold: keys whose scores grow block by block (by far more than 2^8)
+    exercise that path, keys that grow by less than the threshold the path that keeps the old maximum."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(99)
+    S, B, N, d = 512, 2, 2, 64
+    for step in (40.0, 3.0):                   # score offset per key block, in units of the logit
+        qkv = rng.standard_normal((S, B, N, 3, d)).astype(np.float32)
+        # make q . k / sqrt(d) rise by `step` per key block: one channel carries the ramp
+        qkv[:, :, :, 0, 0] = 8.0
+        qkv[:, :, :, 1, 0] = (np.arange(S) // 128)[:, None, None] * step
+        qkv = qkv.reshape(S, B, -1).astype(np.float16)
+        lengths = np.array([S, 300], dtype=np.int32)
+        ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+        st = _status(cuda)
+        out = T.mha(_t(qkv, cuda), B, S, N, mask_idx=_t(lengths, cuda), status=st)
+        assert int(st[0]) == 0
+        ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+        assert ok, (step, worst, bad)
 
 
 def _split_bnsd(qkv, S, B, N, d):
@@ -319,6 +336,11 @@ def test_attention_bnsd_int8(cuda):
     with pytest.raises(RuntimeError, match="S <= 512"):
         big = torch.zeros((1, 1, 600, 64), dtype=torch.int8, device=cuda)
         T.attention_bnsd(big, big, big)
+    # FP16 has no such limit
+    bigh = torch.randn((1, 2, 600, 64), device=cuda).half()
+    full = T.attention_bnsd(bigh, bigh, bigh).float()
+    p = torch.softmax(bigh.float() @ bigh.float().transpose(-1, -2) / 8.0, dim=-1) @ bigh.float()
+    assert (full - p).abs().max().item() < 2e-2
 
 
 @pytest.mark.parametrize("d", [32, 64])
