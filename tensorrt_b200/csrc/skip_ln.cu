@@ -349,6 +349,217 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
     }
 }
 
+// INT8 linear rows, packed arithmetic. The kernel above spends 21 instructions per element and is bound by issue slots at
+// 42 % of the memory bandwidth; this one needs about 10:
+//   * statistics on the raw bytes with dp4a: sum a, sum b, sum a^2, sum b^2, sum a*b are exact integers (five
+//     instructions per four elements) and give sum x and sum x^2 of x = dq_in a + dq_skip b in FP32; a bias adds
+//     2 sum t*bias, accumulated alongside in half2 (a term three orders of magnitude below sum x^2), and two constants;
+//   * the element-wise part in half2, two elements per instruction, like the reference's kernel
+//     (plugin/skipLayerNormPlugin/skipLayerNormKernel.cu:58-103): bytes -> FP16 through the exponent of 1024 (PRMT),
+//     dequantise, (+ bias,) one fused multiply-add for gamma (x - mean) rsigma + beta, already scaled to the INT8 grid
+//     and shifted to [0, 1] so that the instruction's own saturation is the clamp, one more to round (adding 1408 leaves
+//     the integer in the low byte);
+//   * gamma, beta (pre-scaled) and bias sit as half2 tables in shared memory, built once per CTA (no per-row parameter
+//     conversions); the lanes of a row add their integer sums with redux.sync.
+// Every value is within 1 LSB of the exact result (the FP16 steps add up to a few tenths of an LSB at most).
+template <int CPL, int WPR, bool HAS_BIAS>
+__global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t const ld, int64_t const rows,
+    int8_t const* __restrict__ in, int8_t const* __restrict__ skip, __half const* __restrict__ beta,
+    __half const* __restrict__ gamma, __half const* __restrict__ bias, int8_t* __restrict__ out, float const dqIn,
+    float const dqSkip, float const qScale, float const eps)
+{
+    constexpr int E = 16;
+    constexpr int kRowsPerCta = kWarpsPerCta / WPR;
+    __shared__ float2 red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
+    int turn = 0;
+
+    int const lane = threadIdx.x & 31;
+    int const warp = threadIdx.x >> 5;
+    int const rowInCta = warp / WPR;
+    int const wInRow = warp % WPR;
+    int const chunksPerRow = ld / E;
+    float const rld = 1.f / static_cast<float>(ld);
+
+    // sums the per-warp values of the WPR warps that share a row (the values are warp totals already)
+    auto rowCombine = [&](float a, float b) -> float2 {
+        if (WPR == 1)
+            return make_float2(a, b);
+        float2* const slot = red[rowInCta][turn];
+        turn ^= 1;
+        if (lane == 0)
+            slot[wInRow] = make_float2(a, b);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + rowInCta), "n"(WPR * 32) : "memory");
+        float2 t = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < WPR; ++w)
+        {
+            t.x += slot[w].x;
+            t.y += slot[w].y;
+        }
+        return t;
+    };
+
+    // ---- gamma, (beta * q_scale + 128) / 255 and bias as half2 tables in shared memory, built once per CTA: a lane
+    //      reads the eight half2 of a chunk with two 128-bit loads per table and row (no conversions in the row loop,
+    //      and no registers held across it: three CTAs fit an SM) ----
+    extern __shared__ uint4 paramSmem[];
+    __half2* const gTab = reinterpret_cast<__half2*>(paramSmem);
+    __half2* const bqTab = gTab + ld / 2;
+    __half2* const biTab = bqTab + ld / 2;
+    float sBias = 0.f, sBias2 = 0.f;
+    for (int p = threadIdx.x; p < ld / 2; p += kThreads)
+    {
+        float2 const g = __half22float2(reinterpret_cast<__half2 const*>(gamma)[p]);
+        float2 const bt = __half22float2(reinterpret_cast<__half2 const*>(beta)[p]);
+        gTab[p] = __floats2half2_rn(g.x, g.y);
+        bqTab[p] = __floats2half2_rn(fmaf(bt.x, qScale, 128.f) * (1.f / 255.f), fmaf(bt.y, qScale, 128.f) * (1.f / 255.f));
+        if (HAS_BIAS)
+            biTab[p] = reinterpret_cast<__half2 const*>(bias)[p];
+    }
+    __syncthreads();
+    if (HAS_BIAS)
+    {
+        // sum and sum of squares of the bias over the whole row, by every warp (the statistics use the bias as the
+        // element-wise part sees it: FP16)
+        for (int p = lane; p < ld / 2; p += 32)
+        {
+            float2 const bs = __half22float2(biTab[p]);
+            sBias += bs.x + bs.y;
+            sBias2 = fmaf(bs.x, bs.x, fmaf(bs.y, bs.y, sBias2));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+        {
+            sBias += __shfl_xor_sync(0xffffffffu, sBias, o);
+            sBias2 += __shfl_xor_sync(0xffffffffu, sBias2, o);
+        }
+    }
+    __half2 const dqIn2 = __float2half2_rn(dqIn), dqSkip2 = __float2half2_rn(dqSkip);
+    // the integer sums are weighted with the scales the element-wise part actually multiplies by
+    float const dqInH = __low2float(dqIn2), dqSkipH = __low2float(dqSkip2);
+    __half2 const kMagic = __float2half2_rn(1152.f); // 1024 + 128: exponent byte 0x64 over (byte ^ 0x80)
+    gridDependencyLaunch();
+    gridDependencyWait(); // the rows come from the previous kernel of the stream
+
+    int64_t const rowsRounded = (rows + kRowsPerCta - 1) / kRowsPerCta * kRowsPerCta;
+    for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded;
+         row += static_cast<int64_t>(gridDim.x) * kRowsPerCta)
+    {
+        bool const rowOk = row < rows;
+        uint4 a[CPL], b[CPL];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            bool const ok = rowOk && c < chunksPerRow;
+            a[i] = ok ? ldgStream(in + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+            b[i] = ok ? ldgStream(skip + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+        }
+        int32_t sa = 0, sb = 0, saa = 0, sbb = 0, sab = 0;
+        __half2 cross0 = __float2half2_rn(0.f), cross1 = cross0;
+        __half2 x2[CPL][8];
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
+            uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
+            __half2 bi2[8];
+            if (HAS_BIAS)
+            {
+                int const c = min((i * WPR + wInRow) * 32 + lane, chunksPerRow - 1); // chunks beyond the row carry zeros
+                *reinterpret_cast<uint4*>(&bi2[0]) = *reinterpret_cast<uint4 const*>(biTab + c * 8);
+                *reinterpret_cast<uint4*>(&bi2[4]) = *reinterpret_cast<uint4 const*>(biTab + c * 8 + 4);
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+                int32_t const ia = static_cast<int32_t>(aw[w]), ib = static_cast<int32_t>(bw[w]);
+                sa = __dp4a(ia, 0x01010101, sa);
+                sb = __dp4a(ib, 0x01010101, sb);
+                saa = __dp4a(ia, ia, saa);
+                sbb = __dp4a(ib, ib, sbb);
+                sab = __dp4a(ia, ib, sab);
+                uint32_t const ua = aw[w] ^ 0x80808080u, ub = bw[w] ^ 0x80808080u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    uint32_t const am = __byte_perm(ua, 0x64646464u, h == 0 ? 0x5140 : 0x7362);
+                    uint32_t const bm = __byte_perm(ub, 0x64646464u, h == 0 ? 0x5140 : 0x7362);
+                    __half2 const fa = __hsub2(*reinterpret_cast<__half2 const*>(&am), kMagic);
+                    __half2 const fb = __hsub2(*reinterpret_cast<__half2 const*>(&bm), kMagic);
+                    __half2 t = __hfma2(dqIn2, fa, __hmul2(dqSkip2, fb));
+                    if (HAS_BIAS)
+                    {
+                        __half2 const bs = bi2[2 * w + h];
+                        if (h == 0)
+                            cross0 = __hfma2(t, bs, cross0);
+                        else
+                            cross1 = __hfma2(t, bs, cross1);
+                        t = __hadd2(t, bs);
+                    }
+                    x2[i][2 * w + h] = t;
+                }
+            }
+        }
+        // row sums: exact integers over the warp, the small cross term in FP32
+        sa = __reduce_add_sync(0xffffffffu, sa);
+        sb = __reduce_add_sync(0xffffffffu, sb);
+        saa = __reduce_add_sync(0xffffffffu, saa);
+        sbb = __reduce_add_sync(0xffffffffu, sbb);
+        sab = __reduce_add_sync(0xffffffffu, sab);
+        float s1 = fmaf(dqInH, static_cast<float>(sa), dqSkipH * static_cast<float>(sb));
+        float s2 = fmaf(dqInH * dqInH, static_cast<float>(saa),
+            fmaf(dqSkipH * dqSkipH, static_cast<float>(sbb), 2.f * dqInH * dqSkipH * static_cast<float>(sab)));
+        if (HAS_BIAS)
+        {
+            float2 const c0 = __half22float2(cross0), c1 = __half22float2(cross1);
+            float cr = (c0.x + c0.y) + (c1.x + c1.y);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                cr += __shfl_xor_sync(0xffffffffu, cr, o);
+            s2 = fmaf(2.f, cr, s2);
+        }
+        float2 const sums = rowCombine(s1, s2);
+        float const mu = (sums.x + sBias) * rld;
+        float const rsigma = rsqrtf(fmaxf(fmaf(sums.y + sBias2, rld, -mu * mu), 0.f) + eps);
+        // (gamma (x - mu) rsigma + beta) q_scale, shifted and scaled to [0, 1] <-> [-128, 127]
+        __half2 const k1 = __float2half2_rn(rsigma * qScale * (1.f / 255.f));
+        __half2 const negMu = __float2half2_rn(-mu);
+        __half2 const k255 = __float2half2_rn(255.f), k1408 = __float2half2_rn(1408.f);
+#pragma unroll
+        for (int i = 0; i < CPL; ++i)
+        {
+            int const c = (i * WPR + wInRow) * 32 + lane;
+            if (rowOk && c < chunksPerRow)
+            {
+                uint4 o;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                __half2 g2[8], bq2[8];
+                *reinterpret_cast<uint4*>(&g2[0]) = *reinterpret_cast<uint4 const*>(gTab + c * 8);
+                *reinterpret_cast<uint4*>(&g2[4]) = *reinterpret_cast<uint4 const*>(gTab + c * 8 + 4);
+                *reinterpret_cast<uint4*>(&bq2[0]) = *reinterpret_cast<uint4 const*>(bqTab + c * 8);
+                *reinterpret_cast<uint4*>(&bq2[4]) = *reinterpret_cast<uint4 const*>(bqTab + c * 8 + 4);
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                {
+                    uint32_t r[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                    {
+                        __half2 const c1 = __hmul2(g2[2 * w + h], k1);
+                        __half2 const c0 = __hfma2(c1, negMu, bq2[2 * w + h]);
+                        __half2 const v = __hfma2_sat(c1, x2[i][2 * w + h], c0);
+                        __half2 const q = __hfma2(v, k255, k1408); // round to nearest even; the integer sits in the low byte
+                        r[h] = *reinterpret_cast<uint32_t const*>(&q);
+                    }
+                    ow[w] = __byte_perm(r[0], r[1], 0x6420);
+                }
+                stgStream(out + row * ld + c * E, o);
+            }
+        }
+    }
+}
+
 // INT8 CHW32-interleaved tokens: element (token t, channel c) lives at ((c/32)*total + t)*32 + c%32.
 // A CTA owns 8 consecutive tokens, i.e. 256 contiguous bytes in each of the ld/32 channel groups.
 // Thread -> 16-byte unit u = tid%16 (token u/2, half u%2) of channel group (tid/16 + 16*i), so a
@@ -486,10 +697,16 @@ __global__ void __launch_bounds__(kThreads) skipLnInterleavedKernel(int32_t cons
     }
 }
 
-inline int gridFor(int64_t ctasNeeded, int ctasPerSm)
+// Grid for a grid-stride loop over `groups` units of work with at most ctasPerSm CTAs per SM: every CTA takes the same
+// number of passes (the last pass may be short for a few), instead of a grid of exactly the cap in which some CTAs
+// make one pass more than the others and the rest idle meanwhile (24576 rows: 7 passes against 6 for a third of them).
+inline int gridFor(int64_t groups, int ctasPerSm)
 {
     int64_t const cap = static_cast<int64_t>(smCount()) * ctasPerSm;
-    return static_cast<int>(ctasNeeded < cap ? (ctasNeeded > 0 ? ctasNeeded : 1) : cap);
+    if (groups <= cap)
+        return static_cast<int>(groups > 0 ? groups : 1);
+    int64_t const passes = (groups + cap - 1) / cap;
+    return static_cast<int>((groups + passes - 1) / passes);
 }
 
 template <typename T, int CPL, int WPR>
@@ -559,6 +776,19 @@ int32_t launchDqq(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* i
     __half const* beta, __half const* gamma, __half const* bias, int8_t* out, float dqIn, float dqSkip, float qScale)
 {
     int const rowsPerCta = kWarpsPerCta / WPR;
+    if (CPL <= 2)
+    {
+        // tables built once per CTA: few CTAs with many rows each
+        int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 3);
+        size_t const smem = static_cast<size_t>(ld) * 2 * 3; // three half2 tables of ld / 2 entries
+        if (bias)
+            launchDependent(skipLnDqqPackedKernel<CPL <= 2 ? CPL : 1, WPR, true>, dim3(grid), dim3(kThreads), smem, stream, ld, rows, in,
+                skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+        else
+            launchDependent(skipLnDqqPackedKernel<CPL <= 2 ? CPL : 1, WPR, false>, dim3(grid), dim3(kThreads), smem, stream, ld, rows, in,
+                skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+        return checkLaunch("skipLnDqqPackedKernel");
+    }
     int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 8);
     if (bias)
         launchDependent(skipLnDqqKernel<CPL, WPR, true>, dim3(grid), dim3(kThreads), 0, stream, ld, rows, in, skip, beta, gamma, bias,
