@@ -2,19 +2,24 @@
 """BERT-large S=384 encoder throughput on B200 through the sm_100a plugin kernels.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype int8|fp16] [--impl b200|reference]
+    python bench.py --sweep                      # kernel sweep against the rooflines (one GPU), one JSON object
 
 One step = one forward pass of the 24-layer BERT-large encoder (EmbLayerNorm + 24 x [FC(QKV), fused MHA, FC,
-SkipLayerNorm, FC+GELU, FC, SkipLayerNorm]) over a batch of 64 synthetic sequences of 384 tokens per GPU.
-Prints ONE JSON line (rank 0). With N > 1 (launched by torchrun, one rank per GPU) every rank runs its own
-64 sequences (weak scaling, no collective on the data path); the time is the max over ranks.
+SkipLayerNorm, FC+GELU, FC, SkipLayerNorm]) over ONE global batch of 64 synthetic sequences of 384 tokens, split
+evenly over the N GPUs (64 / 32 / 16 / 8 sequences per GPU: strong scaling, no collective on the data path; the time
+is the max over ranks). Prints ONE JSON line (rank 0). Sub-objects of that line: `weak` (64 sequences per GPU, N > 1
+only), `fp16` (the same network in FP16), `config4` (packed variable-length batch of 256 sequences, lengths uniform
+in [32, 384], sharded by token count), `plugin_path` (the FP16 network driven through the IPluginV3 enqueue() calls
+instead of the C++ layer loop, one GPU only).
 
-`--impl reference` times the CPU restatement of the reference math (oracle/cpu_encoder.py, FP32, all host
-cores) on a bounded sample of the same workload: the reference plugins have no CPU implementation and neither
-TensorRT nor ONNX-Runtime is installed, so this port is the CPU arm.
+`--impl reference` times the CPU restatement of the reference math (oracle/cpu_encoder.py, FP32, all host cores) on a
+bounded sample of the same workload: the reference plugins have no CPU implementation and neither TensorRT nor
+ONNX-Runtime is installed, so this port is the CPU arm.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes as C
 import json
 import os
 import statistics
@@ -28,6 +33,10 @@ sys.path.insert(0, ROOT)
 LAYERS, HIDDEN, HEADS, FFN, SEQ, BATCH = 24, 1024, 16, 4096, 384, 64
 FLOPS_PER_SEQ_LAYER_FC = 24 * HIDDEN * HIDDEN * SEQ      # 2*S*(3E*E + E*E + 2*E*F), F = 4E
 FLOPS_PER_SEQ_LAYER_MHA = 4 * SEQ * SEQ * HIDDEN
+L2_BYTES = 126e6
+# dram__bytes_read.sum + dram__bytes_write.sum per FC launch at 64 sequences per GPU, mean of the four shapes of a
+# layer, from one `ncu --set full` capture of a 2-layer run (a profiler reading: it cannot be measured by the bench)
+FC_DRAM_BYTES_PER_LAUNCH_INT8 = 69.4e6
 
 
 def _peaks():
@@ -59,7 +68,7 @@ class ClockSampler(threading.Thread):
                 self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
                 r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
                 self.reasons.update(k for k, bit in names.items() if r & bit)
-                time.sleep(0.01)
+                time.sleep(0.005)
         except Exception as e:  # NVML missing: report that instead of clocks
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
@@ -68,9 +77,6 @@ class ClockSampler(threading.Thread):
         self.join(timeout=2)
         med = statistics.median(self.samples) if self.samples else None
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
-
-
-FC_DRAM_BYTES_PER_LAUNCH_INT8 = 69.4e6  # dram__bytes_read.sum + dram__bytes_write.sum, mean of QKV / out / FFN1 / FFN2
 
 
 def cpu_forward_rate(batch_hint=None, budget_s=15.0, steps=1, warmup=0):
@@ -102,9 +108,11 @@ def cpu_forward_rate(batch_hint=None, budget_s=15.0, steps=1, warmup=0):
 
 def _workload(dtype):
     if dtype == "int8":
-        return ("BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, batch 64 per GPU "
-                "(BASELINE configs[2]); explicit INT8 with amax/127 scales from one seeded calibration batch")
-    return "BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, batch 64 per GPU, FP16"
+        return ("BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, one global batch of 64 "
+                "split evenly over the GPUs (benchmark configuration 3); explicit INT8 with amax/127 scales from one seeded "
+                "calibration batch")
+    return ("BERT-large encoder, 24 layers, hidden 1024, 16 heads x 64, FFN 4096, seq 384, one global batch of 64 split "
+            "evenly over the GPUs, FP16")
 
 
 def run_reference(args):
@@ -121,8 +129,8 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": f"BERT-large s384 {args.dtype.upper()} encoder sequences/s", "value": value, "unit": "seq/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": _workload(args.dtype), "layers": LAYERS, "per_gpu_batch": BATCH, "seq_len": SEQ,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": _workload(args.dtype), "layers": LAYERS, "global_batch": BATCH, "seq_len": SEQ,
                    "cpu_arm": "bounded sample of the workload on the host cores"},
         "cpu_baseline": {"value": value, "unit": "seq/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "seq/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -131,29 +139,40 @@ def run_reference(args):
     emit(line)
 
 
-def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, profile_steps=3):
-    """Device-resident timing: W warm-up forwards, then K forwards between two CUDA events on the launching stream.
-    Afterwards `profile_steps` more forwards run with every kernel bracketed by CUDA events (same inputs, same stream)
-    to split the step by kernel kind; those instrumented steps are not part of the reported step time."""
-    import ctypes as C
+def _events():
+    import torch
 
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def time_forward(fn, steps, warmup, world, dist):
+    """W warm-up calls, then K calls between two CUDA events on the launching stream; barrier + synchronize on both
+    sides when several ranks run."""
     import torch
 
     for _ in range(warmup):
-        enc.forward(ids, seg, cu, SEQ, out=out)
+        fn()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = _events()
     e0.record()
     for _ in range(steps):
-        enc.forward(ids, seg, cu, SEQ, out=out)
+        fn()
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
     if world > 1:
         dist.barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def kernel_breakdown(enc, ids, seg, cu, out, profile_steps=3):
+    """`profile_steps` forwards with every kernel bracketed by CUDA events (same inputs, same stream) to split the
+    step by kernel kind. The brackets cost the overlap of consecutive kernels (programmatic dependent launch), so the
+    per-kind times add up to more than the step; they are not part of the reported step time."""
+    import torch
+
     kind_ms, kind_n = (C.c_float * 5)(), (C.c_int32 * 5)()
     enc.enable_timing(True)
     enc.forward(ids, seg, cu, SEQ, out=out)  # creates the events
@@ -162,7 +181,7 @@ def time_encoder(enc, ids, seg, cu, steps, warmup, world, dist, out, profile_ste
         enc.forward(ids, seg, cu, SEQ, out=out)
         enc.read_timing(kind_ms, kind_n)  # synchronises, then adds this forward's per-kind times
     enc.enable_timing(False)
-    return ms, [v / profile_steps for v in kind_ms], [v // profile_steps for v in kind_n]
+    return [v / profile_steps for v in kind_ms], [v // profile_steps for v in kind_n]
 
 
 def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
@@ -182,7 +201,7 @@ def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = _events()
     e0.record()
     for i in range(steps):
         enc.forward_host_async(ids_h, seg_h, cu_h, SEQ, outs_dev[i & 1], outs_h[i & 1], copy_stream, i & 1)
@@ -197,7 +216,132 @@ def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
     return ms, h2d, d2h
 
 
+def probe_mma_rate(T, type_id, k_blocks=4000):
+    """TOP/s the tensor pipes sustain for the FC kernels' MMA shape with operands resident in shared memory."""
+    import torch
+
+    v = C.c_float(0)
+    T._lib.check(T._lib.lib.bert_b200_probe_mma_rate(C.c_void_p(torch.cuda.current_stream().cuda_stream), type_id, k_blocks,
+                                                     None, C.byref(v)), "probe_mma_rate")
+    return float(v.value)
+
+
+def rotating(make, nbytes_each, min_total=2.5 * L2_BYTES):
+    """Enough independent copies of a kernel's operands that consecutive launches never find theirs in the L2."""
+    n = max(2, int(min_total // max(nbytes_each, 1)) + 1)
+    return [make() for _ in range(min(n, 64))]
+
+
+def time_rotating(launch, sets, iters=None):
+    import torch
+
+    iters = iters or max(20, 2 * len(sets))
+    for i in range(len(sets)):
+        launch(sets[i])
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    for i in range(iters):
+        launch(sets[i % len(sets)])
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def isolated_skip_ln(T, dev, tokens, ld, int8, bias=True):
+    """SkipLayerNorm (+ bias) alone at `tokens` x `ld`, operands rotated beyond the L2: GB/s of algorithmic traffic."""
+    import torch
+
+    g = torch.ones(ld, device=dev).half()
+    b = torch.zeros(ld, device=dev).half()
+    elem = 1 if int8 else 2
+
+    def make():
+        if int8:
+            x = torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8)
+            return x, torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8), torch.empty_like(x)
+        x = torch.randn(tokens, ld, device=dev).half()
+        return x, torch.randn(tokens, ld, device=dev).half(), torch.empty_like(x)
+
+    sets = rotating(make, 3 * tokens * ld * elem)
+    if int8:
+        ms = time_rotating(lambda s: T.skip_layer_norm_dqq(s[0], s[1], g, b, b if bias else None, 0.02, 0.02, 40.0, out=s[2]), sets)
+    else:
+        ms = time_rotating(lambda s: T.skip_layer_norm(s[0], s[1], g, b, bias=b if bias else None, out=s[2]), sets)
+    return ms, 3 * tokens * ld * elem / (ms * 1e-3) / 1e9
+
+
+class PluginEncoder:
+    """The FP16 network wired from plugin OBJECTS in the fixed [S, B, E] layout, driven through their
+    IPluginV3OneRuntime::enqueue (the C harness stands in for TensorRT): per layer FC -> QKVToContext v4 -> FC ->
+    SkipLayerNorm v5 -> FC(+GELU) -> FC -> SkipLayerNorm v5, what a TensorRT engine built from these plugins executes."""
+
+    def __init__(self, params, batch, dev):
+        import numpy as np
+        import torch
+
+        from tensorrt_b200 import plugin_harness as H
+
+        self.H, self.B, self.dev = H, batch, dev
+        E, N, F = params.hidden, params.heads, params.ffn
+        f32 = lambda t: t.detach().float().cpu().numpy()
+        FC, QKV, SKIP = "CustomFCPluginDynamic", "CustomQKVToContextPluginDynamic", "CustomSkipLayerNormPluginDynamic"
+        self.layers = []
+        for lp in params.layers:
+            fc = lambda w, out, extra=(): H.Plugin(FC, "2", [("out_dims", out), ("type_id", 1), ("W", f32(w).ravel())] + list(extra)).attach()
+            ln = lambda g, b, bias: H.Plugin(SKIP, "5", [("type_id", 1), ("ld", E), ("beta", f32(b)), ("gamma", f32(g)),
+                                                         ("bias", f32(bias))]).attach()
+            self.layers.append((
+                fc(lp.w_qkv, 3 * E, [("bias", f32(lp.b_qkv))]),
+                H.Plugin(QKV, "4", [("type_id", 1), ("hidden_size", E), ("num_heads", N), ("has_mask", 1)]).attach(),
+                fc(lp.w_out, E), ln(lp.ln1_gamma, lp.ln1_beta, lp.b_out),
+                fc(lp.w_ffn1, F, [("bias", f32(lp.b_ffn1)), ("activation", 1)]), fc(lp.w_ffn2, E),
+                ln(lp.ln2_gamma, lp.ln2_beta, lp.b_ffn2)))
+            if not all(p.ok for p in self.layers[-1]):
+                raise RuntimeError("plugin creation failed")
+        d = lambda c: H.make_desc((SEQ, batch, c, 1, 1), H.HALF)
+        self.d = {c: d(c) for c in (E, 3 * E, F)}
+        self.dmask = H.make_desc((batch, 1), H.INT32)
+        buf = lambda c: torch.empty((SEQ, batch, c), dtype=torch.float16, device=dev)
+        self.qkv, self.ctx, self.ao, self.h1, self.f1, self.f2 = buf(3 * E), buf(E), buf(E), buf(E), buf(F), buf(E)
+        self.x = [buf(E), buf(E)]
+        self.mask_idx = torch.full((batch, 1), SEQ, dtype=torch.int32, device=dev)
+        self.ws = torch.empty(4096, dtype=torch.uint8, device=dev)
+        self.E, self.F = E, F
+        self.np = np
+
+    def forward(self, x0):
+        import torch
+
+        s = torch.cuda.current_stream().cuda_stream
+        E, F, d = self.E, self.F, self.d
+
+        def enq(p, ins, outs, ind, outd, ws=None):
+            st = p.enqueue(ind, outd, [t.data_ptr() for t in ins], [t.data_ptr() for t in outs], ws.data_ptr() if ws is not None else None, s)
+            if st != 0:
+                raise RuntimeError(f"plugin enqueue returned {st}")
+
+        x = x0
+        for i, (qkv_p, att_p, out_p, ln1_p, f1_p, f2_p, ln2_p) in enumerate(self.layers):
+            y = self.x[i & 1]
+            enq(qkv_p, [x], [self.qkv], [d[E]], [d[3 * E]])
+            enq(att_p, [self.qkv, self.mask_idx], [self.ctx], [d[3 * E], self.dmask], [d[E]], self.ws)
+            enq(out_p, [self.ctx], [self.ao], [d[E]], [d[E]])
+            enq(ln1_p, [self.ao, x], [self.h1], [d[E], d[E]], [d[E]])
+            enq(f1_p, [self.h1], [self.f1], [d[E]], [d[F]])
+            enq(f2_p, [self.f1], [self.f2], [d[F]], [d[E]])
+            enq(ln2_p, [self.f2, self.h1], [y], [d[E], d[E]], [d[E]])
+            x = y
+        return x
+
+    def close(self):
+        for layer in self.layers:
+            for p in layer:
+                p.close()
+
+
 def run_b200(args):
+    import numpy as np
     import torch
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -216,16 +360,26 @@ def run_b200(args):
         dist.init_process_group("nccl", device_id=dev)
 
     import tensorrt_b200 as T
-    from tensorrt_b200 import synthetic
+    from tensorrt_b200 import sharding, synthetic
 
     peaks = _peaks()
     params = synthetic.make_params(LAYERS, HIDDEN, HEADS, FFN, seed=0, device=dev)
-    ids, seg, cu, _ = synthetic.make_inputs(BATCH, SEQ, seed=100 + rank, device=dev)
-    total = ids.shape[0]
-    out = torch.empty((total, HIDDEN), dtype=torch.float16, device=dev)
+    # the global batch (same on every rank) and this rank's contiguous share of it
+    g_ids, g_seg, _, _ = synthetic.make_inputs(BATCH, SEQ, seed=100, device=dev)
+    mine = sharding.shard_even(BATCH, world, rank)
+    my_b = len(mine)
+
+    def slice_batch(lo, n):
+        ids = g_ids[lo * SEQ:(lo + n) * SEQ].contiguous()
+        seg = g_seg[lo * SEQ:(lo + n) * SEQ].contiguous()
+        cu = torch.arange(0, (n + 1) * SEQ, SEQ, dtype=torch.int32, device=dev)
+        return ids, seg, cu
+
+    ids, seg, cu = slice_batch(mine.start, my_b)
+    w_ids, w_seg, w_cu = slice_batch(0, BATCH)     # 64 sequences per GPU: the weak-scaling side number
+    out = torch.empty((BATCH * SEQ, HIDDEN), dtype=torch.float16, device=dev)
 
     enc16 = T.BertEncoder(params, T.FP16, dev)
-    results = {}
     encs = {"fp16": enc16}
     if args.dtype == "int8" or args.both:
         # explicit INT8: per-tensor scales amax/127 from one seeded calibration batch of the same distribution
@@ -235,70 +389,112 @@ def run_b200(args):
         encs["int8"] = T.BertEncoder(params, T.INT8, dev)
     order = [args.dtype] + (["fp16" if args.dtype == "int8" else "int8"] if args.both else [])
 
+    def reduce_max(*vals):
+        if world == 1:
+            return list(vals)
+        t = torch.tensor(vals, dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    results = {}
     sampler = ClockSampler(local) if rank == 0 else None
+    clocks = None
     for name in order:
         enc = encs[name]
         if sampler and name == args.dtype:
             sampler.start()
-        ms, kind_ms, kind_n = time_encoder(enc, ids, seg, cu, args.steps, args.warmup, world, dist, out)
+        my_out = out[:my_b * SEQ]
+        ms = time_forward(lambda: enc.forward(ids, seg, cu, SEQ, out=my_out), args.steps, args.warmup, world, dist)
         if sampler and name == args.dtype:
             clocks = sampler.stop()
         status = enc.status_word()
-        ms_e2e, h2d, d2h = time_e2e(enc, ids, seg, cu, max(3, args.steps // 2), 3, world, dist, out)
+        kind_ms, kind_n = kernel_breakdown(enc, ids, seg, cu, my_out)
+        ms_e2e, h2d, d2h = time_e2e(enc, ids, seg, cu, args.steps, 3, world, dist, my_out)
+        ms_weak = None
         if world > 1:
-            t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms, ms_e2e = t.tolist()
-        results[name] = dict(ms=ms, ms_e2e=ms_e2e, h2d=h2d, d2h=d2h, kind_ms=kind_ms, kind_n=kind_n, status=status,
+            ms_weak = time_forward(lambda: enc.forward(w_ids, w_seg, w_cu, SEQ, out=out), args.steps, args.warmup, world, dist)
+            ms, ms_e2e, ms_weak = reduce_max(ms, ms_e2e, ms_weak)
+        results[name] = dict(ms=ms, ms_e2e=ms_e2e, ms_weak=ms_weak, h2d=h2d, d2h=d2h, kind_ms=kind_ms, kind_n=kind_n, status=status,
                              launches=enc.launches_per_forward)
+
+    # ---- config 4: packed variable-length batch, lengths uniform in [32, 384] (seed 1), B = 256, token-balanced shards ----
+    lengths_all = np.random.default_rng(1).integers(32, 385, size=256).astype(np.int32)
+    shards = sharding.shard_by_tokens(lengths_all, world)
+    my_len = torch.from_numpy(lengths_all[shards[rank]])
+    c4_cu = torch.zeros(len(my_len) + 1, dtype=torch.int32)
+    c4_cu[1:] = torch.cumsum(my_len, 0)
+    c4_total = int(c4_cu[-1])
+    gen = torch.Generator(device="cpu").manual_seed(4 + rank)
+    c4_ids = torch.randint(0, 30522, (c4_total,), generator=gen, dtype=torch.int32).to(dev)
+    c4_seg = torch.randint(0, 2, (c4_total,), generator=gen, dtype=torch.int32).to(dev)
+    c4_cu = c4_cu.to(dev)
+    c4_out = torch.empty((c4_total, HIDDEN), dtype=torch.float16, device=dev)
+    c4 = {}
+    for name in order:
+        enc = encs[name]
+        c4_ms = time_forward(lambda: enc.forward(c4_ids, c4_seg, c4_cu, SEQ, out=c4_out), max(5, args.steps // 2), 3, world, dist)
+        (c4_ms,) = reduce_max(c4_ms)
+        c4[name] = c4_ms
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
+    # measured tensor-pipe rates for the FC MMA shape (rank 0, after the timed regions)
+    mma_rate = {"int8": probe_mma_rate(T, T.INT8), "fp16": probe_mma_rate(T, T.FP16)}
+
     def roofline(name):
         r = results[name]
         fc_ms, fc_n = r["kind_ms"][1], r["kind_n"][1]
-        flops_per_forward = BATCH * LAYERS * FLOPS_PER_SEQ_LAYER_FC
+        flops_per_forward = my_b * LAYERS * FLOPS_PER_SEQ_LAYER_FC
         achieved = flops_per_forward / (fc_ms * 1e-3) / 1e12 if fc_ms > 0 else None
         if name == "int8":
-            peak, src = 2 * peaks["tc_sustained"], f"2 x {peaks['source']} bf16 sustained (no measured INT8 figure)"
+            peak = mma_rate["int8"]
+            src = ("measured in this run: tcgen05.mma.cta_group::2.kind::i8 256x256x32 chains on all SM pairs, operands "
+                   "resident in shared memory (bert_b200_probe_mma_rate)")
         else:
             peak, src = peaks["tc_sustained"], f"{peaks['source']} bf16 sustained"
-        # DRAM bytes per FC launch from one `ncu --set full` capture of the four launches of a layer at this batch
-        # (profiles/fc_pair_int8_bert_large_layer_fullset.md); no capture exists for FP16 or other batch sizes
-        traffic = FC_DRAM_BYTES_PER_LAUNCH_INT8 if (name == "int8" and BATCH == 64) else None
+        traffic = FC_DRAM_BYTES_PER_LAUNCH_INT8 if (name == "int8" and my_b == 64) else None
         return {"bound": "tensor", "kernel": "fcTcgen05PairKernel (4 FC shapes per layer)", "achieved": achieved, "peak": peak,
                 "unit": "TFLOP/s" if name == "fp16" else "TOP/s", "frac": achieved / peak if achieved else None,
                 "traffic": traffic, "peak_source": src, "launches_per_step": fc_n,
-                "flops_per_launch_avg": flops_per_forward / max(fc_n, 1), "ms_per_launch_avg": fc_ms / max(fc_n, 1)}
+                "flops_per_launch_avg": flops_per_forward / max(fc_n, 1), "ms_per_launch_avg": fc_ms / max(fc_n, 1),
+                "mma_rate_probe": {"int8_tops": mma_rate["int8"], "fp16_tflops": mma_rate["fp16"]}}
 
     def breakdown(name):
         r = results[name]
         kinds = ("emb_layer_norm", "fc", "mha", "skip_layer_norm", "other")
         d = {k: {"ms_per_step": r["kind_ms"][i], "launches": r["kind_n"][i]} for i, k in enumerate(kinds)}
-        mha_flops = BATCH * LAYERS * FLOPS_PER_SEQ_LAYER_MHA
+        d["note"] = ("every launch bracketed by CUDA events in extra forwards: the brackets cost the overlap of consecutive "
+                     "kernels, so these times add up to more than ms_per_step")
+        mha_flops = my_b * LAYERS * FLOPS_PER_SEQ_LAYER_MHA
         if r["kind_ms"][2] > 0:
             d["mha"]["achieved_tflops"] = mha_flops / (r["kind_ms"][2] * 1e-3) / 1e12
+            d["mha"]["frac_of_tensor_peak"] = d["mha"]["achieved_tflops"] / (mma_rate["int8"] if name == "int8" else peaks["tc_sustained"])
         elem = 1 if name == "int8" else 2
-        ln_bytes = 2 * LAYERS * BATCH * SEQ * 3 * HIDDEN * elem
+        ln_bytes = 2 * LAYERS * my_b * SEQ * 3 * HIDDEN * elem
         if r["kind_ms"][3] > 0:
             d["skip_layer_norm"]["achieved_gbs"] = ln_bytes / (r["kind_ms"][3] * 1e-3) / 1e9
             d["skip_layer_norm"]["frac_of_hbm_peak"] = d["skip_layer_norm"]["achieved_gbs"] / peaks["hbm"]
+        # the same kernel alone at the step's shape, operands rotated beyond the L2 (no event between launches)
+        iso_ms, iso_gbs = isolated_skip_ln(T, dev, my_b * SEQ, HIDDEN, name == "int8")
+        d["skip_layer_norm"]["isolated"] = {"ms_per_launch": iso_ms, "achieved_gbs": iso_gbs, "frac_of_hbm_peak": iso_gbs / peaks["hbm"],
+                                            "rows": my_b * SEQ, "l2": "operand sets rotated over more than 2.5 x the 126 MB L2"}
         return d
 
     main = results[args.dtype]
     n = world
     line = {
-        "metric": f"BERT-large s384 {args.dtype.upper()} encoder sequences/s", "value": n * BATCH / (main["ms"] * 1e-3),
+        "metric": f"BERT-large s384 {args.dtype.upper()} encoder sequences/s", "value": BATCH / (main["ms"] * 1e-3),
         "unit": "seq/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms"],
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8" if args.dtype == "int8" else "f16",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8" if args.dtype == "int8" else "f16",
         "data": "synthetic",
         "config": {"workload": _workload(args.dtype),
-                   "layers": LAYERS, "per_gpu_batch": BATCH, "global_batch": n * BATCH, "seq_len": SEQ, "parallelism": f"dp{n} (batch sharding, no collective)",
-                   "l2": "working set per step (activations > 250 MB + weights > 300 MB) exceeds the 126 MB L2"},
-        "e2e": {"value": n * BATCH / (main["ms_e2e"] * 1e-3), "unit": "seq/s", "ms_per_step": main["ms_e2e"],
+                   "layers": LAYERS, "global_batch": BATCH, "per_gpu_batch": my_b, "seq_len": SEQ,
+                   "parallelism": f"dp{n} (one batch of {BATCH} split evenly, no collective)",
+                   "l2": "working set per step (activations + weights > 300 MB per GPU) exceeds the 126 MB L2"},
+        "e2e": {"value": BATCH / (main["ms_e2e"] * 1e-3), "unit": "seq/s", "ms_per_step": main["ms_e2e"],
                 "h2d_bytes_per_step": main["h2d"], "d2h_bytes_per_step": main["d2h"]},
         "gpu_launches": main["launches"] * args.steps,
         "launches_per_step": main["launches"],
@@ -307,11 +503,37 @@ def run_b200(args):
         "kernels": breakdown(args.dtype),
         "device_wait_status": main["status"],
     }
+    if n > 1:
+        line["weak"] = {"value": n * BATCH / (main["ms_weak"] * 1e-3), "unit": "seq/s", "ms_per_step": main["ms_weak"],
+                        "per_gpu_batch": BATCH, "scaling": "weak"}
     for name in order[1:]:
         r = results[name]
-        line[name] = {"value": n * BATCH / (r["ms"] * 1e-3), "unit": "seq/s", "ms_per_step": r["ms"],
-                      "e2e_value": n * BATCH / (r["ms_e2e"] * 1e-3), "roofline": roofline(name), "kernels": breakdown(name),
+        line[name] = {"value": BATCH / (r["ms"] * 1e-3), "unit": "seq/s", "ms_per_step": r["ms"],
+                      "e2e_value": BATCH / (r["ms_e2e"] * 1e-3), "roofline": roofline(name), "kernels": breakdown(name),
                       "device_wait_status": r["status"]}
+        if n > 1:
+            line[name]["weak_value"] = n * BATCH / (r["ms_weak"] * 1e-3)
+    tokens4 = int(lengths_all.sum())
+    line["config4"] = {
+        "workload": "BERT-large packed variable-length batch: 256 sequences, lengths uniform in [32, 384] (seed 1), "
+                    f"{tokens4} tokens, sequences assigned longest-first to the least-loaded GPU (benchmark configuration 4)",
+        "tokens": tokens4, "shard_tokens": [int(lengths_all[s].sum()) for s in shards],
+        **{name: {"seq_per_s": 256 / (c4[name] * 1e-3), "tokens_per_s": tokens4 / (c4[name] * 1e-3), "ms_per_step": c4[name]}
+           for name in order}}
+
+    if n == 1 and not args.no_extras:
+        # the FP16 network through the plugin objects' enqueue() (what a TensorRT engine built from them runs)
+        try:
+            pe = PluginEncoder(params, BATCH, dev)
+            x0 = torch.randn((SEQ, BATCH, HIDDEN), device=dev).half()
+            p_ms = time_forward(lambda: pe.forward(x0), max(5, args.steps // 2), 3, 1, None)
+            line["plugin_path"] = {"value": BATCH / (p_ms * 1e-3), "unit": "seq/s", "ms_per_step": p_ms, "dtype": "f16",
+                                   "enqueues_per_step": 7 * LAYERS,
+                                   "path": "IPluginV3OneRuntime::enqueue of FC v2 / QKVToContext v4 / SkipLayerNorm v5 objects, "
+                                           "fixed [S, B, E] layout, 24 layers (no embedding plugin in the loop)"}
+            pe.close()
+        except Exception as e:  # the plugin library needs the TensorRT headers at build time
+            line["plugin_path"] = {"unavailable": f"{type(e).__name__}: {e}"}
     if n == 1 and not args.no_cpu:
         b, times, cores = cpu_forward_rate(budget_s=15.0)
         line["cpu_baseline"] = {"value": b / times[0], "unit": "seq/s", "cores": cores, "kind": "port",
@@ -321,6 +543,120 @@ def run_b200(args):
     emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_sweep(args):
+    """Kernel sweep against the rooflines (benchmark configuration 5) on one GPU: fused attention as tensor throughput for
+    S in {128, 256, 384, 512}, SkipLayerNorm + bias as HBM GB/s for hidden in {768, 1024, 4096} x tokens 2^10 .. 2^20,
+    the embedding gather + LayerNorm (vocab 30522, hidden 1024) as GB/s; beside each the reference's own kernel from
+    oracle/_ref when that library has been built (tests' checker, timed here as the same-box bar)."""
+    import numpy as np
+    import torch
+
+    import tensorrt_b200 as T
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    ref = None
+    try:
+        from oracle import ref_lib
+
+        if ref_lib.available():
+            ref = ref_lib.RefLib()
+    except Exception:
+        ref = None
+    vp = C.c_void_p
+    res = {"peaks": {"hbm_gbs": peaks["hbm"], "bf16_tflops": peaks["tc"], "bf16_tflops_sustained": peaks["tc_sustained"],
+                     "source": peaks["source"],
+                     "int8_mma_tops_probe": probe_mma_rate(T, T.INT8), "fp16_mma_tflops_probe": probe_mma_rate(T, T.FP16)},
+           "reference_kernels": "oracle/_ref/libref_bert.so" if ref else None}
+    N, d = 16, 64
+    mha = []
+    for S in (128, 256, 384, 512):
+        tiles = -(-S // 128)
+        B = -(-4 * 148 // (N * tiles))          # smallest batch with B * 16 * ceil(S / 128) >= 4 * 148 query tiles
+        flops = 4 * S * S * d * N * B
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        x = torch.randn(S * B, 3 * N * d, device=dev)
+        amax = float(x.abs().max())
+        q16 = lambda: (x.half(), torch.empty(S * B, N * d, device=dev, dtype=torch.float16))
+        q8 = lambda: (torch.clamp(torch.round(x * (127 / amax)), -127, 127).to(torch.int8), torch.empty(S * B, N * d, device=dev, dtype=torch.int8))
+        s1 = (amax / 127) ** 2 * 0.125
+        row = {"S": S, "B": B, "heads": N, "head_size": d}
+        sets16, sets8 = rotating(q16, S * B * 4 * N * d * 2), rotating(q8, S * B * 4 * N * d)
+        ms = time_rotating(lambda s: T.mha(s[0], B, S, N, cu_seqlens=cu), sets16)
+        row["fp16"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_of_bf16_sustained": flops / ms / 1e9 / peaks["tc_sustained"],
+                       "hbm_cap_tflops": (S / 2) * peaks["hbm"] / 1e3}
+        ms = time_rotating(lambda s: T.mha(s[0], B, S, N, cu_seqlens=cu, scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=1.0 / 64), sets8)
+        row["int8"] = {"ms": ms, "tops": flops / ms / 1e9, "frac_of_int8_probe": flops / ms / 1e9 / res["peaks"]["int8_mma_tops_probe"]}
+        if ref is not None:
+            def ref16(s):
+                ref.lib.ref_fmha_v2(None, 1, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
+                                    C.c_float(0.125), C.c_float(1.0), C.c_float(1.0))
+
+            def ref8(s):
+                ref.lib.ref_fmha_v2(None, 2, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
+                                    C.c_float(s1), C.c_float(127.0), C.c_float(1.0 / 64))
+            try:
+                row["fp16"]["reference_tflops"] = flops / time_rotating(ref16, sets16) / 1e9
+                row["int8"]["reference_tops"] = flops / time_rotating(ref8, sets8) / 1e9
+            except Exception as e:
+                row["reference_error"] = str(e)
+        mha.append(row)
+        del sets16, sets8
+    res["mha"] = mha
+
+    ln = []
+    for ld in (768, 1024, 4096):
+        for e in range(10, 21, 2):
+            tokens = 1 << e
+            row = {"hidden": ld, "tokens": tokens}
+            ms, gbs = isolated_skip_ln(T, dev, tokens, ld, False)
+            row["fp16"] = {"ms": ms, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+            ms, gbs = isolated_skip_ln(T, dev, tokens, ld, True)
+            row["int8"] = {"ms": ms, "gbs": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"]}
+            if ref is not None and tokens == 1 << 16:
+                g = torch.ones(ld, device=dev).half()
+                sets = rotating(lambda: (torch.randn(tokens, ld, device=dev).half(), torch.randn(tokens, ld, device=dev).half(),
+                                         torch.empty(tokens, ld, device=dev).half()), 6 * tokens * ld)
+                ms = time_rotating(lambda s: ref.lib.ref_skip_layer_norm(None, 1, ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()),
+                                                                         vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()), vp(g.data_ptr())), sets)
+                row["fp16"]["reference_gbs"] = 6 * tokens * ld / ms / 1e6
+                if ld != 4096:  # the reference's INT8 kernel exists for 768 and 1024 only
+                    sets = rotating(lambda: (torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8),
+                                             torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8),
+                                             torch.empty(tokens, ld, device=dev, dtype=torch.int8)), 3 * tokens * ld)
+                    ms = time_rotating(lambda s: ref.lib.ref_skip_layer_norm_dqq(None, ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()),
+                                                                                 vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()), vp(g.data_ptr()),
+                                                                                 C.c_float(0.02), C.c_float(0.02), C.c_float(40.0)), sets)
+                    row["int8"]["reference_gbs"] = 3 * tokens * ld / ms / 1e6
+            ln.append(row)
+    res["skip_layer_norm_bias"] = ln
+
+    # embedding gather + LayerNorm: vocab 30522, hidden 1024, FP16 tables; bytes = word row in + row out + two ids
+    E, vocab = 1024, 30522
+    word = (0.02 * torch.randn(vocab, E, device=dev)).half()
+    pos = (0.02 * torch.randn(512, E, device=dev)).half()
+    tok = (0.02 * torch.randn(2, E, device=dev)).half()
+    gam, bet = torch.ones(E, device=dev), torch.zeros(E, device=dev)
+    emb = []
+    for S, B in ((128, 32), (384, 64), (384, 512)):
+        sets = rotating(lambda: (torch.randint(0, vocab, (S, B), device=dev, dtype=torch.int32),
+                                 torch.randint(0, 2, (S, B), device=dev, dtype=torch.int32)), S * B * (2 * E * 2 + 8), min_total=0)
+        ms = time_rotating(lambda s: T.emb_layer_norm(s[0], s[1], word, pos, tok, gam, bet), sets, iters=40)
+        nbytes = S * B * (2 * E * 2 + 8)
+        row = {"S": S, "B": B, "tokens": S * B, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm"],
+               "note": "62 MB word table, random rows: every launch gathers different rows; the output (2 KB per token) is written once"}
+        if ref is not None:
+            outr = torch.empty(S, B, E, device=dev, dtype=torch.float16)
+            ms = time_rotating(lambda s: ref.lib.ref_emb_layer_norm(None, 1, E, B, S, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(bet.data_ptr()),
+                                                                    vp(gam.data_ptr()), vp(word.data_ptr()), vp(pos.data_ptr()), vp(tok.data_ptr()),
+                                                                    vocab, 2, vp(outr.data_ptr())), sets, iters=40)
+            row["reference_gbs"] = nbytes / ms / 1e6
+        emb.append(row)
+    res["emb_layer_norm"] = emb
+    emit({"sweep": res})
 
 
 _JSON_FD = None
@@ -356,13 +692,17 @@ def main():
     ap.add_argument("--both", action=argparse.BooleanOptionalAction, default=True,
                     help="also time the other precision and report it in a sub-object")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the plugin-path leg")
+    ap.add_argument("--sweep", action="store_true", help="kernel sweep against the rooflines instead of the encoder step")
     ap.add_argument("--layers", type=int, default=LAYERS, help="profiling captures only: fewer encoder layers")
-    ap.add_argument("--batch", type=int, default=BATCH, help="profiling captures only: sequences per GPU and step")
+    ap.add_argument("--batch", type=int, default=BATCH, help="profiling captures only: sequences in the global batch")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch)
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

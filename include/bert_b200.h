@@ -109,7 +109,8 @@ BERT_B200_API int32_t bert_b200_skip_layer_norm_interleaved_mtron(void* stream, 
 /*
  * Fixed-length: ids are [S,B] (S-major: token (s,b) at s*B+b); output [S,B,ld] in type_id
  * (0 or 1); tables in the output type; beta/gamma FP32. LayerNorm without epsilon.
- * A token whose word or segment id lies outside its table produces the row `beta`.
+ * A token whose word or segment id lies outside its table produces the row `beta`; pos_emb has pos_size rows and
+ * S > pos_size is refused (the reference kernel would read past the table).
  * Extension (not in the reference): if out_i8 != NULL the normalised row is also written
  * quantised, out_i8 = sat8(rni(y * q_scale)); pass NULL to get the reference behaviour.
  * ref: plugin/embLayerNormPlugin/embLayerNormKernel.cu:237-252 (embSkipLayerNorm<T>)
@@ -117,20 +118,22 @@ BERT_B200_API int32_t bert_b200_skip_layer_norm_interleaved_mtron(void* stream, 
 BERT_B200_API int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
     int32_t const* input_ids, int32_t const* token_ids, float const* beta, float const* gamma,
     void const* word_emb, void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size,
-    void* output, int8_t* out_i8, float q_scale);
+    int32_t pos_size, void* output, int8_t* out_i8, float q_scale);
 
 /*
  * Packed variable-length: ids are [total], sequence b owns tokens cu_seqlens[b]..cu_seqlens[b+1];
  * the position row is the index inside the sequence. `skip_out` (may be NULL) receives the
  * pre-LayerNorm sum (the "MTron" second output). `total` = cu_seqlens[B] must be given by the
- * caller (it sizes the grid); S is only an upper bound on the sequence length.
+ * caller (it sizes the grid); S is only an upper bound on the sequence length. A token whose position inside its
+ * sequence is not in [0, pos_size) - a sequence longer than the position table, a cu_seqlens that does not start at 0
+ * or decreases - produces the row `beta`, like a token with an id outside its table.
  * ref: plugin/embLayerNormPlugin/embLayerNormVarSeqlenKernelHFace.cu:105-118 (embSkipLayerNormHFace<T>)
  *      plugin/embLayerNormPlugin/embLayerNormVarSeqlenKernelMTron.cu:106-118 (embSkipLayerNormMTron<T>)
  */
 BERT_B200_API int32_t bert_b200_emb_layer_norm_var_seqlen(void* stream, int32_t type_id, int32_t ld, int32_t B,
     int32_t S, int32_t total, int32_t const* input_ids, int32_t const* token_ids, int32_t const* cu_seqlens,
     float const* beta, float const* gamma, void const* word_emb, void const* pos_emb, void const* tok_emb,
-    int32_t word_size, int32_t tok_size, void* output, void* skip_out, int8_t* out_i8, float q_scale);
+    int32_t word_size, int32_t tok_size, int32_t pos_size, void* output, void* skip_out, int8_t* out_i8, float q_scale);
 
 /*
  * mask_idx[b] = index of the first 0 in column b of the [S,B] int32 mask, S if there is none.
@@ -296,6 +299,25 @@ BERT_B200_API int32_t bert_b200_attention_bnsd(bert_b200_attention_bnsd_params c
  * reference's runner interface have something to ask. ref: UnfusedMHARunner::getWorkspaceSize (mhaRunner.cu:522). */
 BERT_B200_API int64_t bert_b200_mha_workspace_size(bert_b200_mha_params const* params);
 
+/*
+ * Self-test of the bounded device wait (no counterpart in the reference, whose kernels assert instead,
+ * plugin/vc/checkMacrosPlugin.cpp:95-113): launches one small kernel on `stream` in which the library's own wait
+ * routine waits on an mbarrier that nothing arrives at, with `limit_ns` (at most 100 ms) in place of the 2 s the
+ * kernels use. The kernel returns by itself; afterwards *status_word (device) holds the wait's code (1) and
+ * *completed (device, may be NULL) is 0. Asynchronous like the kernels; the context stays usable.
+ */
+BERT_B200_API int32_t bert_b200_selftest_wait_expiry(void* stream, int64_t limit_ns, uint32_t* status_word, uint32_t* completed);
+
+/*
+ * Measurement helper for roofline denominators (no counterpart in the reference): what the tensor pipes of the
+ * current GPU sustain for the MMA shape the FC kernels issue - every SM pair runs `k_blocks` x four
+ * tcgen05.mma.cta_group::2 of 256 x 256 x 32 bytes of K (type_id 2: INT8, 1: FP16) on operands resident in shared
+ * memory, nothing else running. Launches the probe twice on `stream` (warm-up, measurement), BLOCKS until it has
+ * finished and returns tera-operations per second in *tera_ops_host. status_word may be NULL.
+ */
+BERT_B200_API int32_t bert_b200_probe_mma_rate(void* stream, int32_t type_id, int32_t k_blocks, uint32_t* status_word,
+    float* tera_ops_host);
+
 /* ------------------------------------------------------------------------------------------
  * Whole-encoder driver (host layer loop over the kernels above)
  * ------------------------------------------------------------------------------------------ */
@@ -422,6 +444,8 @@ BERT_B200_API int32_t bert_b200_encoder_forward(bert_b200_encoder* enc, void* st
  * capture. All calls on a device share the one buffer, which still holds the previous call's intermediates: the
  * status word is re-zeroed at the start of every call and everything else is overwritten before it is read, but
  * two calls that overlap on the GPU (different streams, or different encoders) corrupt each other - serialise them.
+ * The device address is kept for the life of the process: an application that tears the device's primary context
+ * down (cudaDeviceReset) must reload the library before it uses this entry point again.
  */
 #define BERT_B200_STATIC_WORKSPACE_BYTES (16ll * 1024 * 1024)
 BERT_B200_API int64_t bert_b200_encoder_static_workspace_limit(void);

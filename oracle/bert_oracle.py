@@ -213,7 +213,7 @@ def skip_layer_norm_interleaved(x_il, skip_il, gamma, beta, dq_in, dq_skip, q_sc
 
 
 def gelu_erf(x: np.ndarray) -> np.ndarray:
-    """0.5 x (1 + erf(x / sqrt(2))) (BASELINE configs: 'FFN 3072 with erf-GELU')."""
+    """0.5 x (1 + erf(x / sqrt(2))) (the benchmark configurations' 'FFN 3072 with erf-GELU')."""
     from scipy.special import erf
 
     x = x.astype(np.float64)
@@ -233,7 +233,7 @@ def fc(a: np.ndarray, w_kn: np.ndarray, bias=None, activation: str | None = None
 
 def fc_int8(a_i8, w_kn_i8, alpha, bias=None, activation=None, out_inv_scale=None):
     """INT8 x INT8 -> INT32 (exact), then float: acc*alpha + bias, activation, optional requantisation
-    (BASELINE config 3: 'int8 x int8 -> int32 with the fp32 scale epilogue')."""
+    (benchmark configuration 3: 'int8 x int8 -> int32 with the fp32 scale epilogue')."""
     acc = a_i8.astype(np.float64) @ w_kn_i8.astype(np.float64)  # exact: |acc| < 2^53
     y = acc.astype(np.float32) * np.float32(alpha)
     y = y.astype(np.float64)
@@ -441,7 +441,7 @@ def quantize_weights(p: BertParams):
 
 def calibrate_int8(p: BertParams, ids, seg, cu, S):
     """Sets every activation scale to amax/127 of the FP32 forward on one calibration batch
-    (BASELINE config 3). Layer l's input scale equals layer l-1's output scale."""
+    (benchmark configuration 3). Layer l's input scale equals layer l-1's output scale."""
     quantize_weights(p)
     B = len(cu) - 1
     x, _ = emb_layer_norm_var_seqlen(ids, seg, cu, p.word_emb, p.pos_emb, p.tok_emb, p.emb_gamma, p.emb_beta)

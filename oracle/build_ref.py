@@ -18,7 +18,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
 LIB = OUT / "libref_bert.so"
-REF = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+# the TensorRT-OSS checkout: REFERENCE_ROOT, else a directory "reference" next to this repository
+REF = Path(os.environ.get("REFERENCE_ROOT") or HERE.parent.parent / "reference")
 
 PLUGIN_SOURCES = [
     "plugin/skipLayerNormPlugin/skipLayerNormKernel.cu",

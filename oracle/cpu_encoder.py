@@ -1,4 +1,4 @@
-"""FP32 PyTorch-CPU restatement of the BERT encoder forward (TEST / BASELINE INFRASTRUCTURE, not product).
+"""FP32 PyTorch-CPU restatement of the BERT encoder forward (TEST / CPU-BASELINE INFRASTRUCTURE, not product).
 
 Same operator order and math as oracle/bert_oracle.py (which cites the reference files), written with torch
 CPU tensor ops so that it can use every host core; bench.py times it as the CPU baseline ("port": the reference

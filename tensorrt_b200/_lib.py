@@ -66,8 +66,8 @@ SIGNATURES = {
     "bert_b200_skip_layer_norm_dqq": (i32, [vp, i32, i64, vp, vp, vp, vp, vp, vp, f32, f32, f32]),
     "bert_b200_skip_layer_norm_interleaved_hface": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, f32, f32, f32]),
     "bert_b200_skip_layer_norm_interleaved_mtron": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, f32, f32, f32, f32]),
-    "bert_b200_emb_layer_norm": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, f32]),
-    "bert_b200_emb_layer_norm_var_seqlen": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp, vp, f32]),
+    "bert_b200_emb_layer_norm": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32]),
+    "bert_b200_emb_layer_norm_var_seqlen": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32]),
     "bert_b200_compute_mask_idx": (i32, [vp, i32, i32, vp, vp]),
     "bert_b200_convert_mask": (i32, [u32, u32, u32, u32, u32, vp, vp, vp]),
     "bert_b200_packed_mask_to_lengths": (i32, [vp, i32, i32, u32, u32, u32, vp, vp]),
@@ -76,6 +76,8 @@ SIGNATURES = {
     "bert_b200_attention_bnsd": (i32, [C.POINTER(AttentionBnsdParams), vp]),
     "bert_b200_mha_workspace_size": (i64, [C.POINTER(MhaParams)]),
     "bert_b200_mha": (i32, [C.POINTER(MhaParams), vp]),
+    "bert_b200_selftest_wait_expiry": (i32, [vp, i64, vp, vp]),
+    "bert_b200_probe_mma_rate": (i32, [vp, i32, i32, vp, C.POINTER(f32)]),
     "bert_b200_encoder_workspace_size": (i64, [C.POINTER(EncoderConfig), i32, i32]),
     "bert_b200_encoder_create": (i32, [C.POINTER(EncoderConfig), C.POINTER(vp)]),
     "bert_b200_encoder_destroy": (i32, [vp]),

@@ -67,6 +67,9 @@ def pack_padded_batch(input_ids, token_type_ids, attention_mask):
     """[B, S] padded arrays (mask 1 = valid, valid tokens first) -> packed (ids, segment ids, cu_seqlens) int32."""
     ids, seg, mask = (np.asarray(a) for a in (input_ids, token_type_ids, attention_mask))
     lengths = mask.astype(np.int64).sum(axis=1)
+    if (lengths == 0).any():
+        raise ValueError("pack_padded_batch: sequence(s) %s have no valid token; drop them before packing (an empty "
+                         "sequence has no [CLS] row for the heads to read)" % np.nonzero(lengths == 0)[0].tolist())
     cu = np.zeros(len(lengths) + 1, dtype=np.int32)
     cu[1:] = np.cumsum(lengths)
     pid = np.concatenate([ids[b, :lengths[b]] for b in range(len(lengths))]).astype(np.int32)
@@ -117,5 +120,8 @@ class PoolerHead:
 
         from . import ops
 
-        first = hidden.index_select(0, cu_seqlens[:-1].long()).contiguous()
+        starts = cu_seqlens[:-1].long()
+        if bool((cu_seqlens[1:].long() <= starts).any()):
+            raise ValueError("PoolerHead: every sequence needs at least one token (its first row is the [CLS] row)")
+        first = hidden.index_select(0, starts).contiguous()
         return torch.tanh(ops.fc(first, self.wt, bias=self.bias).float()).half()

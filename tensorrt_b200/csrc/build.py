@@ -40,7 +40,9 @@ def _nvcc() -> str:
 
 def _trt_include() -> Path | None:
     """Directory holding NvInferRuntime.h (TensorRT public headers), if any."""
-    cands = [os.environ.get("TENSORRT_INCLUDE_DIR"), "/root/reference/include", "/usr/include/x86_64-linux-gnu", "/usr/local/tensorrt/include"]
+    # TENSORRT_INCLUDE_DIR, a TensorRT-OSS checkout named by REFERENCE_ROOT or lying next to this repository, system paths
+    ref = os.environ.get("REFERENCE_ROOT") or ROOT.parent / "reference"
+    cands = [os.environ.get("TENSORRT_INCLUDE_DIR"), Path(ref) / "include", "/usr/include/x86_64-linux-gnu", "/usr/local/tensorrt/include"]
     for c in cands:
         if c and (Path(c) / "NvInferRuntime.h").exists():
             return Path(c)

@@ -75,7 +75,7 @@ template <typename T, int CPL, int WPR, bool PACKED>
 __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_t const B, int32_t const tokens,
     int32_t const* __restrict__ inputIds, int32_t const* __restrict__ tokenIds, int32_t const* __restrict__ cuSeqlens,
     float const* __restrict__ beta, float const* __restrict__ gamma, T const* __restrict__ wordEmb,
-    T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize,
+    T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize, int32_t const posSize,
     T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale)
 {
     constexpr int E = Chunk<T>::kElems;
@@ -117,7 +117,9 @@ __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_
                 pos = t / B;
             }
         }
-        bool const idOk = tokOk && wordId >= 0 && wordId < wordSize && segId >= 0 && segId < tokSize;
+        // ids or a position outside their tables (a sequence longer than the position table, a cu_seqlens that does not
+        // start at 0 or runs backwards) read nothing: such a token produces the row `beta`
+        bool const idOk = tokOk && wordId >= 0 && wordId < wordSize && segId >= 0 && segId < tokSize && pos >= 0 && pos < posSize;
 
         float x[CPL][E];
         float s = 0.f;
@@ -212,7 +214,7 @@ template <typename T, bool PACKED>
 __global__ void __launch_bounds__(kThreads) embLnScalarKernel(int32_t const ld, int32_t const B, int32_t const tokens,
     int32_t const* __restrict__ inputIds, int32_t const* __restrict__ tokenIds, int32_t const* __restrict__ cuSeqlens,
     float const* __restrict__ beta, float const* __restrict__ gamma, T const* __restrict__ wordEmb,
-    T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize,
+    T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize, int32_t const posSize,
     T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale)
 {
     int const lane = threadIdx.x & 31;
@@ -236,7 +238,7 @@ __global__ void __launch_bounds__(kThreads) embLnScalarKernel(int32_t const ld, 
             }
             pos = t - cuSeqlens[lo];
         }
-        bool const idOk = wordId >= 0 && wordId < wordSize && segId >= 0 && segId < tokSize;
+        bool const idOk = wordId >= 0 && wordId < wordSize && segId >= 0 && segId < tokSize && pos >= 0 && pos < posSize;
         T const* wr = wordEmb + static_cast<int64_t>(wordId) * ld;
         T const* pr = posEmb + static_cast<int64_t>(pos) * ld;
         T const* tr = tokEmb + static_cast<int64_t>(segId) * ld;
@@ -419,7 +421,7 @@ inline int gridFor(int64_t groups, int ctasPerSm)
 template <typename T, bool PACKED>
 int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, int32_t const* ids, int32_t const* seg,
     int32_t const* cu, float const* beta, float const* gamma, T const* word, T const* pos, T const* tok, int32_t wordSize,
-    int32_t tokSize, T* out, T* skipOut, int8_t* outI8, float qScale)
+    int32_t tokSize, int32_t posSize, T* out, T* skipOut, int8_t* outI8, float qScale)
 {
     constexpr int E = 16 / sizeof(T);
     bool const vec = ld % E == 0 && ld / E <= 32 * 4 * 8 && aligned16(word) && aligned16(pos) && aligned16(tok)
@@ -429,7 +431,7 @@ int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, 
     {
         int const grid = gridFor((tokens + kWarpsPerCta - 1) / kWarpsPerCta, 8);
         embLnScalarKernel<T, PACKED><<<grid, kThreads, 0, stream>>>(ld, B, tokens, ids, seg, cu, beta, gamma, word, pos,
-            tok, wordSize, tokSize, out, skipOut, outI8, qScale);
+            tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale);
         return checkLaunch("embLnScalarKernel");
     }
     int const chunks = ld / E;
@@ -443,7 +445,7 @@ int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, 
         int const tokPerCta = kWarpsPerCta / W;                                                                        \
         int const grid = gridFor((tokens + tokPerCta - 1) / tokPerCta, 8);                                             \
         embLnKernel<T, C, W, PACKED><<<grid, kThreads, 0, stream>>>(ld, B, tokens, ids, seg, cu, beta, gamma, word,    \
-            pos, tok, wordSize, tokSize, out, skipOut, outI8, qScale);                                                 \
+            pos, tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale);                                        \
         return checkLaunch("embLnKernel");                                                                             \
     }
     B200_EMB_CASE(1, 1)
@@ -467,49 +469,50 @@ using namespace b200;
 
 extern "C" int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
     int32_t const* input_ids, int32_t const* token_ids, float const* beta, float const* gamma, void const* word_emb,
-    void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size, void* output, int8_t* out_i8,
-    float q_scale)
+    void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size, int32_t pos_size, void* output,
+    int8_t* out_i8, float q_scale)
 {
     B200_REQUIRE(ld > 0 && B >= 0 && S >= 0, "emb_layer_norm: bad sizes ld=%d B=%d S=%d", ld, B, S);
     B200_REQUIRE(static_cast<int64_t>(B) * S < (1ll << 31), "emb_layer_norm: B*S overflows int32");
     B200_REQUIRE(input_ids && token_ids && beta && gamma && word_emb && pos_emb && tok_emb && output,
         "emb_layer_norm: null pointer");
-    B200_REQUIRE(word_size > 0 && tok_size > 0, "emb_layer_norm: empty table");
+    B200_REQUIRE(word_size > 0 && tok_size > 0 && pos_size > 0, "emb_layer_norm: empty table");
+    B200_REQUIRE(S <= pos_size, "emb_layer_norm: S=%d exceeds the position table (%d rows)", S, pos_size);
     if (B * S == 0)
         return BERT_B200_OK;
     auto s = static_cast<cudaStream_t>(stream);
     if (type_id == BERT_B200_FP16)
         return dispatchEmb<__half, false>(s, ld, B, B * S, input_ids, token_ids, nullptr, beta, gamma,
             static_cast<__half const*>(word_emb), static_cast<__half const*>(pos_emb), static_cast<__half const*>(tok_emb),
-            word_size, tok_size, static_cast<__half*>(output), nullptr, out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<__half*>(output), nullptr, out_i8, q_scale);
     if (type_id == BERT_B200_FP32)
         return dispatchEmb<float, false>(s, ld, B, B * S, input_ids, token_ids, nullptr, beta, gamma,
             static_cast<float const*>(word_emb), static_cast<float const*>(pos_emb), static_cast<float const*>(tok_emb),
-            word_size, tok_size, static_cast<float*>(output), nullptr, out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<float*>(output), nullptr, out_i8, q_scale);
     B200_FAIL(BERT_B200_NOT_SUPPORTED, "emb_layer_norm: type_id %d", type_id);
 }
 
 extern "C" int32_t bert_b200_emb_layer_norm_var_seqlen(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
     int32_t total, int32_t const* input_ids, int32_t const* token_ids, int32_t const* cu_seqlens, float const* beta,
     float const* gamma, void const* word_emb, void const* pos_emb, void const* tok_emb, int32_t word_size,
-    int32_t tok_size, void* output, void* skip_out, int8_t* out_i8, float q_scale)
+    int32_t tok_size, int32_t pos_size, void* output, void* skip_out, int8_t* out_i8, float q_scale)
 {
     (void) S;
     B200_REQUIRE(ld > 0 && B >= 0 && total >= 0, "emb_layer_norm_var_seqlen: bad sizes ld=%d B=%d total=%d", ld, B, total);
     B200_REQUIRE(input_ids && token_ids && cu_seqlens && beta && gamma && word_emb && pos_emb && tok_emb && output,
         "emb_layer_norm_var_seqlen: null pointer");
-    B200_REQUIRE(word_size > 0 && tok_size > 0, "emb_layer_norm_var_seqlen: empty table");
+    B200_REQUIRE(word_size > 0 && tok_size > 0 && pos_size > 0, "emb_layer_norm_var_seqlen: empty table");
     if (total == 0 || B == 0)
         return BERT_B200_OK;
     auto s = static_cast<cudaStream_t>(stream);
     if (type_id == BERT_B200_FP16)
         return dispatchEmb<__half, true>(s, ld, B, total, input_ids, token_ids, cu_seqlens, beta, gamma,
             static_cast<__half const*>(word_emb), static_cast<__half const*>(pos_emb), static_cast<__half const*>(tok_emb),
-            word_size, tok_size, static_cast<__half*>(output), static_cast<__half*>(skip_out), out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<__half*>(output), static_cast<__half*>(skip_out), out_i8, q_scale);
     if (type_id == BERT_B200_FP32)
         return dispatchEmb<float, true>(s, ld, B, total, input_ids, token_ids, cu_seqlens, beta, gamma,
             static_cast<float const*>(word_emb), static_cast<float const*>(pos_emb), static_cast<float const*>(tok_emb),
-            word_size, tok_size, static_cast<float*>(output), static_cast<float*>(skip_out), out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<float*>(output), static_cast<float*>(skip_out), out_i8, q_scale);
     B200_FAIL(BERT_B200_NOT_SUPPORTED, "emb_layer_norm_var_seqlen: type_id %d", type_id);
 }
 

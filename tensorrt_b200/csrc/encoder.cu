@@ -206,6 +206,28 @@ extern "C" int32_t bert_b200_encoder_create(bert_b200_encoder_config const* cfg,
             B200_FAIL(BERT_B200_BAD_PARAM, "encoder_create: null layer weight pointer");
         }
     }
+    if (cfg->type_id == BERT_B200_INT8)
+    {
+        // a zero or non-finite scale turns 1 / s into inf / NaN inside the quantising epilogues, and a layer that
+        // dequantises its input with another step than the one the previous layer quantised with is silently wrong
+        auto good = [](float v) { return std::isfinite(v) && v > 0.f; };
+        for (size_t i = 0; i < e->layers.size(); ++i)
+        {
+            auto const& l = e->layers[i];
+            bool const ok = good(l.s_in) && good(l.s_wqkv) && good(l.s_qkv) && good(l.s_ctx) && good(l.s_wout) && good(l.s_attn_out)
+                && good(l.s_ln1) && good(l.s_wffn1) && good(l.s_ffn1) && good(l.s_wffn2) && good(l.s_ffn2) && good(l.s_out)
+                && good(cfg->dq_probs);
+            bool const chained = i == 0 || e->layers[i - 1].s_out == l.s_in;
+            if (!ok || !chained)
+            {
+                int const layer = static_cast<int>(i);
+                delete e;
+                if (!ok)
+                    B200_FAIL(BERT_B200_BAD_PARAM, "encoder_create: layer %d has a scale (or dq_probs) that is not finite and positive", layer);
+                B200_FAIL(BERT_B200_BAD_PARAM, "encoder_create: layer %d dequantises its input with s_in != s_out of layer %d", layer, layer - 1);
+            }
+        }
+    }
     *out = e;
     return BERT_B200_OK;
 }
@@ -280,7 +302,7 @@ static int32_t forwardImpl(bert_b200_encoder* enc, cudaStream_t stream, int32_t 
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward: clearing the status word failed");
     // FP16: embedding output is the first layer input. INT8: additionally quantised with the first layer's input scale.
     B200_STEP(BERT_B200_KIND_EMB, bert_b200_emb_layer_norm_var_seqlen(stream, BERT_B200_FP16, E, B, maxSeqlen, total, ids, seg, cu, c.emb_beta,
-        c.emb_gamma, c.word_emb, c.pos_emb, c.tok_emb, c.vocab_size, c.type_vocab_size, i8 ? static_cast<void*>(w.xf16) : w.x,
+        c.emb_gamma, c.word_emb, c.pos_emb, c.tok_emb, c.vocab_size, c.type_vocab_size, c.max_positions, i8 ? static_cast<void*>(w.xf16) : w.x,
         nullptr, i8 ? reinterpret_cast<int8_t*>(w.x) : nullptr, i8 ? 1.f / enc->layers[0].s_in : 0.f));
 
     int32_t const headSize = c.hidden_size / c.num_heads;
@@ -602,8 +624,10 @@ int32_t staticWorkspace(void** out)
     static void* perDevice[64] = {nullptr};
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= 64)
+    if (e != cudaSuccess)
         B200_FAIL(BERT_B200_CUDA_ERROR, "encoder_forward_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64)
+        B200_FAIL(BERT_B200_NOT_SUPPORTED, "encoder_forward_static: device ordinal %d is outside the 64 this entry point keeps an address for", dev);
     std::lock_guard<std::mutex> lock(mtx);
     if (!perDevice[dev])
     {

@@ -388,7 +388,7 @@ public:
             int32_t st = abiStatus(bert_b200_emb_layer_norm(stream, typeId(w.type), w.ld, B, S,
                                        static_cast<int32_t const*>(inputs[0]), static_cast<int32_t const*>(inputs[1]),
                                        static_cast<float const*>(w.dBeta.ptr), static_cast<float const*>(w.dGamma.ptr),
-                                       w.dWord.ptr, w.dPos.ptr, w.dTok.ptr, w.wordVocab, w.tokVocab, outputs[0], nullptr, 0.f),
+                                       w.dWord.ptr, w.dPos.ptr, w.dTok.ptr, w.wordVocab, w.tokVocab, w.posVocab, outputs[0], nullptr, 0.f),
                 "emb_layer_norm");
             if (st != BERT_B200_OK)
                 return st;
@@ -546,7 +546,7 @@ public:
                                  static_cast<int32_t const*>(inputs[0]), static_cast<int32_t const*>(inputs[1]),
                                  static_cast<int32_t const*>(inputs[2]), static_cast<float const*>(w.dBeta.ptr),
                                  static_cast<float const*>(w.dGamma.ptr), w.dWord.ptr, w.dPos.ptr, w.dTok.ptr, w.wordVocab,
-                                 w.tokVocab, outputs[0], mtron ? outputs[1] : nullptr, nullptr, 0.f),
+                                 w.tokVocab, w.posVocab, outputs[0], mtron ? outputs[1] : nullptr, nullptr, 0.f),
                 "emb_layer_norm_var_seqlen");
         }
         catch (std::exception const& e)

@@ -115,7 +115,8 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull; // 2 s
 
 // The polling loop is one out-of-line copy per kernel image: inlined at every wait it was a sizeable part of the
 // code of the persistent kernels, whose single-thread roles are sensitive to instruction-cache misses.
-static __device__ __noinline__ bool mbarWaitSlow(uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code)
+static __device__ __noinline__ bool mbarWaitSlow(
+    uint32_t barAddr, uint32_t parity, volatile uint32_t* abortFlag, uint32_t code, uint64_t limitNs = kWaitLimitNs)
 {
     // The clock is only consulted every 256 failed polls (a read of %globaltimer costs far more than a poll, and most
     // waits end within a few polls), so the common case is nothing but try_wait.
@@ -132,7 +133,7 @@ static __device__ __noinline__ bool mbarWaitSlow(uint32_t barAddr, uint32_t pari
             uint64_t const now = globalTimerNs();
             if (t0 == 0)
                 t0 = now;
-            else if (now - t0 > kWaitLimitNs)
+            else if (now - t0 > limitNs)
             {
                 *abortFlag = code;
                 return false;

@@ -78,7 +78,7 @@ def emb_layer_norm(input_ids, token_ids, word_emb, pos_emb, tok_emb, gamma, beta
     out_i8 = torch.empty((S, B, ld), dtype=torch.int8, device=word_emb.device) if q_scale is not None else None
     check(lib.bert_b200_emb_layer_norm(_stream(), _TYPE_ID[word_emb.dtype], ld, B, S, _ptr(input_ids), _ptr(token_ids),
                                        _ptr(beta), _ptr(gamma), _ptr(word_emb), _ptr(pos_emb), _ptr(tok_emb),
-                                       word_emb.shape[0], tok_emb.shape[0], _ptr(out), _ptr(out_i8),
+                                       word_emb.shape[0], tok_emb.shape[0], pos_emb.shape[0], _ptr(out), _ptr(out_i8),
                                        q_scale or 0.0), "emb_layer_norm")
     return out if q_scale is None else (out, out_i8)
 
@@ -95,7 +95,7 @@ def emb_layer_norm_var_seqlen(input_ids, token_ids, cu_seqlens, max_seqlen, word
     check(lib.bert_b200_emb_layer_norm_var_seqlen(_stream(), _TYPE_ID[word_emb.dtype], ld, B, max_seqlen, total,
                                                   _ptr(input_ids), _ptr(token_ids), _ptr(cu_seqlens), _ptr(beta),
                                                   _ptr(gamma), _ptr(word_emb), _ptr(pos_emb), _ptr(tok_emb),
-                                                  word_emb.shape[0], tok_emb.shape[0], _ptr(out), _ptr(skip),
+                                                  word_emb.shape[0], tok_emb.shape[0], pos_emb.shape[0], _ptr(out), _ptr(skip),
                                                   _ptr(out_i8), q_scale or 0.0), "emb_layer_norm_var_seqlen")
     res = [out]
     if with_skip:

@@ -88,6 +88,35 @@ def test_encoder_config_validation():
     assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 2
 
 
+def test_encoder_create_checks_int8_scales():
+    """INT8: every dequantisation step must be finite and positive, and a layer must read its input with the step the
+    previous layer wrote it with - otherwise the quantising epilogues produce inf / NaN or silently wrong values."""
+    from tensorrt_b200 import _lib
+
+    fake = C.c_void_p(0x1000)   # never dereferenced by create
+    layers = (_lib.LayerWeights * 2)()
+    names = [n for n, _ in _lib.LayerWeights._fields_]
+    for lw in layers:
+        for n in names:
+            setattr(lw, n, fake if not n.startswith("s_") else 0.05)
+    cfg = _lib.EncoderConfig(2, 2, 128, 2, 512, 100, 64, 2, 1.0 / 127, fake, fake, fake, fake, fake, layers)
+    h = C.c_void_p()
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 0
+    _lib.lib.bert_b200_encoder_destroy(h)
+    layers[1].s_ffn1 = 0.0
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 2
+    assert b"layer 1" in _lib.lib.bert_b200_last_error()
+    layers[1].s_ffn1 = float("nan")
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 2
+    layers[1].s_ffn1 = 0.05
+    layers[1].s_in = 0.06                                  # layer 0 wrote its output with step 0.05
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 2
+    assert b"s_in != s_out" in _lib.lib.bert_b200_last_error()
+    cfg.type_id = 1                                        # FP16 ignores the scales
+    assert _lib.lib.bert_b200_encoder_create(C.byref(cfg), C.byref(h)) == 0
+    _lib.lib.bert_b200_encoder_destroy(h)
+
+
 def test_no_cpu_fallback():
     import torch
 

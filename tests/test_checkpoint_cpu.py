@@ -62,3 +62,15 @@ def test_qkv_packing_order():
     assert p.ffn == 128 and p.hidden == 64 and len(p.layers) == 1
     with pytest.raises(ValueError):
         params_from_bert_state_dict(sd, num_heads=5)
+
+
+def test_empty_sequences_are_rejected_before_packing():
+    """An all-zero mask row would make the next sequence's first token look like this one's [CLS] row."""
+    import pytest
+
+    from tensorrt_b200.checkpoint import pack_padded_batch
+
+    ids = np.ones((3, 4), dtype=np.int64)
+    mask = np.array([[1, 1, 0, 0], [0, 0, 0, 0], [1, 0, 0, 0]])
+    with pytest.raises(ValueError, match="no valid token"):
+        pack_padded_batch(ids, ids * 0, mask)

@@ -128,3 +128,37 @@ def test_cu_seqlens_bit_exact(cuda, B):
     out = T.lengths_to_cu_seqlens(_t(lengths, cuda)).cpu().numpy()
     assert out.dtype == np.int32
     assert np.array_equal(out, O.cu_seqlens(lengths))
+
+
+def test_positions_outside_the_table_are_guarded(cuda):
+    """A packed sequence longer than the position table, and a cu_seqlens that does not start at 0, would index the
+    position table out of range: such tokens read nothing and produce the row `beta` (like ids outside their
+    tables); every other token is unaffected. The fixed-length entry refuses S beyond the table on the host."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(9)
+    E, vocab, npos = 256, 100, 40
+    word, pos, tok = ((0.02 * rng.standard_normal((n, E))).astype(np.float16) for n in (vocab, npos, 2))
+    gam = (1 + 0.02 * rng.standard_normal(E)).astype(np.float32)
+    bet = (0.02 * rng.standard_normal(E)).astype(np.float32)
+    dev = [_t(a, cuda) for a in (word, pos, tok, gam, bet)]
+    lengths = np.array([30, 55, 40], dtype=np.int32)           # the second sequence overruns the 40-row table
+    cu = O.cu_seqlens(lengths)
+    total = int(cu[-1])
+    ids = rng.integers(0, vocab, size=total).astype(np.int32)
+    seg = rng.integers(0, 2, size=total).astype(np.int32)
+    out = T.emb_layer_norm_var_seqlen(_t(ids, cuda), _t(seg, cuda), _t(cu, cuda), 64, *dev).float().cpu().numpy()
+    posn = np.concatenate([np.arange(n) for n in lengths])
+    ok_rows = posn < npos
+    sub_cu = O.cu_seqlens(np.minimum(lengths, npos))
+    ref, _ = O.emb_layer_norm_var_seqlen(ids[ok_rows], seg[ok_rows], sub_cu, word, pos, tok, gam, bet)
+    assert O.close_abs_or_rel(out[ok_rows], ref, 1e-2, 1e-2)[0]
+    assert np.allclose(out[~ok_rows], bet.astype(np.float16).astype(np.float32)[None], atol=1e-3)
+    # cu_seqlens starting at 5: tokens 0..4 lie before every sequence start (negative position)
+    cu2 = (cu + 5).astype(np.int32)
+    cu2[-1] = total
+    out2 = T.emb_layer_norm_var_seqlen(_t(ids, cuda), _t(seg, cuda), _t(cu2, cuda), 64, *dev).float().cpu().numpy()
+    assert np.isfinite(out2).all()
+    assert np.allclose(out2[:5], bet.astype(np.float16).astype(np.float32)[None], atol=1e-3)
+    with pytest.raises(RuntimeError, match="position table"):
+        T.emb_layer_norm(_t(np.zeros((npos + 1, 2), np.int32), cuda), _t(np.zeros((npos + 1, 2), np.int32), cuda), *dev)
