@@ -216,7 +216,7 @@ def time_e2e(enc, ids, seg, cu, steps, warmup, world, dist, out_dev):
     return ms, h2d, d2h
 
 
-def probe_mma_rate(T, type_id, k_blocks=4000):
+def probe_mma_rate(T, type_id, k_blocks=20000):
     """TOP/s the tensor pipes sustain for the FC kernels' MMA shape with operands resident in shared memory."""
     import torch
 
@@ -430,7 +430,7 @@ def run_b200(args):
     c4_cu = c4_cu.to(dev)
     c4_out = torch.empty((c4_total, HIDDEN), dtype=torch.float16, device=dev)
     c4 = {}
-    for name in order:
+    for name in ([] if args.no_extras else order):
         enc = encs[name]
         c4_ms = time_forward(lambda: enc.forward(c4_ids, c4_seg, c4_cu, SEQ, out=c4_out), max(5, args.steps // 2), 3, world, dist)
         (c4_ms,) = reduce_max(c4_ms)
@@ -514,7 +514,7 @@ def run_b200(args):
         if n > 1:
             line[name]["weak_value"] = n * BATCH / (r["ms_weak"] * 1e-3)
     tokens4 = int(lengths_all.sum())
-    line["config4"] = {
+    line["config4"] = None if args.no_extras else {
         "workload": "BERT-large packed variable-length batch: 256 sequences, lengths uniform in [32, 384] (seed 1), "
                     f"{tokens4} tokens, sequences assigned longest-first to the least-loaded GPU (benchmark configuration 4)",
         "tokens": tokens4, "shard_tokens": [int(lengths_all[s].sum()) for s in shards],
@@ -659,6 +659,71 @@ def run_sweep(args):
     emit({"sweep": res})
 
 
+def run_case(name):
+    """Profiling captures: ONE kernel launched a few times on inputs larger than the L2 and a few GB at most, so that a
+    profiler capture of it (`-k <kernel> -c 1..3`) ends in a minute: mha_f16 / mha_i8 (S=384, 64 sequences, 16 heads x
+    64), ln_f16 / ln_i8 (SkipLayerNorm + bias, 131072 rows of 1024), emb (S=384, 256 sequences, vocab 30522, hidden
+    1024), fc_f16 / fc_i8 (the four BERT-large FC shapes at 24576 rows, two launches each). Prints no bench value."""
+    import torch
+
+    import tensorrt_b200 as T
+
+    dev = torch.device("cuda:0")
+    N, d = 16, 64
+    if name in ("mha_f16", "mha_i8"):
+        S, B = 384, 64
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+        if name == "mha_f16":
+            qkv = torch.randn(S * B, 3 * N * d, device=dev).half()
+            for _ in range(4):
+                out = T.mha(qkv, B, S, N, cu_seqlens=cu)
+        else:
+            q8 = torch.randint(-127, 127, (S * B, 3 * N * d), device=dev, dtype=torch.int8)
+            for _ in range(4):
+                out = T.mha(q8, B, S, N, cu_seqlens=cu, scale_bmm1=1e-4, scale_softmax=127.0, scale_bmm2=0.01)
+    elif name in ("ln_f16", "ln_i8"):
+        tokens, ld = 131072, 1024
+        g = torch.ones(ld, device=dev).half()
+        b = torch.zeros(ld, device=dev).half()
+        if name == "ln_f16":
+            x, s = torch.randn(tokens, ld, device=dev).half(), torch.randn(tokens, ld, device=dev).half()
+            out = torch.empty_like(x)
+            for _ in range(4):
+                T.skip_layer_norm(x, s, g, b, bias=b, out=out)
+        else:
+            x = torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8)
+            s = torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8)
+            out = torch.empty_like(x)
+            for _ in range(4):
+                T.skip_layer_norm_dqq(x, s, g, b, b, 0.02, 0.02, 40.0, out=out)
+    elif name == "emb":
+        E, vocab, S, B = 1024, 30522, 384, 256
+        word = (0.02 * torch.randn(vocab, E, device=dev)).half()
+        pos = (0.02 * torch.randn(512, E, device=dev)).half()
+        tok = (0.02 * torch.randn(2, E, device=dev)).half()
+        gam, bet = torch.ones(E, device=dev), torch.zeros(E, device=dev)
+        for _ in range(4):
+            ids = torch.randint(0, vocab, (S, B), device=dev, dtype=torch.int32)
+            seg = torch.randint(0, 2, (S, B), device=dev, dtype=torch.int32)
+            out = T.emb_layer_norm(ids, seg, word, pos, tok, gam, bet)
+    elif name in ("fc_f16", "fc_i8"):
+        for (m, k, n, act) in [(24576, 1024, 3072, 0), (24576, 1024, 1024, 0), (24576, 1024, 4096, 1), (24576, 4096, 1024, 0)]:
+            bias = torch.zeros(n, device=dev) if act or n == 3072 else None
+            if name == "fc_f16":
+                a, w = torch.randn(m, k, device=dev).half(), (0.02 * torch.randn(n, k, device=dev)).half()
+                for _ in range(2):
+                    out = T.fc(a, w, bias, T.ACT_GELU_ERF if act else T.ACT_NONE)
+            else:
+                a = torch.randint(-127, 127, (m, k), device=dev, dtype=torch.int8)
+                w = torch.randint(-127, 127, (n, k), device=dev, dtype=torch.int8)
+                for _ in range(2):
+                    out = T.fc(a, w, bias, T.ACT_GELU_ERF if act else T.ACT_NONE, alpha=1e-4, out_dtype=torch.int8, out_scale=20.0)
+    else:
+        raise SystemExit(f"unknown case {name}")
+    torch.cuda.synchronize()
+    print("case", name, "ok", float(out.float().abs().mean()), file=sys.stderr)
+
+
 _JSON_FD = None
 
 
@@ -692,15 +757,18 @@ def main():
     ap.add_argument("--both", action=argparse.BooleanOptionalAction, default=True,
                     help="also time the other precision and report it in a sub-object")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-extras", action="store_true", help="skip the plugin-path leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the plugin-path and packed variable-length legs")
     ap.add_argument("--sweep", action="store_true", help="kernel sweep against the rooflines instead of the encoder step")
+    ap.add_argument("--case", default=None, help="profiling captures only: launch ONE kernel a few times (see run_case)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="profiling captures only: fewer encoder layers")
     ap.add_argument("--batch", type=int, default=BATCH, help="profiling captures only: sequences in the global batch")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch)
     if args.warmup < 3:
         args.warmup = 3
-    if args.sweep:
+    if args.case:
+        run_case(args.case)
+    elif args.sweep:
         run_sweep(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -121,6 +121,17 @@ BERT_B200_API int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, in
     int32_t pos_size, void* output, int8_t* out_i8, float q_scale);
 
 /*
+ * The same launch also writes the second output of the fixed-length embedding plugin: mask_idx[b] = index of the first 0
+ * in column b of the [S,B] int32 `mask`, S if there is none (one warp per sequence after its share of the rows; no
+ * second kernel). mask and mask_idx NULL: exactly bert_b200_emb_layer_norm.
+ * ref: plugin/embLayerNormPlugin/embLayerNormPlugin.cpp:251-336 (enqueue: embSkipLayerNorm, then computeMaskIdx)
+ */
+BERT_B200_API int32_t bert_b200_emb_layer_norm_mask_idx(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
+    int32_t const* input_ids, int32_t const* token_ids, float const* beta, float const* gamma,
+    void const* word_emb, void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size,
+    int32_t pos_size, void* output, int8_t* out_i8, float q_scale, int32_t const* mask, int32_t* mask_idx);
+
+/*
  * Packed variable-length: ids are [total], sequence b owns tokens cu_seqlens[b]..cu_seqlens[b+1];
  * the position row is the index inside the sequence. `skip_out` (may be NULL) receives the
  * pre-LayerNorm sum (the "MTron" second output). `total` = cu_seqlens[B] must be given by the

@@ -67,6 +67,7 @@ SIGNATURES = {
     "bert_b200_skip_layer_norm_interleaved_hface": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, f32, f32, f32]),
     "bert_b200_skip_layer_norm_interleaved_mtron": (i32, [vp, i32, i32, vp, vp, vp, vp, vp, vp, f32, f32, f32, f32]),
     "bert_b200_emb_layer_norm": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32]),
+    "bert_b200_emb_layer_norm_mask_idx": (i32, [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, f32, vp, vp]),
     "bert_b200_emb_layer_norm_var_seqlen": (i32, [vp, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, vp, vp, vp, f32]),
     "bert_b200_compute_mask_idx": (i32, [vp, i32, i32, vp, vp]),
     "bert_b200_convert_mask": (i32, [u32, u32, u32, u32, u32, vp, vp, vp]),

@@ -69,14 +69,35 @@ __device__ __forceinline__ float tokSum(float v, float* slot, int wInRow, int la
     return t;
 }
 
+// First s with mask[s][b] == 0 in column b of the [S, B] mask, S if there is none; one warp per sequence.
+__device__ __forceinline__ void maskIdxOfSequence(int32_t const S, int32_t const B, int32_t const b, int const lane,
+    int32_t const* __restrict__ mask, int32_t* __restrict__ maskIdx)
+{
+    int first = S;
+    for (int base = 0; base < S && first == S; base += 32)
+    {
+        int const s = base + lane;
+        bool const zero = s < S && mask[static_cast<int64_t>(s) * B + b] == 0;
+        uint32_t const ballot = __ballot_sync(0xffffffffu, zero);
+        if (ballot)
+            first = base + __ffs(ballot) - 1;
+    }
+    if (lane == 0)
+        maskIdx[b] = first;
+}
+
 // PACKED = false: token t = s*B + b, position s = t / B.
 // PACKED = true : token t belongs to the sequence b with cu[b] <= t < cu[b+1]; position t - cu[b].
+// PACKED = false with maskIdx != nullptr: `cuSeqlens` is the [S, B] input mask and the same launch also writes the mask
+// index of every sequence (the second output of the fixed-length embedding plugin), one warp per sequence after the
+// warp's share of the rows.
 template <typename T, int CPL, int WPR, bool PACKED>
 __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_t const B, int32_t const tokens,
     int32_t const* __restrict__ inputIds, int32_t const* __restrict__ tokenIds, int32_t const* __restrict__ cuSeqlens,
     float const* __restrict__ beta, float const* __restrict__ gamma, T const* __restrict__ wordEmb,
     T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize, int32_t const posSize,
-    T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale)
+    T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale,
+    int32_t* __restrict__ maskIdx)
 {
     constexpr int E = Chunk<T>::kElems;
     constexpr int kTokPerCta = kWarpsPerCta / WPR;
@@ -207,6 +228,11 @@ __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_
             }
         }
     }
+    if (!PACKED && maskIdx != nullptr)
+    {
+        for (int b = blockIdx.x * kWarpsPerCta + warp; b < B; b += gridDim.x * kWarpsPerCta)
+            maskIdxOfSequence(tokens / B, B, b, lane, cuSeqlens, maskIdx);
+    }
 }
 
 // Scalar version for row lengths that are not a multiple of the 16-byte chunk; one warp per token.
@@ -215,7 +241,8 @@ __global__ void __launch_bounds__(kThreads) embLnScalarKernel(int32_t const ld, 
     int32_t const* __restrict__ inputIds, int32_t const* __restrict__ tokenIds, int32_t const* __restrict__ cuSeqlens,
     float const* __restrict__ beta, float const* __restrict__ gamma, T const* __restrict__ wordEmb,
     T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize, int32_t const posSize,
-    T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale)
+    T* __restrict__ out, T* __restrict__ skipOut, int8_t* __restrict__ outI8, float const qScale,
+    int32_t* __restrict__ maskIdx)
 {
     int const lane = threadIdx.x & 31;
     int const warp = threadIdx.x >> 5;
@@ -268,27 +295,20 @@ __global__ void __launch_bounds__(kThreads) embLnScalarKernel(int32_t const ld, 
                 outI8[off] = quantChar(y * qScale);
         }
     }
+    if (!PACKED && maskIdx != nullptr)
+    {
+        for (int b = blockIdx.x * kWarpsPerCta + warp; b < B; b += gridDim.x * kWarpsPerCta)
+            maskIdxOfSequence(tokens / B, B, b, lane, cuSeqlens, maskIdx);
+    }
 }
 
 // One warp per sequence: first s with mask[s][b] == 0, S if none.
 __global__ void __launch_bounds__(kThreads) maskIdxKernel(int32_t const S, int32_t const B, int32_t const* __restrict__ mask,
     int32_t* __restrict__ maskIdx)
 {
-    int const lane = threadIdx.x & 31;
     int const b = blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-    if (b >= B)
-        return;
-    int first = S;
-    for (int base = 0; base < S && first == S; base += 32)
-    {
-        int const s = base + lane;
-        bool const zero = s < S && mask[static_cast<int64_t>(s) * B + b] == 0;
-        uint32_t const ballot = __ballot_sync(0xffffffffu, zero);
-        if (ballot)
-            first = base + __ffs(ballot) - 1;
-    }
-    if (lane == 0)
-        maskIdx[b] = first;
+    if (b < B)
+        maskIdxOfSequence(S, B, b, threadIdx.x & 31, mask, maskIdx);
 }
 
 // Bit layout of the reference fused-attention mask: see bert_b200_convert_mask in the header.
@@ -421,7 +441,7 @@ inline int gridFor(int64_t groups, int ctasPerSm)
 template <typename T, bool PACKED>
 int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, int32_t const* ids, int32_t const* seg,
     int32_t const* cu, float const* beta, float const* gamma, T const* word, T const* pos, T const* tok, int32_t wordSize,
-    int32_t tokSize, int32_t posSize, T* out, T* skipOut, int8_t* outI8, float qScale)
+    int32_t tokSize, int32_t posSize, T* out, T* skipOut, int8_t* outI8, float qScale, int32_t* maskIdx = nullptr)
 {
     constexpr int E = 16 / sizeof(T);
     bool const vec = ld % E == 0 && ld / E <= 32 * 4 * 8 && aligned16(word) && aligned16(pos) && aligned16(tok)
@@ -431,7 +451,7 @@ int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, 
     {
         int const grid = gridFor((tokens + kWarpsPerCta - 1) / kWarpsPerCta, 8);
         embLnScalarKernel<T, PACKED><<<grid, kThreads, 0, stream>>>(ld, B, tokens, ids, seg, cu, beta, gamma, word, pos,
-            tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale);
+            tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale, maskIdx);
         return checkLaunch("embLnScalarKernel");
     }
     int const chunks = ld / E;
@@ -445,7 +465,7 @@ int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, 
         int const tokPerCta = kWarpsPerCta / W;                                                                        \
         int const grid = gridFor((tokens + tokPerCta - 1) / tokPerCta, 8);                                             \
         embLnKernel<T, C, W, PACKED><<<grid, kThreads, 0, stream>>>(ld, B, tokens, ids, seg, cu, beta, gamma, word,    \
-            pos, tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale);                                        \
+            pos, tok, wordSize, tokSize, posSize, out, skipOut, outI8, qScale, maskIdx);                               \
         return checkLaunch("embLnKernel");                                                                             \
     }
     B200_EMB_CASE(1, 1)
@@ -467,10 +487,10 @@ int32_t dispatchEmb(cudaStream_t stream, int32_t ld, int32_t B, int32_t tokens, 
 
 using namespace b200;
 
-extern "C" int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
+extern "C" int32_t bert_b200_emb_layer_norm_mask_idx(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
     int32_t const* input_ids, int32_t const* token_ids, float const* beta, float const* gamma, void const* word_emb,
     void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size, int32_t pos_size, void* output,
-    int8_t* out_i8, float q_scale)
+    int8_t* out_i8, float q_scale, int32_t const* mask, int32_t* mask_idx)
 {
     B200_REQUIRE(ld > 0 && B >= 0 && S >= 0, "emb_layer_norm: bad sizes ld=%d B=%d S=%d", ld, B, S);
     B200_REQUIRE(static_cast<int64_t>(B) * S < (1ll << 31), "emb_layer_norm: B*S overflows int32");
@@ -478,18 +498,28 @@ extern "C" int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, int32
         "emb_layer_norm: null pointer");
     B200_REQUIRE(word_size > 0 && tok_size > 0 && pos_size > 0, "emb_layer_norm: empty table");
     B200_REQUIRE(S <= pos_size, "emb_layer_norm: S=%d exceeds the position table (%d rows)", S, pos_size);
+    B200_REQUIRE(mask_idx == nullptr || mask != nullptr || S == 0, "emb_layer_norm: mask_idx without a mask");
     if (B * S == 0)
-        return BERT_B200_OK;
+        return mask_idx && B > 0 ? bert_b200_compute_mask_idx(stream, S, B, mask, mask_idx) : BERT_B200_OK;
     auto s = static_cast<cudaStream_t>(stream);
     if (type_id == BERT_B200_FP16)
-        return dispatchEmb<__half, false>(s, ld, B, B * S, input_ids, token_ids, nullptr, beta, gamma,
+        return dispatchEmb<__half, false>(s, ld, B, B * S, input_ids, token_ids, mask, beta, gamma,
             static_cast<__half const*>(word_emb), static_cast<__half const*>(pos_emb), static_cast<__half const*>(tok_emb),
-            word_size, tok_size, pos_size, static_cast<__half*>(output), nullptr, out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<__half*>(output), nullptr, out_i8, q_scale, mask_idx);
     if (type_id == BERT_B200_FP32)
-        return dispatchEmb<float, false>(s, ld, B, B * S, input_ids, token_ids, nullptr, beta, gamma,
+        return dispatchEmb<float, false>(s, ld, B, B * S, input_ids, token_ids, mask, beta, gamma,
             static_cast<float const*>(word_emb), static_cast<float const*>(pos_emb), static_cast<float const*>(tok_emb),
-            word_size, tok_size, pos_size, static_cast<float*>(output), nullptr, out_i8, q_scale);
+            word_size, tok_size, pos_size, static_cast<float*>(output), nullptr, out_i8, q_scale, mask_idx);
     B200_FAIL(BERT_B200_NOT_SUPPORTED, "emb_layer_norm: type_id %d", type_id);
+}
+
+extern "C" int32_t bert_b200_emb_layer_norm(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,
+    int32_t const* input_ids, int32_t const* token_ids, float const* beta, float const* gamma, void const* word_emb,
+    void const* pos_emb, void const* tok_emb, int32_t word_size, int32_t tok_size, int32_t pos_size, void* output,
+    int8_t* out_i8, float q_scale)
+{
+    return bert_b200_emb_layer_norm_mask_idx(stream, type_id, ld, B, S, input_ids, token_ids, beta, gamma, word_emb, pos_emb,
+        tok_emb, word_size, tok_size, pos_size, output, out_i8, q_scale, nullptr, nullptr);
 }
 
 extern "C" int32_t bert_b200_emb_layer_norm_var_seqlen(void* stream, int32_t type_id, int32_t ld, int32_t B, int32_t S,

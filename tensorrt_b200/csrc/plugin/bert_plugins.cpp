@@ -385,21 +385,22 @@ public:
             PLG_VALIDATE(w.onDevice());
             int32_t const B = static_cast<int32_t>(inDesc[0].dims.d[BDIM]);
             int32_t const S = static_cast<int32_t>(inDesc[0].dims.d[SDIM]);
-            int32_t st = abiStatus(bert_b200_emb_layer_norm(stream, typeId(w.type), w.ld, B, S,
-                                       static_cast<int32_t const*>(inputs[0]), static_cast<int32_t const*>(inputs[1]),
-                                       static_cast<float const*>(w.dBeta.ptr), static_cast<float const*>(w.dGamma.ptr),
-                                       w.dWord.ptr, w.dPos.ptr, w.dTok.ptr, w.wordVocab, w.tokVocab, w.posVocab, outputs[0], nullptr, 0.f),
-                "emb_layer_norm");
-            if (st != BERT_B200_OK)
-                return st;
             auto const* mask = static_cast<int32_t const*>(inputs[2]);
             uint32_t wm = 0, wn = 0;
             bool const packed = (fullMask || mhaMaskPackedSize(static_cast<DataType>(mhaTypeId), S) != kUnfusedMaskSize)
                 && packedMaskWarps(S, wm, wn);
-            if (packed)
-                return abiStatus(bert_b200_convert_mask(S, B, wm, wn, 1, mask, static_cast<uint32_t*>(outputs[1]), stream),
-                    "convert_mask");
-            return abiStatus(bert_b200_compute_mask_idx(stream, S, B, mask, static_cast<int32_t*>(outputs[1])), "compute_mask_idx");
+            // the mask index comes out of the embedding launch itself; only the packed fused-attention mask is a second kernel
+            int32_t const st = abiStatus(
+                bert_b200_emb_layer_norm_mask_idx(stream, typeId(w.type), w.ld, B, S, static_cast<int32_t const*>(inputs[0]),
+                    static_cast<int32_t const*>(inputs[1]), static_cast<float const*>(w.dBeta.ptr),
+                    static_cast<float const*>(w.dGamma.ptr), w.dWord.ptr, w.dPos.ptr, w.dTok.ptr, w.wordVocab, w.tokVocab,
+                    w.posVocab, outputs[0], nullptr, 0.f, packed ? nullptr : mask,
+                    packed ? nullptr : static_cast<int32_t*>(outputs[1])),
+                "emb_layer_norm");
+            if (st != BERT_B200_OK || !packed)
+                return st;
+            return abiStatus(bert_b200_convert_mask(S, B, wm, wn, 1, mask, static_cast<uint32_t*>(outputs[1]), stream),
+                "convert_mask");
         }
         catch (std::exception const& e)
         {

@@ -401,7 +401,9 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
 
     // ---- gamma, (beta * q_scale + 128) / 255 and bias as half2 tables in shared memory, built once per CTA: a lane
     //      reads the eight half2 of a chunk with two 128-bit loads per table and row (no conversions in the row loop,
-    //      and no registers held across it: three CTAs fit an SM) ----
+    //      and no registers held across it: three CTAs fit an SM). Each table is two planes - half2 0..3 of every
+    //      chunk, then half2 4..7 - so that consecutive lanes read consecutive 16 bytes (no bank conflicts) ----
+    int const plane = ld / 4; // half2 per plane
     extern __shared__ uint4 paramSmem[];
     __half2* const gTab = reinterpret_cast<__half2*>(paramSmem);
     __half2* const bqTab = gTab + ld / 2;
@@ -411,10 +413,11 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
     {
         float2 const g = __half22float2(reinterpret_cast<__half2 const*>(gamma)[p]);
         float2 const bt = __half22float2(reinterpret_cast<__half2 const*>(beta)[p]);
-        gTab[p] = __floats2half2_rn(g.x, g.y);
-        bqTab[p] = __floats2half2_rn(fmaf(bt.x, qScale, 128.f) * (1.f / 255.f), fmaf(bt.y, qScale, 128.f) * (1.f / 255.f));
+        int const d = ((p >> 2) & 1) * plane + (p >> 3) * 4 + (p & 3);
+        gTab[d] = __floats2half2_rn(g.x, g.y);
+        bqTab[d] = __floats2half2_rn(fmaf(bt.x, qScale, 128.f) * (1.f / 255.f), fmaf(bt.y, qScale, 128.f) * (1.f / 255.f));
         if (HAS_BIAS)
-            biTab[p] = reinterpret_cast<__half2 const*>(bias)[p];
+            biTab[d] = reinterpret_cast<__half2 const*>(bias)[p];
     }
     __syncthreads();
     if (HAS_BIAS)
@@ -467,8 +470,8 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
             if (HAS_BIAS)
             {
                 int const c = min((i * WPR + wInRow) * 32 + lane, chunksPerRow - 1); // chunks beyond the row carry zeros
-                *reinterpret_cast<uint4*>(&bi2[0]) = *reinterpret_cast<uint4 const*>(biTab + c * 8);
-                *reinterpret_cast<uint4*>(&bi2[4]) = *reinterpret_cast<uint4 const*>(biTab + c * 8 + 4);
+                *reinterpret_cast<uint4*>(&bi2[0]) = *reinterpret_cast<uint4 const*>(biTab + c * 4);
+                *reinterpret_cast<uint4*>(&bi2[4]) = *reinterpret_cast<uint4 const*>(biTab + plane + c * 4);
             }
 #pragma unroll
             for (int w = 0; w < 4; ++w)
@@ -535,10 +538,10 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
                 uint4 o;
                 uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
                 __half2 g2[8], bq2[8];
-                *reinterpret_cast<uint4*>(&g2[0]) = *reinterpret_cast<uint4 const*>(gTab + c * 8);
-                *reinterpret_cast<uint4*>(&g2[4]) = *reinterpret_cast<uint4 const*>(gTab + c * 8 + 4);
-                *reinterpret_cast<uint4*>(&bq2[0]) = *reinterpret_cast<uint4 const*>(bqTab + c * 8);
-                *reinterpret_cast<uint4*>(&bq2[4]) = *reinterpret_cast<uint4 const*>(bqTab + c * 8 + 4);
+                *reinterpret_cast<uint4*>(&g2[0]) = *reinterpret_cast<uint4 const*>(gTab + c * 4);
+                *reinterpret_cast<uint4*>(&g2[4]) = *reinterpret_cast<uint4 const*>(gTab + plane + c * 4);
+                *reinterpret_cast<uint4*>(&bq2[0]) = *reinterpret_cast<uint4 const*>(bqTab + c * 4);
+                *reinterpret_cast<uint4*>(&bq2[4]) = *reinterpret_cast<uint4 const*>(bqTab + plane + c * 4);
 #pragma unroll
                 for (int w = 0; w < 4; ++w)
                 {

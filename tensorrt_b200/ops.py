@@ -70,17 +70,27 @@ def skip_layer_norm_interleaved(x, skip, gamma, beta, dq_in, dq_skip, q_scale, q
     return out, preln
 
 
-def emb_layer_norm(input_ids, token_ids, word_emb, pos_emb, tok_emb, gamma, beta, q_scale=None):
-    """Fixed layout: ids [S, B] int32 -> [S, B, E]; optional fused INT8 copy when q_scale is given."""
+def emb_layer_norm(input_ids, token_ids, word_emb, pos_emb, tok_emb, gamma, beta, q_scale=None, mask=None):
+    """Fixed layout: ids [S, B] int32 -> [S, B, E]; optional fused INT8 copy when q_scale is given; with the [S, B] int32
+    `mask` the same launch also returns the mask index [B] (last element of the result)."""
     S, B = input_ids.shape
     ld = word_emb.shape[1]
     out = torch.empty((S, B, ld), dtype=word_emb.dtype, device=word_emb.device)
     out_i8 = torch.empty((S, B, ld), dtype=torch.int8, device=word_emb.device) if q_scale is not None else None
-    check(lib.bert_b200_emb_layer_norm(_stream(), _TYPE_ID[word_emb.dtype], ld, B, S, _ptr(input_ids), _ptr(token_ids),
-                                       _ptr(beta), _ptr(gamma), _ptr(word_emb), _ptr(pos_emb), _ptr(tok_emb),
-                                       word_emb.shape[0], tok_emb.shape[0], pos_emb.shape[0], _ptr(out), _ptr(out_i8),
-                                       q_scale or 0.0), "emb_layer_norm")
-    return out if q_scale is None else (out, out_i8)
+    mask_idx = torch.empty((B,), dtype=torch.int32, device=word_emb.device) if mask is not None else None
+    if mask is not None and (tuple(mask.shape) != (S, B) or mask.dtype != torch.int32 or not mask.is_contiguous()):
+        raise ValueError("mask must be a contiguous int32 [S, B] tensor")
+    check(lib.bert_b200_emb_layer_norm_mask_idx(_stream(), _TYPE_ID[word_emb.dtype], ld, B, S, _ptr(input_ids),
+                                                _ptr(token_ids), _ptr(beta), _ptr(gamma), _ptr(word_emb), _ptr(pos_emb),
+                                                _ptr(tok_emb), word_emb.shape[0], tok_emb.shape[0], pos_emb.shape[0],
+                                                _ptr(out), _ptr(out_i8), q_scale or 0.0, _ptr(mask), _ptr(mask_idx)),
+          "emb_layer_norm")
+    res = [out]
+    if q_scale is not None:
+        res.append(out_i8)
+    if mask is not None:
+        res.append(mask_idx)
+    return res[0] if len(res) == 1 else tuple(res)
 
 
 def emb_layer_norm_var_seqlen(input_ids, token_ids, cu_seqlens, max_seqlen, word_emb, pos_emb, tok_emb, gamma, beta,

@@ -103,6 +103,26 @@ def test_mask_idx_bit_exact(cuda, S, B):
     assert np.array_equal(out, lengths.astype(np.int32))
 
 
+@pytest.mark.parametrize("S,B,E,dtype", [(1, 1, 128, np.float32), (20, 5, 100, np.float32), (128, 32, 768, np.float16),
+                                         (384, 64, 1024, np.float16), (3, 700, 1024, np.float16)])
+def test_mask_idx_from_the_embedding_launch(cuda, S, B, E, dtype):
+    """The fixed-length embedding launch also emits the mask index (more sequences than warps in the grid included);
+    the hidden states are bit-identical to the launch without a mask."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S * B + E)
+    word, pos, tok, gamma, beta = _tables(rng, 1000, 512, E, dtype)
+    ids = rng.integers(0, 1000, size=(S, B)).astype(np.int32)
+    seg = rng.integers(0, 2, size=(S, B)).astype(np.int32)
+    lengths = rng.integers(0, S + 1, size=B)
+    lengths[0] = S
+    mask = (np.arange(S)[:, None] < lengths[None, :]).astype(np.int32)
+    args = [_t(a, cuda) for a in (ids, seg, word, pos, tok, gamma, beta)]
+    out, idx = T.emb_layer_norm(*args, mask=_t(mask, cuda))
+    assert np.array_equal(idx.cpu().numpy(), O.mask_idx(mask))
+    assert torch.equal(out, T.emb_layer_norm(*args))
+
+
 @pytest.mark.parametrize("S,wm,wn", [(64, 2, 2), (96, 2, 2), (128, 2, 2), (384, 1, 8)])
 def test_packed_mask_bit_exact(cuda, S, wm, wn):
     import tensorrt_b200 as T

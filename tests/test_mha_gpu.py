@@ -264,27 +264,30 @@ def test_mha_fp16_long_sequences_on_tensor_cores(cuda, S, d, packed):
     assert ok, (worst, bad)
 
 
-def test_mha_fp16_rescales_when_a_later_block_dominates(cuda):
-    """The online softmax keeps one running maximum per row and rescales the accumulated context when a later key
-    block exceeds it by more than the lazy threshold: keys whose scores grow block by block (by far more than 2^8)
-    exercise that path, keys that grow by less than the threshold the path that keeps the old maximum."""
+@pytest.mark.parametrize("unit", [128, 32, 7])
+@pytest.mark.parametrize("step", [40.0, 3.0, -40.0])
+def test_mha_fp16_running_maximum_moves(cuda, unit, step):
+    """The online softmax keeps one running maximum per row, tracked per chunk of 32 keys, and rescales what the row has
+    accumulated (row sum, context of earlier key blocks, probabilities of the current block written so far) whenever a
+    chunk exceeds it by more than the lazy threshold. Keys whose scores rise by `step` every `unit` keys - per key
+    block, per chunk, or at odd positions inside chunks; by far more than the threshold, by less than it, or falling -
+    exercise every one of those paths."""
     import tensorrt_b200 as T
 
-    rng = np.random.default_rng(99)
+    rng = np.random.default_rng(99 + unit)
     S, B, N, d = 512, 2, 2, 64
-    for step in (40.0, 3.0):                   # score offset per key block, in units of the logit
-        qkv = rng.standard_normal((S, B, N, 3, d)).astype(np.float32)
-        # make q . k / sqrt(d) rise by `step` per key block: one channel carries the ramp
-        qkv[:, :, :, 0, 0] = 8.0
-        qkv[:, :, :, 1, 0] = (np.arange(S) // 128)[:, None, None] * step
-        qkv = qkv.reshape(S, B, -1).astype(np.float16)
-        lengths = np.array([S, 300], dtype=np.int32)
-        ref = O.mha(qkv, B, S, N, d, lengths=lengths)
-        st = _status(cuda)
-        out = T.mha(_t(qkv, cuda), B, S, N, mask_idx=_t(lengths, cuda), status=st)
-        assert int(st[0]) == 0
-        ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
-        assert ok, (step, worst, bad)
+    qkv = rng.standard_normal((S, B, N, 3, d)).astype(np.float32)
+    # q . k / sqrt(d) gets the offset (key index // unit) * step: one channel carries the ramp
+    qkv[:, :, :, 0, 0] = 8.0
+    qkv[:, :, :, 1, 0] = ((np.arange(S) // unit) * step * (unit / 128.0))[:, None, None]
+    qkv = qkv.reshape(S, B, -1).astype(np.float16)
+    lengths = np.array([S, 300], dtype=np.int32)
+    ref = O.mha(qkv, B, S, N, d, lengths=lengths)
+    st = _status(cuda)
+    out = T.mha(_t(qkv, cuda), B, S, N, mask_idx=_t(lengths, cuda), status=st)
+    assert int(st[0]) == 0
+    ok, worst, bad = O.close_abs_or_rel(out.cpu().numpy(), ref, 1e-2, 1e-2)
+    assert ok, (unit, step, worst, bad)
 
 
 def _split_bnsd(qkv, S, B, N, d):
