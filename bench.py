@@ -601,6 +601,21 @@ def run_sweep(args):
             try:
                 row["fp16"]["reference_tflops"] = flops / time_rotating(ref16, sets16) / 1e9
                 row["int8"]["reference_tops"] = flops / time_rotating(ref8, sets8) / 1e9
+                if S in (128, 384):
+                    # the fixed-length kernels of plugin versions 1-3: the same bytes read as [S, B, N, 3, d], full mask
+                    wm, wn = (1, 8) if S == 384 else (2, 2)
+                    xm = -(-S // (16 * wm))
+                    packed = torch.empty((B, xm, wm * wn * 32), dtype=torch.int32, device=dev)
+                    ones = torch.ones((S, B), dtype=torch.int32, device=dev)
+                    ref.lib.ref_convert_mask(S, B, wm, wn, 1, vp(ones.data_ptr()), vp(packed.data_ptr()), None)
+                    torch.cuda.synchronize()
+
+                    def ref_v1(tid, s, a, b, c):
+                        ref.lib.ref_fmha_v1(None, tid, B, S, N, d, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(packed.data_ptr()),
+                                            C.c_float(a), C.c_float(b), C.c_float(c))
+
+                    row["fp16"]["reference_fixed_length_tflops"] = flops / time_rotating(lambda s: ref_v1(1, s, 0.125, 1.0, 1.0), sets16) / 1e9
+                    row["int8"]["reference_fixed_length_tops"] = flops / time_rotating(lambda s: ref_v1(2, s, s1, 127.0, 1.0 / 64), sets8) / 1e9
             except Exception as e:
                 row["reference_error"] = str(e)
         mha.append(row)
@@ -656,6 +671,29 @@ def run_sweep(args):
             row["reference_gbs"] = nbytes / ms / 1e6
         emb.append(row)
     res["emb_layer_norm"] = emb
+
+    # the four FC shapes of a BERT-large layer at 24576 tokens (+ a square one): tera-operations/s per epilogue, operands
+    # rotated; torch.matmul (cuBLAS, FP16, no epilogue) on the same operands as the library bar
+    fc = []
+    for (m, k, n) in ((24576, 1024, 3072), (24576, 1024, 1024), (24576, 1024, 4096), (24576, 4096, 1024), (8192, 8192, 8192)):
+        row = {"m": m, "k": k, "n": n}
+        ops = 2.0 * m * n * k
+        bias = torch.zeros(n, device=dev)
+        s16 = rotating(lambda: (torch.randn(m, k, device=dev).half(), (0.02 * torch.randn(n, k, device=dev)).half(),
+                                torch.empty(m, n, device=dev, dtype=torch.float16)), 2 * (m * k + n * k + m * n))
+        row["fp16"] = ops / time_rotating(lambda t: T.fc(t[0], t[1], out=t[2]), s16) / 1e9
+        row["fp16_bias_gelu"] = ops / time_rotating(lambda t: T.fc(t[0], t[1], bias, T.ACT_GELU_ERF, out=t[2]), s16) / 1e9
+        row["cublas_fp16_matmul"] = ops / time_rotating(lambda t: torch.matmul(t[0], t[1].t(), out=t[2]), s16) / 1e9
+        del s16
+        s8 = rotating(lambda: (torch.randint(-127, 128, (m, k), device=dev, dtype=torch.int8),
+                               torch.randint(-127, 128, (n, k), device=dev, dtype=torch.int8),
+                               torch.empty(m, n, device=dev, dtype=torch.int8)), m * k + n * k + m * n)
+        row["int8"] = ops / time_rotating(lambda t: T.fc(t[0], t[1], alpha=1e-4, out_dtype=torch.int8, out_scale=20.0, out=t[2]), s8) / 1e9
+        row["int8_bias_gelu"] = ops / time_rotating(lambda t: T.fc(t[0], t[1], bias, T.ACT_GELU_ERF, alpha=1e-4, out_dtype=torch.int8,
+                                                                   out_scale=20.0, out=t[2]), s8) / 1e9
+        del s8
+        fc.append(row)
+    res["fc_tera_ops"] = fc
     emit({"sweep": res})
 
 

@@ -37,6 +37,8 @@ def _sources():
     srcs = [REF / s for s in PLUGIN_SOURCES]
     # the precompiled sm100 attention kernels the reference ships as byte arrays (executed, never inspected)
     srcs += sorted((REF / "plugin/bertQKVToContextPlugin/fused_multihead_attention_v2").glob("*kernel.sm100.cpp"))
+    # and the fixed-length kernels of plugin versions 1-3
+    srcs += sorted((REF / "plugin/bertQKVToContextPlugin/fused_multihead_attention").glob("*kernel.sm100.cpp"))
     return srcs
 
 

@@ -18,7 +18,7 @@ class RefLib:
     def __init__(self):
         self.lib = C.CDLL(str(LIB_PATH))
         for n in ("ref_skip_layer_norm", "ref_skip_layer_norm_dqq", "ref_skip_layer_norm_interleaved", "ref_emb_layer_norm",
-                  "ref_emb_layer_norm_var_seqlen", "ref_compute_mask_idx", "ref_convert_mask", "ref_fmha_v2"):
+                  "ref_emb_layer_norm_var_seqlen", "ref_compute_mask_idx", "ref_convert_mask", "ref_fmha_v2", "ref_fmha_v1"):
             getattr(self.lib, n).restype = C.c_int32
 
     @staticmethod
@@ -103,4 +103,18 @@ class RefLib:
         st = self.lib.ref_fmha_v2(self._s(), tid, B, S, N, d, total, self._p(qkv), self._p(out), self._p(cu),
                                   1 if interleaved else 0, C.c_float(s1), C.c_float(ssm), C.c_float(s2))
         self._check(st, "fmha_v2 (precompiled sm100 kernel)")
+        return out
+
+    def fmha_v1(self, qkv, mask, N, d, scales=None):
+        """Fixed-length kernels of plugin versions 1-3: qkv FP16/INT8 [S, B, 3*N*d], mask int32 [S, B] (1 = key
+        present); returns [S, B, N*d]. S in {64, 96, 128, 384} (FP16) or {128, 384} (INT8)."""
+        S, B = mask.shape
+        wm, wn = (1, 8) if S == 384 else (2, 2)
+        packed = self.convert_mask(mask, wm, wn)
+        out = torch.zeros((S, B, N * d), dtype=qkv.dtype, device=qkv.device)
+        tid = 2 if qkv.dtype == torch.int8 else 1
+        s1, ssm, s2 = scales if scales is not None else (d ** -0.5, 1.0, 1.0)
+        st = self.lib.ref_fmha_v1(self._s(), tid, B, S, N, d, self._p(qkv), self._p(out), self._p(packed), C.c_float(s1),
+                                  C.c_float(ssm), C.c_float(s2))
+        self._check(st, "fmha_v1 (precompiled sm100 kernel)")
         return out

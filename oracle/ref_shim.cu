@@ -10,7 +10,9 @@
 // plugin/embLayerNormPlugin/embLayerNormKernel.cu:87-96, 159-183, 237-252, embLayerNormVarSeqlenKernel{HFace,MTron}.cu);
 // the attention kernels are the precompiled sm100 binaries the reference ships, launched through its own
 // FusedMultiHeadAttentionXMMAKernelV2::run (plugin/bertQKVToContextPlugin/fused_multihead_attention_v2/
-// fused_multihead_attention_v2.h:1083-1239) with parameters filled like mhaRunner.cu:985-1035 and :1160-1200.
+// fused_multihead_attention_v2.h:1083-1239) with parameters filled like mhaRunner.cu:985-1035 and :1160-1200; the
+// fixed-length kernels of plugin versions 1-3 through FusedMultiHeadAttentionXMMAKernel::run
+// (fused_multihead_attention/fused_multihead_attention.h) with parameters filled like mhaRunner.cu:653-713 and :797-850.
 #include "bertQKVToContextPlugin/fused_multihead_attention_v2/fused_multihead_attention_v2.h"
 #include <NvInferRuntime.h>
 #include <cuda_fp16.h>
@@ -234,6 +236,59 @@ REF_API int32_t ref_fmha_v2(void* stream, int32_t type_id, int32_t B, int32_t S,
             p.scale_bmm2 = reinterpret_cast<uint32_t const&>(h2);
             p.qkv_stride_in_bytes = 3 * N * d * 2;
             p.o_stride_in_bytes = N * d * 2;
+        }
+        k->run(p, static_cast<cudaStream_t>(stream));
+        return static_cast<int32_t>(cudaPeekAtLastError());
+    }
+    catch (std::exception const& e)
+    {
+        fprintf(stderr, "[reference] %s\n", e.what());
+        return -1;
+    }
+}
+
+// The reference's precompiled sm100 FIXED-LENGTH attention kernels (plugin versions 1-3). qkv is [S][B][N][3][d]
+// (FP16 or INT8), out [S][B][N][d], packed_mask the output of convertMask for the same S and B (warps 2 x 2 for
+// S <= 128, 1 x 8 for S = 384). The runner accepts S in {64, 96, 128, 384} for FP16 and {128, 384} for INT8.
+REF_API int32_t ref_fmha_v1(void* stream, int32_t type_id, int32_t B, int32_t S, int32_t N, int32_t d, void* qkv, void* out,
+    void* packed_mask, float scale_bmm1, float scale_softmax, float scale_bmm2)
+{
+    try
+    {
+        bool const int8 = type_id == 2;
+        if (!(S == 128 || S == 384 || (!int8 && (S == 64 || S == 96))))
+            return -2;
+        FusedMultiHeadAttentionXMMAKernel const* k = getXMMAKernels(int8 ? DATA_TYPE_INT8 : DATA_TYPE_FP16, kSM_100);
+        if (!k || !k->isValid(d, S))
+            return -2;
+        uint32_t const warpsM = S == 384 ? 1 : 2, warpsN = S == 384 ? 8 : 2;
+        uint32_t const threadsPerCta = warpsM * warpsN * 32;
+        uint32_t const xmmasM = (S + 16 * warpsM - 1) / (16 * warpsM);
+        Fused_multihead_attention_params p{};
+        p.b = B;
+        p.h = N;
+        p.s = S;
+        p.d = d;
+        p.qkv_ptr = qkv;
+        p.packed_mask_ptr = packed_mask;
+        p.o_ptr = out;
+        int64_t const elem = int8 ? 1 : 2;
+        p.qkv_stride_in_bytes = static_cast<int64_t>(3) * B * N * d * elem;
+        p.o_stride_in_bytes = static_cast<int64_t>(B) * N * d * elem;
+        p.packed_mask_stride_in_bytes = static_cast<int64_t>(xmmasM) * threadsPerCta * sizeof(uint32_t);
+        if (int8)
+        {
+            p.scale_bmm1 = reinterpret_cast<uint32_t const&>(scale_bmm1);
+            p.scale_bmm2 = reinterpret_cast<uint32_t const&>(scale_bmm2);
+            p.scale_softmax = reinterpret_cast<uint32_t const&>(scale_softmax);
+            p.enable_i2f_trick = -double(1 << 22) * double(scale_bmm2) <= -128.f && double(1 << 22) * double(scale_bmm2) >= 127.f;
+        }
+        else
+        {
+            half2 h1 = __float2half2_rn(scale_bmm1), h2 = __float2half2_rn(1.f);
+            p.scale_bmm1 = reinterpret_cast<uint32_t const&>(h1);
+            p.scale_softmax = reinterpret_cast<uint32_t const&>(h2);
+            p.scale_bmm2 = reinterpret_cast<uint32_t const&>(h2);
         }
         k->run(p, static_cast<cudaStream_t>(stream));
         return static_cast<int32_t>(cudaPeekAtLastError());

@@ -151,6 +151,45 @@ def test_attention_int8_three_way(cuda, ref, S, lengths, interleaved):
     assert close(y_new, y_ref), "product vs reference kernels"
 
 
+@pytest.mark.parametrize("S,lengths,int8", [(128, [128, 77, 5, 128], False), (384, [384, 200, 1], False), (64, [64, 33], False),
+                                            (96, [96, 50], False), (128, [128, 77, 5, 128], True), (384, [384, 200, 1], True)])
+def test_attention_fixed_length_kernels_three_way(cuda, ref, S, lengths, int8):
+    """The fixed-length path of plugin versions 1-3 ([S, B, N, 3, d] input, input mask packed by convertMask): the
+    reference's precompiled fixed-length sm100 kernels, the oracle and the product."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(S + 100 * int8)
+    N, d = 4, 64
+    lengths = np.array(lengths, dtype=np.int32)
+    B = len(lengths)
+    mask = (np.arange(S)[:, None] < lengths[None, :]).astype(np.int32)
+    x = rng.standard_normal((S, B, 3 * N * d))
+    if int8:
+        s_qkv = O.amax_scale(x)
+        q8 = O.quantize(x, 1.0 / s_qkv)
+        s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+        s2 = float((1.0 / 127.0) * s_qkv / (0.5 * s_qkv))
+        y_orc = O.mha_int8(q8, B, S, N, d, s1, 127.0, s2, lengths=lengths)
+        y_ref = ref.fmha_v1(_t(q8, cuda), _t(mask, cuda), N, d, scales=(s1, 127.0, s2)).cpu().numpy()
+        y_new = T.mha(_t(q8, cuda), B, S, N, mask_idx=_t(lengths, cuda), scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=s2).cpu().numpy()
+
+        def close(a, b):
+            dd = np.abs(a.astype(np.int32) - b.astype(np.int32))
+            return dd.max() <= 2 and (dd > 1).sum() <= max(1, int(1e-5 * dd.size)) and (dd == 0).mean() > 0.98
+
+        assert close(y_ref, y_orc), "reference kernels vs oracle"
+        assert close(y_new, y_orc), "product vs oracle"
+        assert close(y_new, y_ref), "product vs reference kernels"
+    else:
+        qkv = x.astype(np.float16)
+        y_orc = O.mha(qkv, B, S, N, d, lengths=lengths)
+        y_ref = ref.fmha_v1(_t(qkv, cuda), _t(mask, cuda), N, d).cpu().numpy()
+        y_new = T.mha(_t(qkv, cuda), B, S, N, mask_idx=_t(lengths, cuda)).cpu().numpy()
+        assert O.close_abs_or_rel(y_ref, y_orc, 1e-2, 1e-2)[0]
+        assert O.close_abs_or_rel(y_new, y_orc, 1e-2, 1e-2)[0]
+        assert O.close_abs_or_rel(y_new, y_ref, 1e-2, 1e-2)[0]
+
+
 @pytest.mark.parametrize("int8", [False, True])
 def test_attention_benchmark_size_three_way(cuda, ref, int8):
     """BERT-large S = 384, 64 sequences x 16 heads, ragged packed lengths: the product against the reference's own
