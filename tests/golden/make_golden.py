@@ -95,6 +95,27 @@ def main(out_path):
     np.savez_compressed(out_path, **g)
     print("wrote", out_path, os.path.getsize(out_path), "bytes,", len(g), "arrays")
 
+    # a file of its own (the arrays above stay byte-identical): the fixed-length kernels of plugin versions 1-3, S = 128,
+    # one head of 64, input mask packed by the reference's convertMask
+    rng = np.random.default_rng(20250101)
+    f = {}
+    N, d, S_ = 1, 64, 128
+    lengths = np.array([128, 45], dtype=np.int32)
+    B = len(lengths)
+    mask = (np.arange(S_)[:, None] < lengths[None, :]).astype(np.int32)
+    xq = rng.standard_normal((S_, B, 3 * N * d))
+    q16 = xq.astype(np.float16)
+    s_qkv = O.amax_scale(xq)
+    q8 = O.quantize(xq, 1.0 / s_qkv)
+    s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(0.125))
+    s2 = float((1.0 / 127.0) * s_qkv / (0.5 * s_qkv))
+    f.update(lengths=lengths, qkv_f16=q16, qkv_i8=q8, i8_scales=np.array([s1, 127.0, s2], dtype=np.float32))
+    f["f16_out"] = ref.fmha_v1(t(q16), t(mask), N, d).cpu().numpy()
+    f["i8_out"] = ref.fmha_v1(t(q8), t(mask), N, d, scales=(s1, 127.0, s2)).cpu().numpy()
+    fixed_path = os.path.join(os.path.dirname(out_path), "reference_kernels_fixed_length.npz")
+    np.savez_compressed(fixed_path, **f)
+    print("wrote", fixed_path, os.path.getsize(fixed_path), "bytes,", len(f), "arrays")
+
 
 if __name__ == "__main__":
     main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_kernels.npz"))
