@@ -167,6 +167,22 @@ def time_forward(fn, steps, warmup, world, dist):
     return e0.elapsed_time(e1) / steps
 
 
+def step_latency(fn, n=100):
+    """Median and 99th percentile of single steps, each between its own pair of CUDA events (N = 1 only; the
+    convention of the reference's own reporting: samples/common/sampleReporting.cpp:232-265)."""
+    import torch
+
+    evs = [_events() for _ in range(n)]
+    torch.cuda.synchronize()
+    for e0, e1 in evs:
+        e0.record()
+        fn()
+        e1.record()
+    torch.cuda.synchronize()
+    t = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+    return {"median": t[len(t) // 2], "p99": t[min(len(t) - 1, int(0.99 * len(t)))], "min": t[0], "samples": n}
+
+
 def kernel_breakdown(enc, ids, seg, cu, out, profile_steps=3):
     """`profile_steps` forwards with every kernel bracketed by CUDA events (same inputs, same stream) to split the
     step by kernel kind. The brackets cost the overlap of consecutive kernels (programmatic dependent launch), so the
@@ -408,13 +424,31 @@ def run_b200(args):
         if sampler and name == args.dtype:
             clocks = sampler.stop()
         status = enc.status_word()
+        lat = step_latency(lambda: enc.forward(ids, seg, cu, SEQ, out=my_out)) if world == 1 else None
+        if lat is not None:
+            # the same forward captured once into a CUDA graph and replayed (170 launches become one): what is left of
+            # the step when the host submits nothing
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    enc.forward(ids, seg, cu, SEQ, out=my_out)
+                    side.synchronize()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        enc.forward(ids, seg, cu, SEQ, out=my_out)
+                torch.cuda.current_stream().wait_stream(side)
+                lat["cuda_graph_replay_ms"] = time_forward(graph.replay, args.steps, 3, 1, None)
+                del graph
+            except Exception as e:
+                lat["cuda_graph_replay_ms"] = f"unavailable: {type(e).__name__}: {e}"
         kind_ms, kind_n = kernel_breakdown(enc, ids, seg, cu, my_out)
         ms_e2e, h2d, d2h = time_e2e(enc, ids, seg, cu, args.steps, 3, world, dist, my_out)
         ms_weak = None
         if world > 1:
             ms_weak = time_forward(lambda: enc.forward(w_ids, w_seg, w_cu, SEQ, out=out), args.steps, args.warmup, world, dist)
             ms, ms_e2e, ms_weak = reduce_max(ms, ms_e2e, ms_weak)
-        results[name] = dict(ms=ms, ms_e2e=ms_e2e, ms_weak=ms_weak, h2d=h2d, d2h=d2h, kind_ms=kind_ms, kind_n=kind_n, status=status,
+        results[name] = dict(ms=ms, ms_e2e=ms_e2e, ms_weak=ms_weak, h2d=h2d, d2h=d2h, kind_ms=kind_ms, kind_n=kind_n, status=status, lat=lat,
                              launches=enc.launches_per_forward)
 
     # ---- config 4: packed variable-length batch, lengths uniform in [32, 384] (seed 1), B = 256, token-balanced shards ----
@@ -503,6 +537,8 @@ def run_b200(args):
         "kernels": breakdown(args.dtype),
         "device_wait_status": main["status"],
     }
+    if main["lat"]:
+        line["step_latency_ms"] = main["lat"]
     if n > 1:
         line["weak"] = {"value": n * BATCH / (main["ms_weak"] * 1e-3), "unit": "seq/s", "ms_per_step": main["ms_weak"],
                         "per_gpu_batch": BATCH, "scaling": "weak"}
@@ -511,6 +547,8 @@ def run_b200(args):
         line[name] = {"value": BATCH / (r["ms"] * 1e-3), "unit": "seq/s", "ms_per_step": r["ms"],
                       "e2e_value": BATCH / (r["ms_e2e"] * 1e-3), "roofline": roofline(name), "kernels": breakdown(name),
                       "device_wait_status": r["status"]}
+        if r["lat"]:
+            line[name]["step_latency_ms"] = r["lat"]
         if n > 1:
             line[name]["weak_value"] = n * BATCH / (r["ms_weak"] * 1e-3)
     tokens4 = int(lengths_all.sum())

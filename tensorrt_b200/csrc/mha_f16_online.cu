@@ -19,14 +19,15 @@
 //   warp 9          : one lane loads K / V blocks (128 keys x 64 channels, 16 KB) into a ring of 12 stages. The
 //                     blocks of an item stay resident for all its query tiles when they fit (S <= 768); longer
 //                     sequences stream their blocks once per pair of query tiles.
-//   warp 10         : one lane issues the scores of both streams,  S = Q K_j^T  (128 x 128, FP32, TMEM columns
-//                     128*stream ..), as soon as the softmax threads hold the previous block in registers.
-//   warp 11         : one lane issues the context products of both streams,  O (+)= P_j V_j  (128 x 64, A operand = P
-//                     straight from TMEM columns 256 + 64*stream .., accumulator in columns 384 + 64*stream ..).
-//                     (Every tcgen05.mma / commit keeps its issuing thread busy for 50-120 cycles; one thread for all
-//                     twelve MMAs and four commits of a block would be the slowest link.)
-//                     Neither issuer ever blocks on one stream: an operand that a loader delivers only after the other
-//                     stream has been served must not stall that other stream.
+//   warps 10 / 11   : one lane each, the MMA thread of stream 0 / 1. It issues the stream's scores  S = Q K_j^T
+//                     (128 x 128, FP32, TMEM columns 128*stream ..) as soon as the softmax threads hold the previous
+//                     block in registers - the first block of the stream's NEXT tile right behind the last block of
+//                     this one -, and the context products  O (+)= P_j V_j  (128 x 64, A operand = P straight from TMEM
+//                     columns 256 + 64*stream .., accumulator in columns 384 + 64*stream ..) as soon as P_j is stored.
+//                     (Every tcgen05.mma / commit keeps its issuing thread busy for 50-120 cycles: the twelve MMAs and
+//                     four commits of a block are a thread's work of its own per stream.) A thread per stream may block
+//                     on its stream's barriers; one thread serving both streams must not - an operand that a loader
+//                     delivers only after the OTHER stream has been served would never arrive.
 // Online softmax: the running maximum m only moves when the block maximum exceeds it by more than 8 in the log2
 // domain (P then stays below 2^8, far inside FP16); when it moves, the softmax threads scale the row sum and the
 // context accumulator in TMEM themselves (after the previous P V product has completed). The final context is
