@@ -264,6 +264,34 @@ def time_rotating(launch, sets, iters=None):
     return e0.elapsed_time(e1) / iters
 
 
+def time_rotating_graph(launch, sets, reps=10):
+    """The same rotation captured once into a CUDA graph (one launch per operand set) and replayed: per-launch time
+    without the host's share (Python, ctypes, tensor-map encoding), which for launches of 10-30 us is as large as the
+    kernel. `launch(set, stream_handle)` must enqueue on the given stream."""
+    import torch
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for t in sets:
+            launch(t, side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for t in sets:
+                launch(t, side.cuda_stream)
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (reps * len(sets))
+
+
 def isolated_skip_ln(T, dev, tokens, ld, int8, bias=True):
     """SkipLayerNorm (+ bias) alone at `tokens` x `ld`, operands rotated beyond the L2: GB/s of algorithmic traffic."""
     import torch
@@ -623,22 +651,24 @@ def run_sweep(args):
         s1 = (amax / 127) ** 2 * 0.125
         row = {"S": S, "B": B, "heads": N, "head_size": d}
         sets16, sets8 = rotating(q16, S * B * 4 * N * d * 2), rotating(q8, S * B * 4 * N * d)
-        ms = time_rotating(lambda s: T.mha(s[0], B, S, N, cu_seqlens=cu), sets16)
+        # attention launches are timed as CUDA-graph replays (ours and the reference's alike)
+        ms = time_rotating_graph(lambda s, st: T.mha(s[0], B, S, N, cu_seqlens=cu, out=s[1]), sets16)
         row["fp16"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_of_bf16_sustained": flops / ms / 1e9 / peaks["tc_sustained"],
                        "hbm_cap_tflops": (S / 2) * peaks["hbm"] / 1e3}
-        ms = time_rotating(lambda s: T.mha(s[0], B, S, N, cu_seqlens=cu, scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=1.0 / 64), sets8)
+        ms = time_rotating_graph(lambda s, st: T.mha(s[0], B, S, N, cu_seqlens=cu, scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=1.0 / 64,
+                                                     out=s[1]), sets8)
         row["int8"] = {"ms": ms, "tops": flops / ms / 1e9, "frac_of_int8_probe": flops / ms / 1e9 / res["peaks"]["int8_mma_tops_probe"]}
         if ref is not None:
-            def ref16(s):
-                ref.lib.ref_fmha_v2(None, 1, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
+            def ref16(s, st):
+                ref.lib.ref_fmha_v2(vp(st), 1, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
                                     C.c_float(0.125), C.c_float(1.0), C.c_float(1.0))
 
-            def ref8(s):
-                ref.lib.ref_fmha_v2(None, 2, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
+            def ref8(s, st):
+                ref.lib.ref_fmha_v2(vp(st), 2, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
                                     C.c_float(s1), C.c_float(127.0), C.c_float(1.0 / 64))
             try:
-                row["fp16"]["reference_tflops"] = flops / time_rotating(ref16, sets16) / 1e9
-                row["int8"]["reference_tops"] = flops / time_rotating(ref8, sets8) / 1e9
+                row["fp16"]["reference_tflops"] = flops / time_rotating_graph(ref16, sets16) / 1e9
+                row["int8"]["reference_tops"] = flops / time_rotating_graph(ref8, sets8) / 1e9
                 if S in (128, 384):
                     # the fixed-length kernels of plugin versions 1-3: the same bytes read as [S, B, N, 3, d], full mask
                     wm, wn = (1, 8) if S == 384 else (2, 2)
@@ -648,12 +678,14 @@ def run_sweep(args):
                     ref.lib.ref_convert_mask(S, B, wm, wn, 1, vp(ones.data_ptr()), vp(packed.data_ptr()), None)
                     torch.cuda.synchronize()
 
-                    def ref_v1(tid, s, a, b, c):
-                        ref.lib.ref_fmha_v1(None, tid, B, S, N, d, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(packed.data_ptr()),
+                    def ref_v1(tid, s, st, a, b, c):
+                        ref.lib.ref_fmha_v1(vp(st), tid, B, S, N, d, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(packed.data_ptr()),
                                             C.c_float(a), C.c_float(b), C.c_float(c))
 
-                    row["fp16"]["reference_fixed_length_tflops"] = flops / time_rotating(lambda s: ref_v1(1, s, 0.125, 1.0, 1.0), sets16) / 1e9
-                    row["int8"]["reference_fixed_length_tops"] = flops / time_rotating(lambda s: ref_v1(2, s, s1, 127.0, 1.0 / 64), sets8) / 1e9
+                    row["fp16"]["reference_fixed_length_tflops"] = flops / time_rotating_graph(
+                        lambda s, st: ref_v1(1, s, st, 0.125, 1.0, 1.0), sets16) / 1e9
+                    row["int8"]["reference_fixed_length_tops"] = flops / time_rotating_graph(
+                        lambda s, st: ref_v1(2, s, st, s1, 127.0, 1.0 / 64), sets8) / 1e9
             except Exception as e:
                 row["reference_error"] = str(e)
         mha.append(row)

@@ -173,19 +173,24 @@ def attention_bnsd(q, k, v, kv_lengths=None, scale_bmm1=None, scale_softmax=1.0,
 
 
 def mha(qkv, B, S, num_heads, head_size=64, cu_seqlens=None, mask_idx=None, scale_bmm1=None, scale_softmax=1.0,
-        scale_bmm2=1.0, status=None, interleaved=False, workspace=None, use_workspace=True):
+        scale_bmm2=1.0, status=None, interleaved=False, workspace=None, use_workspace=True, out=None):
     """Fused attention. qkv: fixed [S, B, 3*N*d] (cu_seqlens None), packed [total, 3*N*d], or with
-    interleaved=True the INT8 CHW32 form [3*N*d/32, total, 32] (output [N*d/32, total, 32])."""
+    interleaved=True the INT8 CHW32 form [3*N*d/32, total, 32] (output [N*d/32, total, 32]). `out`: a tensor of the
+    output's shape and type to write into instead of a new one."""
     E = num_heads * head_size
     if interleaved:
         total = qkv.shape[1]
-        out = torch.empty((E // 32, total, 32), dtype=qkv.dtype, device=qkv.device)
+        shape = (E // 32, total, 32)
     elif cu_seqlens is None:
-        out = torch.empty((S, B, E), dtype=qkv.dtype, device=qkv.device)
+        shape = (S, B, E)
         total = 0
     else:
         total = qkv.shape[0]
-        out = torch.empty((total, E), dtype=qkv.dtype, device=qkv.device)
+        shape = (total, E)
+    if out is None:
+        out = torch.empty(shape, dtype=qkv.dtype, device=qkv.device)
+    elif tuple(out.shape) != shape or out.dtype != qkv.dtype or not out.is_contiguous():
+        raise ValueError(f"out must be a contiguous {qkv.dtype} tensor of shape {shape}")
     if scale_bmm1 is None:
         scale_bmm1 = head_size ** -0.5
     p = _lib.MhaParams(_TYPE_ID[qkv.dtype], B, S, num_heads, head_size, total, _ptr(qkv), _ptr(out), _ptr(cu_seqlens),
