@@ -308,10 +308,11 @@ def isolated_skip_ln(T, dev, tokens, ld, int8, bias=True):
         return x, torch.randn(tokens, ld, device=dev).half(), torch.empty_like(x)
 
     sets = rotating(make, 3 * tokens * ld * elem)
+    # replayed from a CUDA graph: up to a few hundred thousand tokens the launch is shorter than the host's enqueue
     if int8:
-        ms = time_rotating(lambda s: T.skip_layer_norm_dqq(s[0], s[1], g, b, b if bias else None, 0.02, 0.02, 40.0, out=s[2]), sets)
+        ms = time_rotating_graph(lambda s, st: T.skip_layer_norm_dqq(s[0], s[1], g, b, b if bias else None, 0.02, 0.02, 40.0, out=s[2]), sets)
     else:
-        ms = time_rotating(lambda s: T.skip_layer_norm(s[0], s[1], g, b, bias=b if bias else None, out=s[2]), sets)
+        ms = time_rotating_graph(lambda s, st: T.skip_layer_norm(s[0], s[1], g, b, bias=b if bias else None, out=s[2]), sets)
     return ms, 3 * tokens * ld * elem / (ms * 1e-3) / 1e9
 
 
@@ -705,16 +706,16 @@ def run_sweep(args):
                 g = torch.ones(ld, device=dev).half()
                 sets = rotating(lambda: (torch.randn(tokens, ld, device=dev).half(), torch.randn(tokens, ld, device=dev).half(),
                                          torch.empty(tokens, ld, device=dev).half()), 6 * tokens * ld)
-                ms = time_rotating(lambda s: ref.lib.ref_skip_layer_norm(None, 1, ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()),
-                                                                         vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()), vp(g.data_ptr())), sets)
+                ms = time_rotating_graph(lambda s, st: ref.lib.ref_skip_layer_norm(vp(st), 1, ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()),
+                                                                                   vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()), vp(g.data_ptr())), sets)
                 row["fp16"]["reference_gbs"] = 6 * tokens * ld / ms / 1e6
                 if ld != 4096:  # the reference's INT8 kernel exists for 768 and 1024 only
                     sets = rotating(lambda: (torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8),
                                              torch.randint(-127, 127, (tokens, ld), device=dev, dtype=torch.int8),
                                              torch.empty(tokens, ld, device=dev, dtype=torch.int8)), 3 * tokens * ld)
-                    ms = time_rotating(lambda s: ref.lib.ref_skip_layer_norm_dqq(None, ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()),
-                                                                                 vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()), vp(g.data_ptr()),
-                                                                                 C.c_float(0.02), C.c_float(0.02), C.c_float(40.0)), sets)
+                    ms = time_rotating_graph(lambda s, st: ref.lib.ref_skip_layer_norm_dqq(
+                        vp(st), ld, tokens * ld, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()),
+                        vp(g.data_ptr()), C.c_float(0.02), C.c_float(0.02), C.c_float(40.0)), sets)
                     row["int8"]["reference_gbs"] = 3 * tokens * ld / ms / 1e6
             ln.append(row)
     res["skip_layer_norm_bias"] = ln
@@ -729,15 +730,15 @@ def run_sweep(args):
     for S, B in ((128, 32), (384, 64), (384, 512)):
         sets = rotating(lambda: (torch.randint(0, vocab, (S, B), device=dev, dtype=torch.int32),
                                  torch.randint(0, 2, (S, B), device=dev, dtype=torch.int32)), S * B * (2 * E * 2 + 8), min_total=0)
-        ms = time_rotating(lambda s: T.emb_layer_norm(s[0], s[1], word, pos, tok, gam, bet), sets, iters=40)
+        ms = time_rotating_graph(lambda s, st: T.emb_layer_norm(s[0], s[1], word, pos, tok, gam, bet), sets)
         nbytes = S * B * (2 * E * 2 + 8)
         row = {"S": S, "B": B, "tokens": S * B, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm"],
                "note": "62 MB word table, random rows: every launch gathers different rows; the output (2 KB per token) is written once"}
         if ref is not None:
             outr = torch.empty(S, B, E, device=dev, dtype=torch.float16)
-            ms = time_rotating(lambda s: ref.lib.ref_emb_layer_norm(None, 1, E, B, S, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(bet.data_ptr()),
-                                                                    vp(gam.data_ptr()), vp(word.data_ptr()), vp(pos.data_ptr()), vp(tok.data_ptr()),
-                                                                    vocab, 2, vp(outr.data_ptr())), sets, iters=40)
+            ms = time_rotating_graph(lambda s, st: ref.lib.ref_emb_layer_norm(
+                vp(st), 1, E, B, S, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(bet.data_ptr()), vp(gam.data_ptr()), vp(word.data_ptr()),
+                vp(pos.data_ptr()), vp(tok.data_ptr()), vocab, 2, vp(outr.data_ptr())), sets)
             row["reference_gbs"] = nbytes / ms / 1e6
         emb.append(row)
     res["emb_layer_norm"] = emb
