@@ -133,6 +133,19 @@ __device__ __forceinline__ void stgStream(void* p, uint4 v)
                  : "memory");
 }
 
+// 64-bit forms of the two above (rows whose length is a multiple of 8 bytes but fills 16-byte chunks unevenly).
+__device__ __forceinline__ uint2 ldgStream8(void const* p)
+{
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void stgStream8(void* p, uint2 v)
+{
+    asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
 __device__ __forceinline__ void unpackHalf8(uint4 const& v, float (&f)[8])
 {
     __half2 const* h = reinterpret_cast<__half2 const*>(&v);

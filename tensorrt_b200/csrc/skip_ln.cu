@@ -362,13 +362,17 @@ __global__ void __launch_bounds__(kThreads) skipLnDqqKernel(int32_t const ld, in
 //   * gamma, beta (pre-scaled) and bias sit as half2 tables in shared memory, built once per CTA (no per-row parameter
 //     conversions); the lanes of a row add their integer sums with redux.sync.
 // Every value is within 1 LSB of the exact result (the FP16 steps add up to a few tenths of an LSB at most).
-template <int CPL, int WPR, bool HAS_BIAS>
+// CB = bytes per chunk: 16, or 8 for rows that fill 16-byte chunks unevenly (768 = 48 chunks of 16 for 32 lanes, but
+// exactly three chunks of 8 per lane).
+template <int CPL, int WPR, bool HAS_BIAS, int CB = 16>
 __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t const ld, int64_t const rows,
     int8_t const* __restrict__ in, int8_t const* __restrict__ skip, __half const* __restrict__ beta,
     __half const* __restrict__ gamma, __half const* __restrict__ bias, int8_t* __restrict__ out, float const dqIn,
     float const dqSkip, float const qScale, float const eps)
 {
-    constexpr int E = 16;
+    constexpr int E = CB;
+    constexpr int kWords = CB / 4;     // 32-bit words (four INT8 values each) per chunk
+    constexpr int kPairs = CB / 2;     // half2 values per chunk
     constexpr int kRowsPerCta = kWarpsPerCta / WPR;
     __shared__ float2 red[kRowsPerCta][2][WPR > 1 ? WPR : 1];
     int turn = 0;
@@ -403,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
     //      reads the eight half2 of a chunk with two 128-bit loads per table and row (no conversions in the row loop,
     //      and no registers held across it: three CTAs fit an SM). Each table is two planes - half2 0..3 of every
     //      chunk, then half2 4..7 - so that consecutive lanes read consecutive 16 bytes (no bank conflicts) ----
-    int const plane = ld / 4; // half2 per plane
+    int const plane = ld / 4; // half2 per plane (16-byte chunks; an 8-byte chunk is one 128-bit table read already)
     extern __shared__ uint4 paramSmem[];
     __half2* const gTab = reinterpret_cast<__half2*>(paramSmem);
     __half2* const bqTab = gTab + ld / 2;
@@ -413,7 +417,7 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
     {
         float2 const g = __half22float2(reinterpret_cast<__half2 const*>(gamma)[p]);
         float2 const bt = __half22float2(reinterpret_cast<__half2 const*>(beta)[p]);
-        int const d = ((p >> 2) & 1) * plane + (p >> 3) * 4 + (p & 3);
+        int const d = CB == 16 ? ((p >> 2) & 1) * plane + (p >> 3) * 4 + (p & 3) : p;
         gTab[d] = __floats2half2_rn(g.x, g.y);
         bqTab[d] = __floats2half2_rn(fmaf(bt.x, qScale, 128.f) * (1.f / 255.f), fmaf(bt.y, qScale, 128.f) * (1.f / 255.f));
         if (HAS_BIAS)
@@ -449,32 +453,45 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
          row += static_cast<int64_t>(gridDim.x) * kRowsPerCta)
     {
         bool const rowOk = row < rows;
-        uint4 a[CPL], b[CPL];
+        uint32_t a[CPL][kWords], b[CPL][kWords];
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
             int const c = (i * WPR + wInRow) * 32 + lane;
             bool const ok = rowOk && c < chunksPerRow;
-            a[i] = ok ? ldgStream(in + row * ld + c * E) : make_uint4(0, 0, 0, 0);
-            b[i] = ok ? ldgStream(skip + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+            if (CB == 16)
+            {
+                uint4 const va = ok ? ldgStream(in + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+                uint4 const vb = ok ? ldgStream(skip + row * ld + c * E) : make_uint4(0, 0, 0, 0);
+                a[i][0] = va.x, a[i][1] = va.y, a[i][kWords - 2] = va.z, a[i][kWords - 1] = va.w;
+                b[i][0] = vb.x, b[i][1] = vb.y, b[i][kWords - 2] = vb.z, b[i][kWords - 1] = vb.w;
+            }
+            else
+            {
+                uint2 const va = ok ? ldgStream8(in + row * ld + c * E) : make_uint2(0, 0);
+                uint2 const vb = ok ? ldgStream8(skip + row * ld + c * E) : make_uint2(0, 0);
+                a[i][0] = va.x, a[i][1] = va.y;
+                b[i][0] = vb.x, b[i][1] = vb.y;
+            }
         }
         int32_t sa = 0, sb = 0, saa = 0, sbb = 0, sab = 0;
         __half2 cross0 = __float2half2_rn(0.f), cross1 = cross0;
-        __half2 x2[CPL][8];
+        __half2 x2[CPL][kPairs];
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
-            uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
-            uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
-            __half2 bi2[8];
+            uint32_t const* aw = a[i];
+            uint32_t const* bw = b[i];
+            __half2 bi2[kPairs];
             if (HAS_BIAS)
             {
                 int const c = min((i * WPR + wInRow) * 32 + lane, chunksPerRow - 1); // chunks beyond the row carry zeros
                 *reinterpret_cast<uint4*>(&bi2[0]) = *reinterpret_cast<uint4 const*>(biTab + c * 4);
-                *reinterpret_cast<uint4*>(&bi2[4]) = *reinterpret_cast<uint4 const*>(biTab + plane + c * 4);
+                if (CB == 16)
+                    *reinterpret_cast<uint4*>(&bi2[kPairs - 4]) = *reinterpret_cast<uint4 const*>(biTab + plane + c * 4);
             }
 #pragma unroll
-            for (int w = 0; w < 4; ++w)
+            for (int w = 0; w < kWords; ++w)
             {
                 int32_t const ia = static_cast<int32_t>(aw[w]), ib = static_cast<int32_t>(bw[w]);
                 sa = __dp4a(ia, 0x01010101, sa);
@@ -535,15 +552,17 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
             int const c = (i * WPR + wInRow) * 32 + lane;
             if (rowOk && c < chunksPerRow)
             {
-                uint4 o;
-                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-                __half2 g2[8], bq2[8];
+                uint32_t ow[kWords];
+                __half2 g2[kPairs], bq2[kPairs];
                 *reinterpret_cast<uint4*>(&g2[0]) = *reinterpret_cast<uint4 const*>(gTab + c * 4);
-                *reinterpret_cast<uint4*>(&g2[4]) = *reinterpret_cast<uint4 const*>(gTab + plane + c * 4);
                 *reinterpret_cast<uint4*>(&bq2[0]) = *reinterpret_cast<uint4 const*>(bqTab + c * 4);
-                *reinterpret_cast<uint4*>(&bq2[4]) = *reinterpret_cast<uint4 const*>(bqTab + plane + c * 4);
+                if (CB == 16)
+                {
+                    *reinterpret_cast<uint4*>(&g2[kPairs - 4]) = *reinterpret_cast<uint4 const*>(gTab + plane + c * 4);
+                    *reinterpret_cast<uint4*>(&bq2[kPairs - 4]) = *reinterpret_cast<uint4 const*>(bqTab + plane + c * 4);
+                }
 #pragma unroll
-                for (int w = 0; w < 4; ++w)
+                for (int w = 0; w < kWords; ++w)
                 {
                     uint32_t r[2];
 #pragma unroll
@@ -557,7 +576,10 @@ __global__ void __launch_bounds__(kThreads, 3) skipLnDqqPackedKernel(int32_t con
                     }
                     ow[w] = __byte_perm(r[0], r[1], 0x6420);
                 }
-                stgStream(out + row * ld + c * E, o);
+                if (CB == 16)
+                    stgStream(out + row * ld + c * E, make_uint4(ow[0], ow[1], ow[kWords - 2], ow[kWords - 1]));
+                else
+                    stgStream8(out + row * ld + c * E, make_uint2(ow[0], ow[1]));
             }
         }
     }
@@ -802,6 +824,22 @@ int32_t launchDqq(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* i
     return checkLaunch("skipLnDqqKernel");
 }
 
+// One row per warp in 8-byte chunks, CPL of them per lane (see the kernel): rows such as 768 or 256 INT8 values.
+template <int CPL>
+int32_t launchDqq8(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* in, int8_t const* skip, __half const* beta,
+    __half const* gamma, __half const* bias, int8_t* out, float dqIn, float dqSkip, float qScale)
+{
+    int const grid = gridFor((rows + kWarpsPerCta - 1) / kWarpsPerCta, 3);
+    size_t const smem = static_cast<size_t>(ld) * 2 * 3;
+    if (bias)
+        launchDependent(skipLnDqqPackedKernel<CPL, 1, true, 8>, dim3(grid), dim3(kThreads), smem, stream, ld, rows, in, skip, beta,
+            gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+    else
+        launchDependent(skipLnDqqPackedKernel<CPL, 1, false, 8>, dim3(grid), dim3(kThreads), smem, stream, ld, rows, in, skip, beta,
+            gamma, bias, out, dqIn, dqSkip, qScale, 0.f);
+    return checkLaunch("skipLnDqqPackedKernel");
+}
+
 template <bool PRELN>
 int32_t launchInterleaved(cudaStream_t stream, int32_t ld, int32_t total, int8_t const* in, int8_t const* skip,
     __half const* beta, __half const* gamma, int8_t* out, int8_t* preln, float dqIn, float dqSkip, float qScale,
@@ -884,6 +922,16 @@ extern "C" int32_t bert_b200_skip_layer_norm_dqq(void* stream, int32_t ld, int64
     auto const* b = static_cast<__half const*>(beta);
     auto const* g = static_cast<__half const*>(gamma);
     auto const* bi = static_cast<__half const*>(bias);
+    // A row that leaves lanes idle in 16-byte chunks but is a whole number of 8-byte chunks per lane (768 = 3 x 32 x 8,
+    // 256 = 32 x 8) takes the 8-byte form of the packed kernel: every lane has the same amount of work.
+    if (chunks % 32 != 0 && (ld / 8) % 32 == 0 && ld / 8 <= 32 * 3)
+    {
+        int const cpl8 = ld / 8 / 32;
+        if (cpl8 == 1)
+            return launchDqq8<1>(s, ld, n / ld, input, skip, b, g, bi, output, dq_scale_in, dq_scale_skip, q_scale);
+        if (cpl8 == 3)
+            return launchDqq8<3>(s, ld, n / ld, input, skip, b, g, bi, output, dq_scale_in, dq_scale_skip, q_scale);
+    }
 #define B200_DQQ_CASE(C, W)                                                                                            \
     if (cpl == C && wpr == W)                                                                                          \
         return launchDqq<C, W>(s, ld, n / ld, input, skip, b, g, bi, output, dq_scale_in, dq_scale_skip, q_scale);
