@@ -92,7 +92,7 @@ __device__ __forceinline__ void maskIdxOfSequence(int32_t const S, int32_t const
 // index of every sequence (the second output of the fixed-length embedding plugin), one warp per sequence after the
 // warp's share of the rows.
 template <typename T, int CPL, int WPR, bool PACKED>
-__global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_t const B, int32_t const tokens,
+__global__ void __launch_bounds__(kThreads, 4) embLnKernel(int32_t const ld, int32_t const B, int32_t const tokens,
     int32_t const* __restrict__ inputIds, int32_t const* __restrict__ tokenIds, int32_t const* __restrict__ cuSeqlens,
     float const* __restrict__ beta, float const* __restrict__ gamma, T const* __restrict__ wordEmb,
     T const* __restrict__ posEmb, T const* __restrict__ tokEmb, int32_t const wordSize, int32_t const tokSize, int32_t const posSize,
@@ -111,11 +111,10 @@ __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_
     float const rld = 1.f / static_cast<float>(ld);
 
     int const tokensRounded = (tokens + kTokPerCta - 1) / kTokPerCta * kTokPerCta;
-    for (int t = blockIdx.x * kTokPerCta + tokInCta; t < tokensRounded; t += gridDim.x * kTokPerCta)
-    {
-        bool const tokOk = t < tokens;
-        int wordId = 0, segId = 0, pos = 0;
-        if (tokOk)
+    // ids and position of token t (zeros beyond the last token)
+    auto fetchIds = [&](int t, int& wordId, int& segId, int& pos) {
+        wordId = 0, segId = 0, pos = 0;
+        if (t < tokens)
         {
             wordId = __ldg(inputIds + t);
             segId = __ldg(tokenIds + t);
@@ -138,6 +137,16 @@ __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_
                 pos = t / B;
             }
         }
+    };
+    // The gather is a chain of two dependent reads per token (id, then the row): the ids of the warp's NEXT token are
+    // fetched while the rows of the current one are in flight, so only the row read stays on the chain.
+    int const tStride = gridDim.x * kTokPerCta;
+    int nextWord, nextSeg, nextPos;
+    fetchIds(blockIdx.x * kTokPerCta + tokInCta, nextWord, nextSeg, nextPos);
+    for (int t = blockIdx.x * kTokPerCta + tokInCta; t < tokensRounded; t += tStride)
+    {
+        bool const tokOk = t < tokens;
+        int const wordId = nextWord, segId = nextSeg, pos = nextPos;
         // ids or a position outside their tables (a sequence longer than the position table, a cu_seqlens that does not
         // start at 0 or runs backwards) read nothing: such a token produces the row `beta`
         bool const idOk = tokOk && wordId >= 0 && wordId < wordSize && segId >= 0 && segId < tokSize && pos >= 0 && pos < posSize;
@@ -152,6 +161,8 @@ __global__ void __launch_bounds__(kThreads) embLnKernel(int32_t const ld, int32_
             bool const ok = idOk && c < chunksPerRow;
             w[i] = ok ? ldgStream(wordEmb + static_cast<int64_t>(wordId) * ld + c * E) : make_uint4(0, 0, 0, 0);
         }
+        if (t + tStride < tokensRounded)
+            fetchIds(t + tStride, nextWord, nextSeg, nextPos);
 #pragma unroll
         for (int i = 0; i < CPL; ++i)
         {
