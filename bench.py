@@ -264,6 +264,12 @@ def time_rotating(launch, sets, iters=None):
     return e0.elapsed_time(e1) / iters
 
 
+def _product_lib():
+    from tensorrt_b200._lib import lib
+
+    return lib
+
+
 def time_rotating_graph(launch, sets, reps=10):
     """The same rotation captured once into a CUDA graph (one launch per operand set) and replayed: per-launch time
     without the host's share (Python, ctypes, tensor-map encoding), which for launches of 10-30 us is as large as the
@@ -719,6 +725,27 @@ def run_sweep(args):
                     row["int8"]["reference_gbs"] = 3 * tokens * ld / ms / 1e6
             ln.append(row)
     res["skip_layer_norm_bias"] = ln
+
+    # INT8 SkipLayerNorm on the CHW32-interleaved layout of plugin versions 7 / 8 (no bias), hidden 1024
+    il = []
+    for tokens in (24576, 262144):
+        ld = 1024
+        g = torch.ones(ld, device=dev).half()
+        sets = rotating(lambda: (torch.randint(-127, 127, (ld // 32, tokens, 32), device=dev, dtype=torch.int8),
+                                 torch.randint(-127, 127, (ld // 32, tokens, 32), device=dev, dtype=torch.int8),
+                                 torch.empty((ld // 32, tokens, 32), device=dev, dtype=torch.int8)), 3 * tokens * ld)
+        nbytes = 3 * tokens * ld
+        ms = time_rotating_graph(lambda s, st: _product_lib().bert_b200_skip_layer_norm_interleaved_hface(
+            vp(st), ld, tokens, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()),
+            C.c_float(0.02), C.c_float(0.02), C.c_float(40.0)), sets)
+        row = {"hidden": ld, "tokens": tokens, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm"]}
+        if ref is not None:
+            ms = time_rotating_graph(lambda s, st: ref.lib.ref_skip_layer_norm_interleaved(
+                vp(st), 1, ld, tokens, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(g.data_ptr()), vp(g.data_ptr()), vp(s[2].data_ptr()),
+                None, C.c_float(0.02), C.c_float(0.02), C.c_float(40.0), C.c_float(1.0)), sets)
+            row["reference_gbs"] = nbytes / ms / 1e6
+        il.append(row)
+    res["skip_layer_norm_interleaved"] = il
 
     # embedding gather + LayerNorm: vocab 30522, hidden 1024, FP16 tables; bytes = word row in + row out + two ids
     E, vocab = 1024, 30522

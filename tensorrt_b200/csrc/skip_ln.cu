@@ -742,6 +742,171 @@ __global__ void __launch_bounds__(kThreads) skipLnInterleavedKernel(int32_t cons
     }
 }
 
+// The same operator with the arithmetic of skipLnDqqPackedKernel: exact integer statistics by dp4a (one reduction and
+// one barrier per tile instead of two), the element-wise part in half2 with the clamp as the saturation of the FMA,
+// gamma and beta as half2 tables in shared memory (two planes, conflict-free 128-bit reads), and the next tile's loads
+// issued as soon as this tile's bytes are unpacked. Thread (group g = tid / 16 + 16 i, token tid % 16 / 2, half tid % 2)
+// owns 16 channels of one token, as above; NI <= 4 (ld <= 2048).
+template <int NI, bool PRELN>
+__global__ void __launch_bounds__(kThreads, NI <= 2 ? 3 : 2) skipLnInterleavedPackedKernel(int32_t const ld,
+    int32_t const total, int8_t const* __restrict__ in, int8_t const* __restrict__ skip, __half const* __restrict__ beta,
+    __half const* __restrict__ gamma, int8_t* __restrict__ out, int8_t* __restrict__ preln, float const dqIn,
+    float const dqSkip, float const qScale, float const qSkipScale, float const eps)
+{
+    __shared__ float2 red[2][kWarpsPerCta][kIlTokens];
+    extern __shared__ uint4 paramSmem[];
+    __half2* const gTab = reinterpret_cast<__half2*>(paramSmem);
+    __half2* const bqTab = gTab + ld / 2;
+    int const tid = threadIdx.x;
+    int const lane = tid & 31;
+    int const warp = tid >> 5;
+    int const unit = tid & 15;
+    int const tokInCta = unit >> 1;
+    int const half = unit & 1;
+    int const groups = ld / 32;
+    float const rld = 1.f / static_cast<float>(ld);
+    int const numTiles = (total + kIlTokens - 1) / kIlTokens;
+    int const plane = ld / 4; // half2 per plane: half2 0..3 of every 16-channel chunk, then half2 4..7
+
+    for (int p = tid; p < ld / 2; p += kThreads)
+    {
+        float2 const g = __half22float2(reinterpret_cast<__half2 const*>(gamma)[p]);
+        float2 const bt = __half22float2(reinterpret_cast<__half2 const*>(beta)[p]);
+        int const d = ((p >> 2) & 1) * plane + (p >> 3) * 4 + (p & 3);
+        gTab[d] = __floats2half2_rn(g.x, g.y);
+        bqTab[d] = __floats2half2_rn(fmaf(bt.x, qScale, 128.f) * (1.f / 255.f), fmaf(bt.y, qScale, 128.f) * (1.f / 255.f));
+    }
+    __syncthreads();
+    __half2 const dqIn2 = __float2half2_rn(dqIn), dqSkip2 = __float2half2_rn(dqSkip);
+    // the integer sums are weighted with the scales the element-wise part actually multiplies by
+    float const dqInH = __low2float(dqIn2), dqSkipH = __low2float(dqSkip2);
+    __half2 const kMagic = __float2half2_rn(1152.f); // 1024 + 128: exponent byte 0x64 over (byte ^ 0x80)
+    __half2 const k255 = __float2half2_rn(255.f), k1408 = __float2half2_rn(1408.f);
+    __half2 const kPre1 = __float2half2_rn(qSkipScale * (1.f / 255.f)), kPre0 = __float2half2_rn(128.f / 255.f);
+    int turn = 0;
+
+    uint4 a[NI], b[NI];
+    auto loadTile = [&](int tile) {
+        int const tok = tile * kIlTokens + tokInCta;
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            int const g = (tid >> 4) + 16 * i;
+            bool const ok = tok < total && g < groups;
+            int64_t const off = (static_cast<int64_t>(g) * total + tok) * 32 + half * 16;
+            a[i] = ok ? ldgStream(in + off) : make_uint4(0, 0, 0, 0);
+            b[i] = ok ? ldgStream(skip + off) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    if (static_cast<int>(blockIdx.x) < numTiles)
+        loadTile(blockIdx.x);
+    for (int tile = blockIdx.x; tile < numTiles; tile += gridDim.x)
+    {
+        int const tok = tile * kIlTokens + tokInCta;
+        bool const tokOk = tok < total;
+        int32_t sa = 0, sb = 0, saa = 0, sbb = 0, sab = 0;
+        __half2 x2[NI][8];
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            uint32_t const* aw = reinterpret_cast<uint32_t const*>(&a[i]);
+            uint32_t const* bw = reinterpret_cast<uint32_t const*>(&b[i]);
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+            {
+                int32_t const ia = static_cast<int32_t>(aw[w]), ib = static_cast<int32_t>(bw[w]);
+                sa = __dp4a(ia, 0x01010101, sa);
+                sb = __dp4a(ib, 0x01010101, sb);
+                saa = __dp4a(ia, ia, saa);
+                sbb = __dp4a(ib, ib, sbb);
+                sab = __dp4a(ia, ib, sab);
+                uint32_t const ua = aw[w] ^ 0x80808080u, ub = bw[w] ^ 0x80808080u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                {
+                    uint32_t const am = __byte_perm(ua, 0x64646464u, h == 0 ? 0x5140 : 0x7362);
+                    uint32_t const bm = __byte_perm(ub, 0x64646464u, h == 0 ? 0x5140 : 0x7362);
+                    __half2 const fa = __hsub2(*reinterpret_cast<__half2 const*>(&am), kMagic);
+                    __half2 const fb = __hsub2(*reinterpret_cast<__half2 const*>(&bm), kMagic);
+                    x2[i][2 * w + h] = __hfma2(dqIn2, fa, __hmul2(dqSkip2, fb));
+                }
+            }
+        }
+        if (tile + static_cast<int>(gridDim.x) < numTiles)
+            loadTile(tile + gridDim.x);
+        // sums of this thread's 16 * NI channels; lanes with equal token differ in lane bit 0 (half) and bit 4 (group parity)
+        float s1 = fmaf(dqInH, static_cast<float>(sa), dqSkipH * static_cast<float>(sb));
+        float s2 = fmaf(dqInH * dqInH, static_cast<float>(saa),
+            fmaf(dqSkipH * dqSkipH, static_cast<float>(sbb), 2.f * dqInH * dqSkipH * static_cast<float>(sab)));
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+        s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+        if ((lane & 17) == 0)
+            red[turn][warp][tokInCta] = make_float2(s1, s2);
+        __syncthreads();
+        float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarpsPerCta; ++w)
+        {
+            float2 const r = red[turn][w][tokInCta];
+            t1 += r.x;
+            t2 += r.y;
+        }
+        // the other buffer next time: its readers of two tiles ago have all passed the barrier of the last tile
+        turn ^= 1;
+        float const mu = t1 * rld;
+        float const rsigma = rsqrtf(fmaxf(fmaf(t2, rld, -mu * mu), 0.f) + eps);
+        // (gamma (x - mu) rsigma + beta) q_scale, shifted and scaled to [0, 1] <-> [-128, 127]
+        __half2 const k1 = __float2half2_rn(rsigma * qScale * (1.f / 255.f));
+        __half2 const negMu = __float2half2_rn(-mu);
+#pragma unroll
+        for (int i = 0; i < NI; ++i)
+        {
+            int const g = (tid >> 4) + 16 * i;
+            if (tokOk && g < groups)
+            {
+                int64_t const off = (static_cast<int64_t>(g) * total + tok) * 32 + half * 16;
+                int const c = g * 2 + half; // 16-channel chunk of the row
+                uint4 o, pre;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&pre);
+                __half2 g2[8], bq2[8];
+                *reinterpret_cast<uint4*>(&g2[0]) = *reinterpret_cast<uint4 const*>(gTab + c * 4);
+                *reinterpret_cast<uint4*>(&g2[4]) = *reinterpret_cast<uint4 const*>(gTab + plane + c * 4);
+                *reinterpret_cast<uint4*>(&bq2[0]) = *reinterpret_cast<uint4 const*>(bqTab + c * 4);
+                *reinterpret_cast<uint4*>(&bq2[4]) = *reinterpret_cast<uint4 const*>(bqTab + plane + c * 4);
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+                {
+                    uint32_t r[2], rp[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+                    {
+                        __half2 const c1 = __hmul2(g2[2 * w + h], k1);
+                        __half2 const c0 = __hfma2(c1, negMu, bq2[2 * w + h]);
+                        __half2 const v = __hfma2_sat(c1, x2[i][2 * w + h], c0);
+                        __half2 const q = __hfma2(v, k255, k1408); // round to nearest even; the integer sits in the low byte
+                        r[h] = *reinterpret_cast<uint32_t const*>(&q);
+                        if (PRELN)
+                        {
+                            __half2 const vp = __hfma2_sat(kPre1, x2[i][2 * w + h], kPre0);
+                            __half2 const qp = __hfma2(vp, k255, k1408);
+                            rp[h] = *reinterpret_cast<uint32_t const*>(&qp);
+                        }
+                    }
+                    ow[w] = __byte_perm(r[0], r[1], 0x6420);
+                    if (PRELN)
+                        pw[w] = __byte_perm(rp[0], rp[1], 0x6420);
+                }
+                stgStream(out + off, o);
+                if (PRELN)
+                    stgStream(preln + off, pre);
+            }
+        }
+    }
+}
+
 // Grid for a grid-stride loop over `groups` units of work with at most ctasPerSm CTAs per SM: every CTA takes the same
 // number of passes (the last pass may be short for a few), instead of a grid of exactly the cap in which some CTAs
 // make one pass more than the others and the rest idle meanwhile (24576 rows: 7 passes against 6 for a third of them).
@@ -872,6 +1037,20 @@ int32_t launchInterleaved(cudaStream_t stream, int32_t ld, int32_t total, int8_t
     // The large interleaved reference kernels add FP32 epsilon
     // (plugin/skipLayerNormPlugin/skipLayerNormInt8InterleavedKernelHFace.cu:178).
     float const eps = std::numeric_limits<float>::epsilon();
+    // rows of up to 2048 channels: the packed-arithmetic kernel (tables built once per CTA: few CTAs, many tiles each)
+#define B200_IL_PACKED_CASE(N)                                                                                         \
+    if (ni == N)                                                                                                       \
+    {                                                                                                                  \
+        int const gridP = gridFor(tiles, N <= 2 ? 3 : 2);                                                              \
+        skipLnInterleavedPackedKernel<N, PRELN><<<gridP, kThreads, static_cast<size_t>(ld) * 4, stream>>>(              \
+            ld, total, in, skip, beta, gamma, out, preln, dqIn, dqSkip, qScale, qSkipScale, eps);                      \
+        return checkLaunch("skipLnInterleavedPackedKernel");                                                           \
+    }
+    B200_IL_PACKED_CASE(1)
+    B200_IL_PACKED_CASE(2)
+    B200_IL_PACKED_CASE(3)
+    B200_IL_PACKED_CASE(4)
+#undef B200_IL_PACKED_CASE
 #define B200_IL_CASE(N)                                                                                                \
     if (ni == N)                                                                                                       \
     {                                                                                                                  \
