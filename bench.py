@@ -665,6 +665,24 @@ def run_sweep(args):
         ms = time_rotating_graph(lambda s, st: T.mha(s[0], B, S, N, cu_seqlens=cu, scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=1.0 / 64,
                                                      out=s[1]), sets8)
         row["int8"] = {"ms": ms, "tops": flops / ms / 1e9, "frac_of_int8_probe": flops / ms / 1e9 / res["peaks"]["int8_mma_tops_probe"]}
+        if S == 384:
+            # the CHW32-interleaved INT8 form of plugin version 6 (same values, other layout)
+            tot = S * B
+            mk_il = lambda: (torch.randint(-127, 127, (3 * N * d // 32, tot, 32), device=dev, dtype=torch.int8),
+                             torch.empty((N * d // 32, tot, 32), device=dev, dtype=torch.int8))
+            sets_il = rotating(mk_il, tot * 4 * N * d)
+            ms = time_rotating_graph(lambda s, st: T.mha(s[0], B, S, N, cu_seqlens=cu, scale_bmm1=s1, scale_softmax=127.0, scale_bmm2=1.0 / 64,
+                                                         interleaved=True, out=s[1]), sets_il)
+            row["int8_interleaved"] = {"ms": ms, "tops": flops / ms / 1e9}
+            if ref is not None:
+                try:
+                    ms = time_rotating_graph(lambda s, st: ref.lib.ref_fmha_v2(
+                        vp(st), 2, B, S, N, d, tot, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 1, C.c_float(s1),
+                        C.c_float(127.0), C.c_float(1.0 / 64)), sets_il)
+                    row["int8_interleaved"]["reference_tops"] = flops / ms / 1e9
+                except Exception as e:
+                    row["int8_interleaved"]["reference_error"] = str(e)
+            del sets_il
         if ref is not None:
             def ref16(s, st):
                 ref.lib.ref_fmha_v2(vp(st), 1, B, S, N, d, S * B, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu.data_ptr()), 0,
@@ -769,6 +787,23 @@ def run_sweep(args):
             row["reference_gbs"] = nbytes / ms / 1e6
         emb.append(row)
     res["emb_layer_norm"] = emb
+
+    # the packed (variable-length) embedding kernel on the lengths of benchmark configuration 4
+    lens = np.random.default_rng(1).integers(32, 385, size=256).astype(np.int32)
+    cu4 = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(dev)
+    tot4 = int(lens.sum())
+    sets = rotating(lambda: (torch.randint(0, vocab, (tot4,), device=dev, dtype=torch.int32),
+                             torch.randint(0, 2, (tot4,), device=dev, dtype=torch.int32)), 1, min_total=0)
+    nbytes = tot4 * (2 * E * 2 + 8)
+    ms = time_rotating_graph(lambda s, st: T.emb_layer_norm_var_seqlen(s[0], s[1], cu4, 384, word, pos, tok, gam, bet), sets)
+    row = {"sequences": 256, "tokens": tot4, "ms": ms, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / peaks["hbm"]}
+    if ref is not None:
+        outr = torch.empty(tot4, E, device=dev, dtype=torch.float16)
+        ms = time_rotating_graph(lambda s, st: ref.lib.ref_emb_layer_norm_var_seqlen(
+            vp(st), E, 256, 384, vp(s[0].data_ptr()), vp(s[1].data_ptr()), vp(cu4.data_ptr()), vp(bet.data_ptr()), vp(gam.data_ptr()),
+            vp(word.data_ptr()), vp(pos.data_ptr()), vp(tok.data_ptr()), vocab, 2, vp(outr.data_ptr()), None), sets)
+        row["reference_gbs"] = nbytes / ms / 1e6
+    res["emb_layer_norm_var_seqlen"] = row
 
     # the four FC shapes of a BERT-large layer at 24576 tokens (+ a square one): tera-operations/s per epilogue, operands
     # rotated; torch.matmul (cuBLAS, FP16, no epilogue) on the same operands as the library bar
