@@ -99,7 +99,7 @@ def cpu_forward_rate(batch_hint=None, budget_s=15.0, steps=1, warmup=0):
 
     if batch_hint is None:
         t1 = run(1)
-        batch_hint = max(1, min(16, int(budget_s / max(t1, 1e-3))))
+        batch_hint = max(1, min(64, int(budget_s / max(t1, 1e-3))))
     for _ in range(warmup):
         run(batch_hint)
     times = [run(batch_hint) for _ in range(steps)]

