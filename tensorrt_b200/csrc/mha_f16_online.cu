@@ -306,6 +306,22 @@ struct Walker
     }
 };
 
+// The loads [first, last) of a ring of kStages stages, in load order, for a thread that reads none of them: wait until
+// each block has landed, hand its stage back. Out of line: it runs once per tile at most and the kernel is sensitive to
+// the size of its hot code.
+static __device__ __noinline__ bool passThroughLoads(
+    uint32_t fullAddr, uint32_t emptyAddr, uint32_t first, uint32_t last, volatile uint32_t* abortFlag)
+{
+    for (uint32_t L = first; L < last; ++L)
+    {
+        uint32_t const stage = L % kStages;
+        if (!mbarWaitAddr(fullAddr + 8 * stage, (L / kStages) & 1u, abortFlag, kWaitTmaFull))
+            return false;
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(emptyAddr + 8 * stage) : "memory");
+    }
+    return true;
+}
+
 template <bool BNSD>
 __global__ void __maxnreg__(168)
     mhaOnlineF16Kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -462,16 +478,21 @@ __global__ void __maxnreg__(168)
             auto commitAddr = [](uint32_t barAddr) {
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(barAddr) : "memory");
             };
-            // A ring stage goes back to the loader when the MMAs of BOTH streams that read it have completed: each stream
-            // commits once, with its last tile of the sub-item; a sub-item of a single tile has no second stream, and its
-            // thread adds the missing arrival itself.
+            // A ring stage goes back to the loader when BOTH streams' MMA threads are done with it: each commits once, with
+            // its last tile of the sub-item. A sub-item of a single tile is read by one stream only; the other stream's
+            // thread still takes part in every one of its loads (passThrough below).
             auto release = [&](uint32_t stage, Walker const& w) {
                 if (w.t >= w.subEnd - 2)
-                {
                     commitAddr(emptyAddr + 8 * stage);
-                    if (w.subTiles == 1)
-                        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(emptyAddr + 8 * stage) : "memory");
-                }
+            };
+            // The loads of a single-tile sub-item of the OTHER stream, in load order: wait until the block has landed, hand
+            // the stage back. A parity wait on an mbarrier is only valid for the barrier's NEXT phase, so a thread that
+            // waits on the `full` barrier of a ring stage has to have seen every earlier fill of that stage - also the
+            // fills whose data it never reads. (Skipping them - the other stream's thread adding the second arrival - let
+            // a thread that came back to a stage two fills later see "complete" at once and multiply blocks that had not
+            // landed: with many long sequences per CTA the attention hung until the waits expired.)
+            auto passThrough = [&](Walker const& w) {
+                ok = ok && passThroughLoads(fullAddr, emptyAddr, w.loadBase, w.loadBase + 2u * static_cast<uint32_t>(w.g.nb), abortFlag);
             };
             // scores of key block j of the tile `w` stands on
             auto issueQk = [&](Walker const& w, int32_t j) {
@@ -507,9 +528,16 @@ __global__ void __maxnreg__(168)
 
             TR_DECL(2 + s);
             Walker cur(args, geoTable);
-            bool active = cur.begin() && (s == 0 || cur.next());
+            bool active = cur.begin();
+            if (s == 1 && active)
+            {
+                // tile 0 is stream 0's
+                if (cur.subTiles == 1)
+                    passThrough(cur);
+                active = cur.next();
+            }
             uint32_t qk = 0, pv = 0; // groups of score / context MMAs issued so far
-            if (active)
+            if (active && ok)
             {
                 ok = mbarWaitAddr(qFullAddr, (cur.n >> 1) & 1u, abortFlag, kWaitTmaFull);
                 if (ok)
@@ -518,36 +546,62 @@ __global__ void __maxnreg__(168)
             }
             while (active && ok)
             {
+                // the other stream's tile that follows this one, then this stream's next tile
                 Walker nxt = cur;
-                bool const hasNext = nxt.next() && nxt.next();
+                bool const hasMid = nxt.next();
+                bool const midAlone = hasMid && nxt.subTiles == 1; // a sub-item this thread reads nothing of
+                uint32_t const midFirst = nxt.loadBase, midBlocks = static_cast<uint32_t>(nxt.g.nb);
+                bool const hasNext = hasMid && nxt.next();
                 for (int j = 0; j < cur.g.nb && ok; ++j)
                 {
-                    // the scores that follow block j: block j + 1, or the first block of the stream's next tile
-                    if (j + 1 < cur.g.nb)
-                    {
+                    // Two things to issue per block: the scores that follow block j - block j + 1, or the first block of the
+                    // stream's next tile - and the context product of block j. The scores go first, so that the tensor pipe
+                    // has them done when the softmax threads come for them. Across a tile boundary the wait for their
+                    // operands then holds back the product whose completion frees this tile's last V stage, and the loader
+                    // works in load order: that is safe only while fewer than eleven loads lie between that V block and the
+                    // next tile's first K block (none when the tiles share sub-items; the 2 nb loads of the other stream's
+                    // tile when that is a sub-item of its own). With more, the loader would need the stage of that very V
+                    // block first - a cycle - and the product goes first. (One call site each for the two MMA groups: the
+                    // kernel is sensitive to the size of its code.)
+                    bool const lastBlock = j + 1 == cur.g.nb;
+                    bool qkPending = !lastBlock || hasNext, pvPending = true;
+                    bool const qkFirst = !lastBlock || !midAlone || midBlocks <= 5;
+                    bool midPending = lastBlock && midAlone;
+                    if (qkPending)
                         ok = mbarWaitAddr(sFreeAddr, (qk - 1) & 1u, abortFlag, kWaitAccFree);
-                        TR_EVT(1);
-                        if (ok)
-                            issueQk(cur, j + 1);
-                        TR_EVT(2);
-                        ++qk;
-                    }
-                    else if (hasNext)
+                    TR_EVT(1);
+#pragma unroll 1
+                    while ((qkPending || pvPending) && ok)
                     {
-                        ok = mbarWaitAddr(sFreeAddr, (qk - 1) & 1u, abortFlag, kWaitAccFree)
-                            && mbarWaitAddr(qFullAddr, (nxt.n >> 1) & 1u, abortFlag, kWaitTmaFull);
-                        TR_EVT(1);
-                        if (ok)
-                            issueQk(nxt, 0);
-                        TR_EVT(2);
-                        ++qk;
+                        if (qkPending && (qkFirst || !pvPending))
+                        {
+                            if (lastBlock)
+                            {
+                                if (midPending)
+                                    ok = passThroughLoads(fullAddr, emptyAddr, midFirst, midFirst + 2u * midBlocks, abortFlag);
+                                midPending = false;
+                                ok = ok && mbarWaitAddr(qFullAddr, (nxt.n >> 1) & 1u, abortFlag, kWaitTmaFull);
+                            }
+                            if (ok)
+                                issueQk(lastBlock ? nxt : cur, lastBlock ? 0 : j + 1);
+                            TR_EVT(2);
+                            ++qk;
+                            qkPending = false;
+                        }
+                        else
+                        {
+                            ok = mbarWaitAddr(pReadyAddr, pv & 1u, abortFlag, kWaitSoftmax);
+                            TR_EVT(3);
+                            if (ok)
+                                issuePv(cur, j);
+                            TR_EVT(4);
+                            ++pv;
+                            pvPending = false;
+                        }
                     }
-                    ok = ok && mbarWaitAddr(pReadyAddr, pv & 1u, abortFlag, kWaitSoftmax);
-                    TR_EVT(3);
-                    if (ok)
-                        issuePv(cur, j);
-                    TR_EVT(4);
-                    ++pv;
+                    // the other stream's last tile, when this stream has none after it
+                    if (midPending && ok)
+                        ok = passThroughLoads(fullAddr, emptyAddr, midFirst, midFirst + 2u * midBlocks, abortFlag);
                 }
                 cur = nxt;
                 active = hasNext;

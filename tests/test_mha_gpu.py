@@ -437,3 +437,33 @@ def test_mha_benchmark_size_against_oracle(cuda, packed, int8):
             ref = O.mha(seq, 1, S, N, d, **one)
             ok, worst, bad = O.close_abs_or_rel(got, ref, 1e-2, 1e-2)
             assert ok, (b, worst, bad)
+
+
+@pytest.mark.parametrize("seed,N,B,smax", [(1, 16, 39, 1500), (2, 16, 31, 1500), (3, 12, 24, 900), (4, 3, 40, 700)])
+def test_mha_fp16_many_long_ragged_sequences(cuda, seed, N, B, smax):
+    """Many sequences of very different lengths per CTA, most of them longer than the K / V ring holds: work units of
+    one or three query tiles, so that the two query streams of a CTA sit on different sequences and each stage of the
+    ring is filled several times between two visits of the same stream. The status word must stay 0 (no bounded wait
+    may expire) and sampled sequences must match a float32 reference."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(seed)
+    d = 64
+    lengths = rng.integers(1, smax + 1, size=B).astype(np.int32)
+    lengths[0] = smax
+    cu = O.cu_seqlens(lengths)
+    total = int(cu[-1])
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    qkv = torch.randn(total, 3 * N * d, generator=g).half().to(cuda)
+    st = _status(cuda)
+    out = T.mha(qkv, B, int(lengths.max()), N, cu_seqlens=_t(cu, cuda), status=st)
+    torch.cuda.synchronize()
+    assert int(st[0]) == 0
+    x = qkv.float().view(total, N, 3, d)
+    o = out.float().view(total, N, d)
+    for b in (0, 1, B // 2, B - 1):
+        lo, hi = int(cu[b]), int(cu[b + 1])
+        q, k, v = (x[lo:hi, :, i].transpose(0, 1) for i in range(3))
+        ref = (torch.softmax(q @ k.transpose(-1, -2) * d ** -0.5, -1) @ v).transpose(0, 1)
+        err = (o[lo:hi] - ref).abs()
+        assert bool(((err <= 1e-2) | (err <= 1e-2 * ref.abs())).all()), float(err.max())
