@@ -992,6 +992,14 @@ int32_t launchDqq(cudaStream_t stream, int32_t ld, int64_t rows, int8_t const* i
         // tables built once per CTA: few CTAs with many rows each
         int const grid = gridFor((rows + rowsPerCta - 1) / rowsPerCta, 3);
         size_t const smem = static_cast<size_t>(ld) * 2 * 3; // three half2 tables of ld / 2 entries
+        // rows of 8192 values: the tables plus the kernel's static scratch pass the 48 KB a launch gets without asking
+        if (smem > 40 * 1024)
+        {
+            cudaFuncSetAttribute(skipLnDqqPackedKernel<CPL <= 2 ? CPL : 1, WPR, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                static_cast<int>(smem));
+            cudaFuncSetAttribute(skipLnDqqPackedKernel<CPL <= 2 ? CPL : 1, WPR, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                static_cast<int>(smem));
+        }
         if (bias)
             launchDependent(skipLnDqqPackedKernel<CPL <= 2 ? CPL : 1, WPR, true>, dim3(grid), dim3(kThreads), smem, stream, ld, rows, in,
                 skip, beta, gamma, bias, out, dqIn, dqSkip, qScale, 0.f);

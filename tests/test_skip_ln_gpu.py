@@ -74,7 +74,7 @@ def _int8_case(rng, rows, ld):
     return x, s, g, b, bi
 
 
-@pytest.mark.parametrize("ld", [16, 256, 768, 1024, 4096, 6144, 12288, 16384])
+@pytest.mark.parametrize("ld", [16, 256, 768, 1024, 4096, 6144, 8192, 12288, 16384])
 @pytest.mark.parametrize("bias", [False, True])
 def test_skip_ln_dqq(cuda, ld, bias):
     import tensorrt_b200 as T
