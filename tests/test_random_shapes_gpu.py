@@ -4,7 +4,8 @@ GPU. The shapes are drawn from sets that mix the benchmarked sizes with awkward 
 boundary, many long ragged sequences per CTA): a protocol fault of the FP16 attention kernel only showed with such a
 mix, which none of the hand-picked parity cases had.
 
-Tolerances: FP16 1e-2 abs-or-rel (FC: 4e-3 of max(|ref|, 1)); INT8 within one step of the rounded float reference."""
+Tolerances: FP16 1e-2 abs-or-rel (FC: 4e-3 of max(|ref|, 1)); INT8 within one step of the rounded float reference
+(attention: two steps, at least 97 % of the values identical)."""
 import numpy as np
 import pytest
 import torch
@@ -46,8 +47,9 @@ def test_attention_random_shapes(cuda, seed):
             ref = (torch.softmax(q @ k.transpose(-1, -2) * d ** -0.5, -1) @ v).transpose(0, 1)
             err = (o[lo:hi] - ref).abs()
             assert bool(((err <= 1e-2) | (err <= 1e-2 * ref.abs())).all()), (it, N, d, B, smax, float(err.max()))
-    # INT8: status and determinism (its values are pinned bit for bit elsewhere)
-    for it in range(30):
+    # INT8: the quantised dataflow restated in float64 on the GPU (exact integer products; probabilities and results rounded
+    # to nearest and saturated): at most 2 steps apart, at least 97 % of the values identical
+    for it in range(40):
         N = int(rng.choice([1, 2, 12, 16]))
         d = int(rng.choice([32, 64]))
         B = int(rng.integers(1, 40))
@@ -55,13 +57,28 @@ def test_attention_random_shapes(cuda, seed):
         lengths = rng.integers(0, smax + 1, size=B).astype(np.int32)
         if lengths.sum() == 0:
             lengths[0] = 1
-        cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)).to(cuda)
-        q8 = torch.randint(-127, 128, (int(lengths.sum()), 3 * N * d), device=cuda, dtype=torch.int8)
-        kw = dict(head_size=d, cu_seqlens=cu, scale_bmm1=2e-4, scale_softmax=127.0, scale_bmm2=0.02, status=st)
-        a = T.mha(q8, B, int(max(lengths.max(), 1)), N, **kw)
-        b2 = T.mha(q8, B, int(max(lengths.max(), 1)), N, **kw)
+        cu_h = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        total = int(lengths.sum())
+        x = torch.randn(total, 3 * N * d, device=cuda, dtype=torch.float64)
+        s_qkv = float(x.abs().max()) / 127
+        q8 = torch.clamp(torch.round(x / s_qkv), -127, 127).to(torch.int8)
+        s1 = float(np.float32(s_qkv) * np.float32(s_qkv) * np.float32(d ** -0.5))
+        s2 = float((1.0 / 127.0) * s_qkv / (0.5 * s_qkv))
+        out = T.mha(q8, B, int(max(lengths.max(), 1)), N, head_size=d, cu_seqlens=torch.from_numpy(cu_h).to(cuda), scale_bmm1=s1,
+                    scale_softmax=127.0, scale_bmm2=s2, status=st)
         torch.cuda.synchronize()
-        assert int(st[0]) == 0 and torch.equal(a, b2), (it, N, d, B, smax)
+        assert int(st[0]) == 0, (it, N, d, B, smax)
+        xi, o = q8.double().view(total, N, 3, d), out.view(total, N, d)
+        for b in rng.choice(B, size=min(B, 3), replace=False):
+            lo, hi = int(cu_h[b]), int(cu_h[b + 1])
+            if hi == lo:
+                continue
+            q, k, v = (xi[lo:hi, :, i].transpose(0, 1) for i in range(3))
+            logits = (q @ k.transpose(-1, -2)).float().double() * float(np.float32(s1))
+            pq = torch.clamp(torch.round(torch.softmax(logits, -1) * 127.0), -128, 127)
+            ref = torch.clamp(torch.round((pq @ v) * float(np.float32(s2))), -128, 127).transpose(0, 1)
+            dd = (o[lo:hi].double() - ref).abs()
+            assert float(dd.max()) <= 2 and float((dd == 0).double().mean()) > 0.97, (it, N, d, B, smax, float(dd.max()))
 
 
 @pytest.mark.parametrize("seed", [21])
