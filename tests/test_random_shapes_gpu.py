@@ -1,4 +1,4 @@
-"""Randomised shapes for the three kernel families (seeded): every launch must leave the status word at 0 (no bounded
+"""Randomised shapes for the kernel families (seeded): every launch must leave the status word at 0 (no bounded
 device wait may expire) and agree with a float32 / float64 restatement of the operator computed with torch on the same
 GPU. The shapes are drawn from sets that mix the benchmarked sizes with awkward ones (single rows, sizes just past a tile
 boundary, many long ragged sequences per CTA): a protocol fault of the FP16 attention kernel only showed with such a
@@ -149,3 +149,48 @@ def test_skip_layer_norm_random_shapes(cuda, seed):
             oi = T.skip_layer_norm_interleaved(il(x8), il(s8), g, b, dq1, dq2, q)
             r8 = torch.clamp(torch.round(ln(dq1 * x8.float() + dq2 * s8.float(), 1.19e-7) * q), -128, 127)
             assert float((oi.permute(1, 0, 2).reshape(rows, ld).float() - r8).abs().max()) <= 1, ("interleaved", it, ld, rows)
+
+
+@pytest.mark.parametrize("seed", [41])
+def test_embedding_random_shapes(cuda, seed):
+    """Fixed layout (with the mask index from the same launch) and packed layout with empty sequences; FP16 and FP32
+    tables, row lengths on the vector and on the scalar path."""
+    import tensorrt_b200 as T
+
+    rng = np.random.default_rng(seed)
+
+    def ln(v, g, b):
+        return (v - v.mean(-1, keepdim=True)) * torch.rsqrt(v.var(-1, unbiased=False, keepdim=True)) * g + b
+
+    for it in range(40):
+        E = int(rng.choice([8, 100, 128, 384, 768, 1024, 1536, 4096]))
+        vocab = int(rng.choice([2, 100, 30522]))
+        dt = torch.float16 if rng.integers(0, 2) else torch.float32
+        word, pos, tok = ((0.5 * torch.randn(r, E, device=cuda)).to(dt) for r in (vocab, 512, 2))
+        gam, bet = 1 + 0.1 * torch.randn(E, device=cuda), 0.1 * torch.randn(E, device=cuda)
+        tol = 1e-2 if dt == torch.float16 else 2e-5
+        S, B = int(rng.choice([1, 7, 128, 384, 512])), int(rng.integers(1, 70))
+        ids = torch.randint(0, vocab, (S, B), device=cuda, dtype=torch.int32)
+        seg = torch.randint(0, 2, (S, B), device=cuda, dtype=torch.int32)
+        lengths = rng.integers(0, S + 1, size=B)
+        mask = torch.from_numpy((np.arange(S)[:, None] < lengths[None, :]).astype(np.int32)).to(cuda)
+        out, idx = T.emb_layer_norm(ids, seg, word, pos, tok, gam, bet, mask=mask)
+        ref = ln(word.float()[ids.long()] + tok.float()[seg.long()] + pos.float()[:S, None, :], gam, bet)
+        err = (out.float() - ref).abs()
+        assert bool(((err <= tol) | (err <= tol * ref.abs())).all()), ("fixed", it, E, vocab, S, B, float(err.max()))
+        assert np.array_equal(idx.cpu().numpy(), lengths.astype(np.int32)), ("mask index", it)
+        lens = rng.integers(0, int(rng.choice([1, 33, 385, 512])) + 1, size=int(rng.integers(1, 300))).astype(np.int32)
+        if lens.sum() == 0:
+            lens[0] = 1
+        cu = torch.from_numpy(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)).to(cuda)
+        total = int(lens.sum())
+        pid = torch.randint(0, vocab, (total,), device=cuda, dtype=torch.int32)
+        pseg = torch.randint(0, 2, (total,), device=cuda, dtype=torch.int32)
+        o2, sk = T.emb_layer_norm_var_seqlen(pid, pseg, cu, int(lens.max()), word, pos, tok, gam, bet, with_skip=True)
+        posidx = torch.from_numpy(np.concatenate([np.arange(n) for n in lens]).astype(np.int64)).to(cuda)
+        v = word.float()[pid.long()] + tok.float()[pseg.long()] + pos.float()[posidx]
+        ref = ln(v, gam, bet)
+        err = (o2.float() - ref).abs()
+        assert bool(((err <= tol) | (err <= tol * ref.abs())).all()), ("packed", it, E, vocab, float(err.max()))
+        e2 = (sk.float() - v).abs()
+        assert bool(((e2 <= tol) | (e2 <= tol * v.abs())).all()), ("packed pre-LN sum", it)
